@@ -1,0 +1,182 @@
+// capi.cu -- the extern "C" boundary of libsanta_b200.so (declared in
+// include/santa_b200.h): argument validation, the reference's host-side rules,
+// workspace carving and kernel launches.  No allocation, no host
+// synchronisation, no fallback path.
+
+#include "../../include/santa_b200.h"
+#include "common.cuh"
+#include "santa_abi_internal.h"
+
+#include <cmath>
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = int(e);
+  return SANTA_E_CUDA;
+}
+
+int sm_count_of_current_device(int* out) {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+    *out = cached[dev];
+    return SANTA_OK;
+  }
+  int n = 0;
+  e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  *out = n;
+  return SANTA_OK;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct FlashPlan {
+  int block_n, T_c, ncol, ncg, grid;
+  long long items;
+  size_t off_tickets, off_pvrows, off_partials, total;
+};
+
+int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
+  if (B <= 0 || KVH <= 0) return SANTA_E_SHAPE;
+  if (L_valid <= 0) return SANTA_E_LENGTH;
+  const int bn = santa_block_n_rule(L_valid, block_n);
+  if (bn != 32 && bn != 64 && bn != 256) return SANTA_E_BLOCK_N;
+  int sms = 0;
+  if (int rc = sm_count_of_current_device(&sms)) return rc;
+  pl->block_n = bn;
+  pl->T_c = (L_valid + bn - 1) / bn;
+  pl->ncol = B * KVH;
+  pl->ncg = (pl->ncol + santa::kWarpsPerCta - 1) / santa::kWarpsPerCta;
+  pl->items = (long long)pl->ncg * pl->T_c;
+  pl->grid = int(pl->items < (long long)sms ? pl->items : (long long)sms);
+  const size_t slots = size_t(pl->grid) + size_t(pl->ncg);
+  pl->off_tickets = 256;
+  pl->off_pvrows = pl->off_tickets + align_up(size_t(pl->ncg) * 4, 256);
+  pl->off_partials = pl->off_pvrows + align_up(slots * santa::kWarpsPerCta * 4, 256);
+  pl->total = pl->off_partials +
+              slots * santa::kWarpsPerCta * santa::kGH * santa::kPartialStride * sizeof(float);
+  return SANTA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* santa_strerror(int code) {
+  switch (code) {
+    case SANTA_OK: return "ok";
+    case SANTA_E_DTYPE: return "dtype must be bf16 or f16";
+    case SANTA_E_SHAPE: return "unsupported shape: this build supports only D=128 and GH=4 (H/KVH)";
+    case SANTA_E_LENGTH: return "valid_len must be > 0 and must not exceed the storage length";
+    case SANTA_E_BLOCK_N: return "block_n must be 0 (auto) or one of {32,64,256}";
+    case SANTA_E_WORKSPACE: return "workspace is NULL, not 256-byte aligned, or too small";
+    case SANTA_E_ALIGN: return "q/K/V/out pointers must be 16-byte aligned";
+    case SANTA_E_CUDA: return "a CUDA runtime call failed";
+    case SANTA_E_ARG: return "missing or inconsistent argument";
+    case SANTA_E_TOO_LARGE: return "problem size beyond the limit of this entry point";
+    default: return "unknown error";
+  }
+}
+
+int santa_last_cuda_error(void) { return g_last_cuda_error; }
+int santa_abi_version(void) { return 1; }
+
+int santa_block_n_rule(int L_valid, int block_n) {
+  if (block_n > 0) return block_n;
+  if (L_valid <= 1536) return 32;
+  if (L_valid <= 3072) return 64;
+  return 256;
+}
+
+void santa_flash_budget(int L_valid, int block_n, int64_t S, int* T_c, int* S_per_tile) {
+  const int tc = (L_valid + block_n - 1) / block_n;
+  int spt = 0;
+  if (S > 0) {
+    spt = int(S / tc);
+    if (spt < 1) spt = 1;
+  }
+  if (T_c) *T_c = tc;
+  if (S_per_tile) *S_per_tile = spt;
+}
+
+float santa_u01(uint64_t seed, int head_index, int tile_index) {
+  return santa::u01_from_seed(seed, head_index, tile_index);
+}
+
+size_t santa_flash_workspace_bytes(int B, int KVH, int L_valid, int block_n) {
+  FlashPlan pl;
+  if (plan_flash(B, KVH, L_valid, block_n, &pl) != SANTA_OK) return 0;
+  return pl.total;
+}
+
+int32_t* santa_workspace_status(void* workspace) { return static_cast<int32_t*>(workspace); }
+
+int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
+                       int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
+                       float* m_star, int32_t* vrows, void* workspace, size_t workspace_bytes,
+                       const santa_flash_ext* ext, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!q || !K || !V) return SANTA_E_ARG;
+  if (D != santa::kD || KVH <= 0 || H != santa::kGH * KVH || B <= 0) return SANTA_E_SHAPE;
+  if (L_valid <= 0 || L_valid > L_storage) return SANTA_E_LENGTH;
+  const bool want_partial = ext && ext->partial_out;
+  if (!out && !want_partial) return SANTA_E_ARG;
+  if (ext && ((ext->u16 == nullptr) != (ext->counts == nullptr))) return SANTA_E_ARG;
+  if (ext && ((ext->m_tiles == nullptr) != (ext->ell_tiles == nullptr))) return SANTA_E_ARG;
+  if (!aligned16(q) || !aligned16(K) || !aligned16(V) || (out && !aligned16(out))) return SANTA_E_ALIGN;
+
+  FlashPlan pl;
+  if (int rc = plan_flash(B, KVH, L_valid, block_n, &pl)) return rc;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
+    return SANTA_E_WORKSPACE;
+
+  int T_c = 0, spt = 0;
+  santa_flash_budget(L_valid, pl.block_n, S, &T_c, &spt);
+  if (ext && ext->s_per_tile_override >= 0) spt = ext->s_per_tile_override;
+
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  santa::FlashParams p{};
+  p.q = q;
+  p.K = K;
+  p.V = V;
+  p.B = B;
+  p.H = H;
+  p.KVH = KVH;
+  p.L_valid = L_valid;
+  p.L_storage = L_storage;
+  p.T_c = pl.T_c;
+  p.S_per_tile = spt;
+  p.q_scale = 1.0f / std::sqrt((float)D);  // F.cpp:210
+  p.seed = seed;
+  p.batch_offset = ext ? ext->batch_offset : 0;
+  p.tile_offset = ext ? ext->tile_offset : 0;
+  p.ncol = pl.ncol;
+  p.items = pl.items;
+  p.status = reinterpret_cast<int*>(ws);
+  p.tickets = reinterpret_cast<unsigned*>(ws + pl.off_tickets);
+  p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
+  p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.out = out;
+  p.m_star = m_star;
+  p.vrows = vrows;
+  p.partial_out = want_partial ? ext->partial_out : nullptr;
+  p.dbg_m = ext ? ext->m_tiles : nullptr;
+  p.dbg_ell = ext ? ext->ell_tiles : nullptr;
+  p.dbg_u = ext ? ext->u16 : nullptr;
+  p.dbg_c = ext ? ext->counts : nullptr;
+  p.rowmask = ext ? ext->rowmask : nullptr;
+
+  cudaError_t e = santa::launch_flash(p, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+}  // extern "C"

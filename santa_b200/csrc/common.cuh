@@ -1,0 +1,138 @@
+// common.cuh -- device helpers shared by the Flash and Prop translation units.
+//
+// Everything here is header-only so that each translation unit compiles it
+// under its own floating-point flags: the Flash unit is built with
+// --use_fast_math (approximate division, flush-to-zero) and the Prop unit
+// without, exactly as the reference builds its two extensions
+// (flash_style_fused_santa_fixed_tile_budgets/setup.py:15-20,
+//  santa_fused_proportional_tile_budgets/setup.py:39-42).  Sampled row counts
+// are only reproducible bit-for-bit when those flags agree.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <cstdint>
+
+namespace santa {
+
+constexpr int kD = 128;             // head_dim of the vectorised kernels
+constexpr int kGH = 4;              // query heads per kv-head of the vectorised kernels
+constexpr int kRowBytes = kD * 2;   // one K/V row of one kv-head
+constexpr int kChunkRows = 32;      // rows staged per pipeline stage (one row per lane)
+constexpr int kStageBytes = kChunkRows * kRowBytes;
+constexpr int kWarpsPerCta = 8;     // one warp per kv-head column of a column group
+constexpr int kPartialStride = 132; // floats per (slot, warp, head): A[128], m, Z, pad
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+// status word values (0 = ok)
+enum : int {
+  kStatusOk = 0,
+  kStatusStageTimeout = 1,  // a staged K chunk never arrived
+};
+
+// ---------------------------------------------------------------- RNG
+// splitmix64 finaliser over seed ^ (h << 32 ^ t); top 53 bits -> [0,1] double
+// -> float.  Restates flash_style_fused_santa_fixed_tile_budgets/
+// santa_cuda_kernel.cu:74-87 (same function at
+// santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:557-570).
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  uint64_t z = x + 0x9e3779b97f4a7c15ULL;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+  return z ^ (z >> 31);
+}
+__host__ __device__ __forceinline__ float u01_from_seed(uint64_t seed, int h, int t) {
+  const uint64_t key = seed ^ ((uint64_t(int64_t(h)) << 32) ^ uint64_t(int64_t(t)));
+  const uint64_t r = mix64(key);
+  const double u = double(r >> 11) * (1.0 / 9007199254740992.0);
+  return float(u);
+}
+
+// ---------------------------------------------------------------- 16-bit storage
+template <typename TK>
+struct Store16;
+
+template <>
+struct Store16<__nv_bfloat16> {
+  // two packed values -> two floats (element 0 in the low half)
+  static __device__ __forceinline__ float2 unpack(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+  // round to storage precision, return as float
+  static __device__ __forceinline__ float round(float x) {
+    return __bfloat162float(__float2bfloat16(x));
+  }
+  static __device__ __forceinline__ uint16_t bits(float x) {
+    return __bfloat16_as_ushort(__float2bfloat16(x));
+  }
+};
+
+template <>
+struct Store16<__half> {
+  static __device__ __forceinline__ float2 unpack(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+  static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ uint16_t bits(float x) {
+    return __half_as_ushort(__float2half_rn(x));
+  }
+};
+
+// ---------------------------------------------------------------- async staging
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false when the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// One bulk asynchronous copy global -> shared, completion counted on `bar`.
+// Source, destination and size must be multiples of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// ---------------------------------------------------------------- work split
+// `items` work items are dealt to `ctas` CTAs in contiguous, balanced ranges:
+// CTA i owns [lo(i), lo(i+1)) with lo(i) = floor(i*items/ctas).
+__host__ __device__ __forceinline__ long long range_lo(long long i, long long items, long long ctas) {
+  return (i * items) / ctas;
+}
+// the CTA whose range contains item x (requires items >= ctas)
+__host__ __device__ __forceinline__ int cta_of_item(long long x, long long items, long long ctas) {
+  return int(((x + 1) * ctas - 1) / items);
+}
+
+}  // namespace santa

@@ -1,0 +1,152 @@
+"""Python host mirror of the reference operator surface, over the C ABI.
+
+``flash_decode`` / ``prop_decode`` take the same positional and keyword
+arguments, tensor layouts and seed semantics as the reference's
+``santa_flash_batch_cuda.decode_systematic_{batched,scalar}`` and
+``santa_prop_batch_cuda.decode_systematic_scalar`` (santa_cuda.cpp:174-359 of
+flash_style_fused_santa_fixed_tile_budgets, santa_cuda.cpp:270-359 of
+santa_fused_proportional_tile_budgets), raise ``RuntimeError`` with the same
+messages on bad input, and return ``(out, m_star, vrows)``.  Extra keyword-only
+arguments expose what the sharded runs and the parity tests need.  PyTorch only
+supplies device memory and the current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import capi
+
+_workspaces: Dict[Tuple[str, int, int], torch.Tensor] = {}
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _workspace(kind: str, device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch, one per (kind, device, stream); grown on demand.
+
+    Calls on one stream are ordered, so they can share the scratch; the kernels
+    leave it zeroed where it has to be."""
+    stream = torch.cuda.current_stream(device).cuda_stream
+    key = (kind, device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    return capi.SANTA_DTYPE_BF16 if t.dtype == torch.bfloat16 else capi.SANTA_DTYPE_F16
+
+
+@dataclass
+class FlashTrace:
+    """Per-tile and per-row intermediates of one Flash call (parity tests)."""
+    block_n: int
+    T_c: int
+    S_per_tile: int
+    m_tiles: torch.Tensor    # [B,H,T_c] fp32
+    ell_tiles: torch.Tensor  # [B,H,T_c] fp32
+    u16: torch.Tensor        # [B,H,L] int16 view of storage bits
+    counts: torch.Tensor     # [B,H,L] int16
+    rowmask: torch.Tensor    # [B,KVH,L] int32
+
+
+def _check_flash_inputs(q_h, K_g, V_g):
+    # messages follow flash_style_fused_santa_fixed_tile_budgets/santa_cuda.cpp:123-171
+    _check(q_h.is_cuda, "q_h must be CUDA")
+    _check(K_g.is_cuda and V_g.is_cuda, "K_g and V_g must be CUDA")
+    _check(q_h.dtype in (torch.bfloat16, torch.float16), "q_h must be bf16 or f16")
+    _check(K_g.dtype in (torch.bfloat16, torch.float16), "K_g must be bf16 or f16")
+    _check(K_g.dtype == V_g.dtype, "K_g and V_g must have the same dtype")
+    _check(q_h.dtype == K_g.dtype, "q_h dtype must match K_g/V_g dtype")
+    _check(q_h.device == K_g.device and q_h.device == V_g.device, "device mismatch")
+    _check(K_g.is_contiguous() and V_g.is_contiguous(),
+           "K_g/V_g must be contiguous. Expected [L,KVH,D] for single or [B,L,KVH,D] for batch.")
+    if q_h.dim() == 2:
+        _check(K_g.dim() == 3 and V_g.dim() == 3, "Single-request path expects q_h [H,D], K_g/V_g [L,KVH,D]")
+        _check(K_g.shape == V_g.shape, "K_g and V_g must have the same shape")
+        _check(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))")
+        return False, 1, q_h.size(0), q_h.size(1), K_g.size(0), K_g.size(1)
+    _check(q_h.dim() == 3 and K_g.dim() == 4 and V_g.dim() == 4,
+           "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]")
+    _check(K_g.shape == V_g.shape, "K_g and V_g must have the same shape")
+    _check(q_h.size(0) == K_g.size(0), "Batch mismatch between q_h and K_g/V_g")
+    _check(q_h.size(2) == K_g.size(3), "D mismatch (q_h.size(2) vs K_g.size(3))")
+    return True, q_h.size(0), q_h.size(1), q_h.size(2), K_g.size(1), K_g.size(2)
+
+
+def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_len=-1, *,
+                 batch_offset=0, tile_offset=0, s_per_tile=None, partial=False, trace=False):
+    """S2ANTA-Flash decode.  Returns ``(out, m_star, vrows)``; with ``partial=True``
+    the first element is the unnormalised partial ``[B,H,130]`` fp32 instead of
+    ``out``; with ``trace=True`` a ``FlashTrace`` is appended."""
+    batched, B, H, D, L_storage, KVH = _check_flash_inputs(q_h, K_g, V_g)
+    if seed < 0:
+        raise TypeError("seed must be a non-negative 64-bit integer")
+    q = q_h.contiguous()
+    L = int(valid_len) if valid_len > 0 else L_storage
+    _check(L > 0, f"valid_len must be > 0; got {L}")
+    _check(L <= L_storage, f"valid_len exceeds storage length: valid_len={L} storage={L_storage}")
+    _check(D == 128, f"This build supports only D=128. Got D={D}")
+    _check(H % KVH == 0, f"H must be divisible by KVH. Got H={H} KVH={KVH}")
+    _check(H // KVH == 4, f"This build supports only GH=4 (H/KVH). Got GH={H // KVH} (H={H} KVH={KVH})")
+    bn = capi.block_n_rule(L, int(block_n))
+    _check(bn in (32, 64, 256), f"block_n must be 0 (auto) or one of {{32,64,256}}. Got block_n={bn}")
+    T_c, spt = capi.flash_budget(L, bn, int(S))
+    if s_per_tile is not None:
+        spt = int(s_per_tile)
+
+    dev = q.device
+    with torch.cuda.device(dev):
+        lib = capi.lib()
+        nbytes = lib.santa_flash_workspace_bytes(B, KVH, L, bn)
+        ws = _workspace("flash", dev, nbytes)
+        fopt = dict(device=dev, dtype=torch.float32)
+        out = None if partial else torch.empty((B, H, D) if batched else (H, D), device=dev, dtype=q.dtype)
+        m_star = torch.empty((B, H) if batched else (H,), **fopt)
+        vrows = torch.empty((B, KVH) if (want_vrows and batched) else ((KVH,) if want_vrows else (0,)),
+                            device=dev, dtype=torch.int32)
+        ext = capi.FlashExt(batch_offset=int(batch_offset), tile_offset=int(tile_offset),
+                            s_per_tile_override=-1 if s_per_tile is None else int(s_per_tile))
+        part = None
+        if partial:
+            part = torch.empty((B, H, D + 2), **fopt)
+            ext.partial_out = part.data_ptr()
+        tr = None
+        if trace:
+            tr = FlashTrace(bn, T_c, spt,
+                            torch.empty((B, H, T_c), **fopt), torch.empty((B, H, T_c), **fopt),
+                            torch.zeros((B, H, L), device=dev, dtype=torch.int16),
+                            torch.zeros((B, H, L), device=dev, dtype=torch.int16),
+                            torch.zeros((B, KVH, L), device=dev, dtype=torch.int32))
+            ext.m_tiles, ext.ell_tiles = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr()
+            ext.u16, ext.counts, ext.rowmask = tr.u16.data_ptr(), tr.counts.data_ptr(), tr.rowmask.data_ptr()
+        rc = lib.santa_flash_decode(
+            q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), _dtype_code(q), B, H, KVH, D, L, L_storage,
+            int(S), int(seed) & (2**64 - 1), bn,
+            None if out is None else out.data_ptr(), m_star.data_ptr(),
+            vrows.data_ptr() if want_vrows else None,
+            ws.data_ptr(), ws.numel(), C.byref(ext), torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    res = (part if partial else out, m_star, vrows)
+    return res + (tr,) if trace else res
+
+
+def workspace_status(kind: str, device: torch.device) -> int:
+    """Synchronise and read the status word of the scratch used on the current stream."""
+    stream = torch.cuda.current_stream(device).cuda_stream
+    key = (kind, device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        return 0
+    torch.cuda.synchronize(device)
+    return int(ws[:4].view(torch.int32).item())
