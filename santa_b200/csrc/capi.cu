@@ -35,13 +35,48 @@ int sm_count_of_current_device(int* out) {
   return SANTA_OK;
 }
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library
+// does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map of a K cache [B][L_storage][KVH][128] of 16-bit elements with a
+// {128, 1, kStageRows, 1} box: one kv-head's rows of kStageRows tokens.
+int encode_k_map(CUtensorMap* tm, const void* K, int B, int L_storage, int KVH) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return cuda_fail(cudaErrorNotSupported);
+  const cuuint64_t dims[4] = {cuuint64_t(santa::kD), cuuint64_t(KVH), cuuint64_t(L_storage), cuuint64_t(B)};
+  const cuuint64_t strides[3] = {cuuint64_t(santa::kRowBytes), cuuint64_t(KVH) * santa::kRowBytes,
+                                 cuuint64_t(L_storage) * KVH * santa::kRowBytes};
+  const cuuint32_t box[4] = {cuuint32_t(santa::kD), 1u, cuuint32_t(santa::kStageRows), 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(K), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+  return SANTA_OK;
+}
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct FlashPlan {
   int block_n, T_c, ncol, ncg, grid;
   long long items;
-  size_t off_tickets, off_pvrows, off_partials, total;
+  size_t off_pvrows, off_partials, total;
 };
 
 int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
@@ -54,15 +89,15 @@ int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
   pl->block_n = bn;
   pl->T_c = (L_valid + bn - 1) / bn;
   pl->ncol = B * KVH;
-  pl->ncg = (pl->ncol + santa::kWarpsPerCta - 1) / santa::kWarpsPerCta;
+  pl->ncg = (pl->ncol + santa::kGroupWarps - 1) / santa::kGroupWarps;
   pl->items = (long long)pl->ncg * pl->T_c;
-  pl->grid = int(pl->items < (long long)sms ? pl->items : (long long)sms);
-  const size_t slots = size_t(pl->grid) + size_t(pl->ncg);
-  pl->off_tickets = 256;
-  pl->off_pvrows = pl->off_tickets + align_up(size_t(pl->ncg) * 4, 256);
-  pl->off_partials = pl->off_pvrows + align_up(slots * santa::kWarpsPerCta * 4, 256);
+  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
+  pl->grid = int(pl->items < (long long)sms ? pl->items : (long long)sms);  // one persistent CTA per SM
+  const size_t slots = size_t(santa::kGroupsPerCta) * pl->grid + size_t(pl->ncg);
+  pl->off_pvrows = 256;
+  pl->off_partials = pl->off_pvrows + align_up(slots * santa::kGroupWarps * 4, 256);
   pl->total = pl->off_partials +
-              slots * santa::kWarpsPerCta * santa::kGH * santa::kPartialStride * sizeof(float);
+              slots * santa::kGroupWarps * santa::kGH * santa::kPartialStride * sizeof(float);
   return SANTA_OK;
 }
 
@@ -144,6 +179,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   santa::FlashParams p{};
+  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH)) return rc;
   p.q = q;
   p.K = K;
   p.V = V;
@@ -161,20 +197,29 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   p.ncol = pl.ncol;
   p.items = pl.items;
   p.status = reinterpret_cast<int*>(ws);
-  p.tickets = reinterpret_cast<unsigned*>(ws + pl.off_tickets);
   p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
   p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
-  p.out = out;
-  p.m_star = m_star;
-  p.vrows = vrows;
-  p.partial_out = want_partial ? ext->partial_out : nullptr;
   p.dbg_m = ext ? ext->m_tiles : nullptr;
   p.dbg_ell = ext ? ext->ell_tiles : nullptr;
   p.dbg_u = ext ? ext->u16 : nullptr;
   p.dbg_c = ext ? ext->counts : nullptr;
   p.rowmask = ext ? ext->rowmask : nullptr;
 
-  cudaError_t e = santa::launch_flash(p, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
+  santa::FlashMergeParams mp{};
+  mp.H = H;
+  mp.KVH = KVH;
+  mp.T_c = pl.T_c;
+  mp.S_per_tile = spt;
+  mp.items = pl.items;
+  mp.ctas = pl.grid;
+  mp.partials = p.partials;
+  mp.partial_vrows = p.partial_vrows;
+  mp.out = out;
+  mp.m_star = m_star;
+  mp.vrows = vrows;
+  mp.partial_out = want_partial ? ext->partial_out : nullptr;
+
+  cudaError_t e = santa::launch_flash(p, mp, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   return SANTA_OK;
 }

@@ -21,9 +21,12 @@ namespace santa {
 constexpr int kD = 128;             // head_dim of the vectorised kernels
 constexpr int kGH = 4;              // query heads per kv-head of the vectorised kernels
 constexpr int kRowBytes = kD * 2;   // one K/V row of one kv-head
-constexpr int kChunkRows = 32;      // rows staged per pipeline stage (one row per lane)
-constexpr int kStageBytes = kChunkRows * kRowBytes;
-constexpr int kWarpsPerCta = 8;     // one warp per kv-head column of a column group
+constexpr int kChunkRows = 32;      // rows per sampler chunk (one row per lane, as in the reference scan)
+constexpr int kStageRows = 16;      // rows staged per pipeline slot
+constexpr int kStageBytes = kStageRows * kRowBytes;
+constexpr int kGroupWarps = 8;      // one warp per kv-head column of a column group
+constexpr int kGroupsPerCta = 2;    // independent warp groups per CTA (one CTA per SM)
+constexpr int kMaxCtas = 256;       // upper bound on persistent CTAs (>= SM count)
 constexpr int kPartialStride = 132; // floats per (slot, warp, head): A[128], m, Z, pad
 constexpr uint32_t kSpinLimit = 1u << 24;
 
@@ -124,6 +127,18 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       : "memory");
 }
 
+// One tiled TMA load of a 4-D box (coordinates innermost first) global -> shared.
+// `tmap` must live in kernel-parameter, constant or global memory.  The
+// innermost coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
+      "[%6];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- work split
 // `items` work items are dealt to `ctas` CTAs in contiguous, balanced ranges:
 // CTA i owns [lo(i), lo(i+1)) with lo(i) = floor(i*items/ctas).
@@ -133,6 +148,21 @@ __host__ __device__ __forceinline__ long long range_lo(long long i, long long it
 // the CTA whose range contains item x (requires items >= ctas)
 __host__ __device__ __forceinline__ int cta_of_item(long long x, long long items, long long ctas) {
   return int(((x + 1) * ctas - 1) / items);
+}
+// Each CTA runs two independent warp groups; group v = 2*cta + half owns the
+// first ceil(n/2) (half 0) or the remaining floor(n/2) (half 1) items of its
+// CTA's range.  A half-1 range is empty when the CTA owns a single item.
+__host__ __device__ __forceinline__ void group_range(int v, long long items, long long ctas, long long* lo,
+                                                     long long* hi) {
+  const long long a = range_lo(v >> 1, items, ctas), b = range_lo((v >> 1) + 1, items, ctas);
+  const long long mid = a + (b - a + 1) / 2;
+  *lo = (v & 1) ? mid : a;
+  *hi = (v & 1) ? b : mid;
+}
+__host__ __device__ __forceinline__ int group_of_item(long long x, long long items, long long ctas) {
+  const int i = cta_of_item(x, items, ctas);
+  const long long a = range_lo(i, items, ctas), b = range_lo(i + 1, items, ctas);
+  return 2 * i + (x >= a + (b - a + 1) / 2 ? 1 : 0);
 }
 
 }  // namespace santa

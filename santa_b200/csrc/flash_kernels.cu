@@ -1,9 +1,14 @@
 // flash_kernels.cu -- S2ANTA-Flash decode attention (fixed per-tile sample
-// budget) for sm_100a: one persistent launch that streams K once, samples rows
-// by systematic resampling inside every tile, gathers the sampled V rows and
-// merges tiles with a running log-sum-exp; the last CTA to finish a column
-// group folds the per-CTA partials into the output, so there is no second
-// launch and no device-side wait.
+// budget) for sm_100a.  Two launches on one stream, chained with programmatic
+// dependent launch:
+//   flash_decode_kernel  persistent; streams K once through TMA, samples rows by
+//                        systematic resampling inside every tile, gathers the
+//                        sampled V rows and folds tiles into a running
+//                        log-sum-exp state; every warp group writes one partial
+//                        (A[128], m, Z per head) per column group it touched;
+//   flash_merge_kernel   one small CTA per (batch, head) folds the partials into
+//                        out / m_star / vrows (or an unnormalised partial for a
+//                        cross-device combine).
 //
 // Replaces, with identical sampled row counts, the reference's
 //   fused_tiles_vec_gqa_gh4_d128_bn   (flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:96-380)
@@ -16,62 +21,64 @@
 // flush-to-zero ex2, which the sampled counts depend on.
 //
 // Work layout.  A "column" is one (batch, kv-head) pair; eight consecutive
-// columns form a column group handled by the eight warps of a CTA, so that the
-// eight 256-byte K rows of a token are fetched together.  Work items are
-// (column group, tile) pairs; CTA i owns a contiguous balanced range of them.
-// Each warp is autonomous: it owns a staging ring fed by its own bulk copies
-// and never synchronises with the other warps while streaming.
+// columns form a column group handled by the eight warps of a warp group, so
+// that the eight 256-byte K rows of a token are fetched together.  Work items
+// are (column group, tile) pairs; CTA i (one per SM) owns a contiguous balanced
+// range of them and splits it between its two warp groups.  Each warp is
+// autonomous: it owns a staging ring fed by its own TMA loads, a score buffer
+// and an exchange buffer, and never synchronises with any other warp.  All hot
+// loops are rolled so that the instruction footprint stays small.
+
+#include <cooperative_groups.h>
 
 #include "santa_abi_internal.h"
 #include "stream_scores.cuh"
 
 namespace santa {
 
-constexpr int kFlashStages = 3;
-constexpr int kEmitCap = 256;  // at most one entry per row of a tile
-constexpr size_t kFlashSmemBytes = size_t(kWarpsPerCta) * (kFlashStages * kStageBytes + kEmitCap * 8 + kEmitCap) +
-                                   size_t(kWarpsPerCta) * kFlashStages * 8;
+constexpr int kFlashStages = 2;
+constexpr int kMaxTileRows = 256;
+constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // per warp: scores, then u, then the emit list
+constexpr int kWarpSmem = kFlashStages * kStageBytes + kScoreBytes + kRedFloats * 4;
+constexpr int kCtaWarps = kGroupWarps * kGroupsPerCta;
+constexpr size_t kFlashSmemBytes = size_t(kCtaWarps) * kWarpSmem + size_t(kCtaWarps) * kFlashStages * 8;
 
 template <typename TK, int BN>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(const FlashParams p) {
-  constexpr int CPT = BN / kChunkRows;       // chunks per tile
+__global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const __grid_constant__ FlashParams p) {
   constexpr int NW = (BN == 256) ? 8 : 4;    // warps of the reference block (fixes the ell order)
   constexpr int NH = NW / 4;                 // 32-row halves per reference pass
-  constexpr int NJ = CPT / NH;               // reference passes over the tile
 
   extern __shared__ __align__(128) unsigned char smem[];
-  const int warp = threadIdx.x >> 5;
+  const int cta_warp = threadIdx.x >> 5;
+  const int warp = cta_warp & (kGroupWarps - 1);  // column within the column group
   const int lane = threadIdx.x & 31;
+  const int vgroup = blockIdx.x * kGroupsPerCta + (cta_warp / kGroupWarps);
 
-  unsigned char* ring_mem = smem + size_t(warp) * (kFlashStages * kStageBytes);
-  unsigned char* aux = smem + size_t(kWarpsPerCta) * (kFlashStages * kStageBytes);
-  uint2* em_cnt = reinterpret_cast<uint2*>(aux + size_t(warp) * kEmitCap * 8);
-  uint8_t* em_row = aux + size_t(kWarpsPerCta) * kEmitCap * 8 + size_t(warp) * kEmitCap;
-  uint64_t* bars =
-      reinterpret_cast<uint64_t*>(aux + size_t(kWarpsPerCta) * (kEmitCap * 8 + kEmitCap)) + warp * kFlashStages;
-  __shared__ int s_last;
+  unsigned char* wbase = smem + size_t(cta_warp) * kWarpSmem;
+  float* scorebuf = reinterpret_cast<float*>(wbase + kFlashStages * kStageBytes);
+  float* red = reinterpret_cast<float*>(wbase + kFlashStages * kStageBytes + kScoreBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kCtaWarps) * kWarpSmem) + cta_warp * kFlashStages;
 
   WarpRing<kFlashStages> ring;
-  ring.init(ring_mem, bars, lane);
+  ring.init(wbase, bars, lane);
   __syncthreads();
 
   const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
-  const unsigned char* __restrict__ Kg = static_cast<const unsigned char*>(p.K);
   const unsigned char* __restrict__ Vg = static_cast<const unsigned char*>(p.V);
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
 
-  const long long lo = range_lo(blockIdx.x, p.items, gridDim.x);
-  const long long hi = range_lo(blockIdx.x + 1, p.items, gridDim.x);
-  bool dead = false;  // set when a staged chunk never arrived
+  long long lo, hi;
+  group_range(vgroup, p.items, gridDim.x, &lo, &hi);
+  bool dead = false;  // set when a staged piece never arrived
 
   long long it = lo;
   while (it < hi) {
     const int cg = int(it / p.T_c);
     const int t_lo = int(it - (long long)cg * p.T_c);
     const int t_hi = (hi - it < (long long)(p.T_c - t_lo)) ? t_lo + int(hi - it) : p.T_c;
-    const int col = cg * kWarpsPerCta + warp;
+    const int col = cg * kGroupWarps + warp;
     const bool active = col < p.ncol;
-    const int slot = blockIdx.x + cg;
+    const int slot = vgroup + cg;  // distinct for every (warp group, column group) pair that occurs
 
     if (active) {
       const int b = col / p.KVH;
@@ -79,14 +86,14 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
       const int h0 = kv * kGH;
       QRegs Q;
       load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
-      const unsigned char* kcol = Kg + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
       const unsigned char* vcol = Vg + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
 
-      const int nchunks = (t_hi - t_lo) * CPT;
       const int row_base = t_lo * BN;
+      const int row_end = (t_hi * BN < p.L_valid) ? t_hi * BN : p.L_valid;
+      const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
       int issued = 0;
-      for (; issued < kFlashStages && issued < nchunks; ++issued)
-        ring.issue(ring.count + issued, kcol, row_stride, row_base + issued * kChunkRows, p.L_valid, lane);
+      for (; issued < kFlashStages && issued < npieces; ++issued)
+        ring.issue(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
 
       float M[kGH], Z[kGH], A[kGH][4];
 #pragma unroll
@@ -98,63 +105,101 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
       }
       int vrow_count = 0;
 
+#pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t) {
         const int n0 = t * BN;
         const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
 
-        // ---- stream the tile's chunks, scores stay in registers ----------
-        float sc[CPT][kGH];
-#pragma unroll
-        for (int ch = 0; ch < CPT; ++ch) {
+        // ---- stream the tile: scores of row r land in scorebuf[4r..4r+3] ----
+        const int npc = (tile_len + kStageRows - 1) / kStageRows;
+#pragma unroll 1
+        for (int pc = 0; pc < npc; ++pc) {
           if (!dead && !ring.wait(ring.count)) {
             dead = true;
             if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
           }
-          score_chunk<TK>(ring.stage_ptr(ring.count), Q, lane, sc[ch]);
-          __syncwarp();
-          if (issued < nchunks && !dead) {
-            ring.issue(ring.count + kFlashStages, kcol, row_stride, row_base + issued * kChunkRows, p.L_valid,
-                       lane);
+          const unsigned char* st = ring.stage_ptr(ring.count);
+          score_rows8<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+          score_rows8<TK>(st + 8 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 8) * kGH, lane);
+          if (issued < npieces && !dead) {
+            ring.issue(ring.count + kFlashStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
             ++issued;
           }
           ++ring.count;
         }
+        const float4* sb4 = reinterpret_cast<const float4*>(scorebuf);
+        float4* sb4w = reinterpret_cast<float4*>(scorebuf);
 
         // ---- tile statistics (reference :223-273) -------------------------
         float m[kGH], ell[kGH];
 #pragma unroll
-        for (int g = 0; g < kGH; ++g) {
-          float v = -CUDART_INF_F;
-#pragma unroll
-          for (int ch = 0; ch < CPT; ++ch) {
-            const bool valid = ch * kChunkRows + lane < tile_len;
-            sc[ch][g] = valid ? sc[ch][g] : -CUDART_INF_F;
-            v = fmaxf(v, sc[ch][g]);
+        for (int g = 0; g < kGH; ++g) m[g] = -CUDART_INF_F;
+#pragma unroll 1
+        for (int ch = 0; ch < nch; ++ch) {
+          if (ch * kChunkRows + lane < tile_len) {
+            const float4 s = sb4[ch * kChunkRows + lane];
+            m[0] = fmaxf(m[0], s.x);
+            m[1] = fmaxf(m[1], s.y);
+            m[2] = fmaxf(m[2], s.z);
+            m[3] = fmaxf(m[3], s.w);
           }
+        }
 #pragma unroll
-          for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
-          m[g] = v;
+        for (int g = 0; g < kGH; ++g)
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) m[g] = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], off));
+
+        // u = exp(s - m) replaces the scores in place; ell is summed in the
+        // reference's order: per-thread strided partials (chunk parity picks
+        // the half for block_n 256), an 8-row tree per reference warp, then
+        // the reference warps in order.
+        float V0[kGH], V1[kGH];
+#pragma unroll
+        for (int g = 0; g < kGH; ++g) V0[g] = V1[g] = 0.f;
+#pragma unroll 1
+        for (int ch = 0; ch < nch; ++ch) {
+          const bool valid = ch * kChunkRows + lane < tile_len;
+          float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (valid) {
+            const float4 s = sb4[ch * kChunkRows + lane];
+            u.x = __expf(s.x - m[0]);
+            u.y = __expf(s.y - m[1]);
+            u.z = __expf(s.z - m[2]);
+            u.w = __expf(s.w - m[3]);
+          }
+          sb4w[ch * kChunkRows + lane] = u;
+          if (NH == 2 && (ch & 1)) {
+            V1[0] = __fadd_rn(V1[0], u.x);
+            V1[1] = __fadd_rn(V1[1], u.y);
+            V1[2] = __fadd_rn(V1[2], u.z);
+            V1[3] = __fadd_rn(V1[3], u.w);
+          } else {
+            V0[0] = __fadd_rn(V0[0], u.x);
+            V0[1] = __fadd_rn(V0[1], u.y);
+            V0[2] = __fadd_rn(V0[2], u.z);
+            V0[3] = __fadd_rn(V0[3], u.w);
+          }
         }
 #pragma unroll
         for (int g = 0; g < kGH; ++g) {
-#pragma unroll
-          for (int ch = 0; ch < CPT; ++ch) sc[ch][g] = __expf(sc[ch][g] - m[g]);  // u, fp32; 0 on masked rows
-          // ell in the reference's order: per-thread strided partials, an
-          // 8-row tree per reference warp, reference warps summed in order.
-          float x[NH];
-#pragma unroll
-          for (int hf = 0; hf < NH; ++hf) {
-            float v = sc[hf][g];
-#pragma unroll
-            for (int jj = 1; jj < NJ; ++jj) v = __fadd_rn(v, sc[jj * NH + hf][g]);
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
-            x[hf] = v;
+          float x0 = V0[g], x1 = V1[g];
+          x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 4));
+          x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 2));
+          x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 1));
+          float e = __shfl_sync(0xffffffffu, x0, 0);
+          e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 8));
+          e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 16));
+          e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 24));
+          if (NH == 2) {
+            x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 4));
+            x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 2));
+            x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 1));
+            e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 0));
+            e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 8));
+            e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 16));
+            e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 24));
           }
-          float e = __shfl_sync(0xffffffffu, x[0], 0);
-#pragma unroll
-          for (int w = 1; w < NW; ++w) e = __fadd_rn(e, __shfl_sync(0xffffffffu, x[w / 4], 8 * (w & 3)));
           ell[g] = e;
         }
 
@@ -167,56 +212,60 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
           carry[g] = 0.f;
         }
         int n_emit = 0;
-#pragma unroll
-        for (int ch = 0; ch < CPT; ++ch) {
+        uint4* emit = reinterpret_cast<uint4*>(scorebuf);  // entry i overwrites row i, which is already consumed
+#pragma unroll 1
+        for (int ch = 0; ch < nch; ++ch) {
           const int remain = tile_len - ch * kChunkRows;
-          if (remain > 0) {  // warp-uniform
-            const int last_lane = remain > 32 ? 31 : remain - 1;
-            const bool valid = lane < remain;
-            int c[kGH];
+          const int last_lane = remain > 32 ? 31 : remain - 1;
+          const bool valid = lane < remain;
+          const float4 u4 = sb4[ch * kChunkRows + lane];
+          const float uu[kGH] = {u4.x, u4.y, u4.z, u4.w};
+          int c[kGH];
+#pragma unroll
+          for (int g = 0; g < kGH; ++g) {
+            const float u16v = Store16<TK>::round(uu[g]);
+            const float xv = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
+            float res = xv;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+              const float nb = __shfl_up_sync(0xffffffffu, res, off);
+              if (lane >= off) res = __fadd_rn(res, nb);
+            }
+            const float pre = __fsub_rn(res, xv);
+            const float pre_g = __fadd_rn(carry[g], pre);
+            const float cum_g = __fadd_rn(pre_g, xv);
+            const float f_prev = floorf(__fadd_rn(a0[g], pre_g));
+            const float f_curr = floorf(__fadd_rn(a0[g], cum_g));
+            int cc = (int)__fsub_rn(f_curr, f_prev);
+            cc = cc < 0 ? 0 : cc;
+            cc = cc > 32767 ? 32767 : cc;
+            c[g] = valid ? cc : 0;
+            const float chunk_total = __shfl_sync(0xffffffffu, __fadd_rn(pre, xv), last_lane);
+            carry[g] = __fadd_rn(carry[g], chunk_total);
+          }
+          if (p.dbg_u != nullptr && valid) {
 #pragma unroll
             for (int g = 0; g < kGH; ++g) {
-              const float u16v = Store16<TK>::round(sc[ch][g]);
-              const float xv = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
-              float res = xv;
-#pragma unroll
-              for (int off = 1; off < 32; off <<= 1) {
-                const float nb = __shfl_up_sync(0xffffffffu, res, off);
-                if (lane >= off) res = __fadd_rn(res, nb);
-              }
-              const float pre = __fsub_rn(res, xv);
-              const float pre_g = __fadd_rn(carry[g], pre);
-              const float cum_g = __fadd_rn(pre_g, xv);
-              const float f_prev = floorf(__fadd_rn(a0[g], pre_g));
-              const float f_curr = floorf(__fadd_rn(a0[g], cum_g));
-              int cc = (int)__fsub_rn(f_curr, f_prev);
-              cc = cc < 0 ? 0 : cc;
-              cc = cc > 32767 ? 32767 : cc;
-              c[g] = valid ? cc : 0;
-              const float chunk_total = __shfl_sync(0xffffffffu, __fadd_rn(pre, xv), last_lane);
-              carry[g] = __fadd_rn(carry[g], chunk_total);
-              if (p.dbg_u != nullptr && valid) {
-                const size_t o = (size_t(b) * p.H + h0 + g) * p.L_valid + n0 + ch * kChunkRows + lane;
-                p.dbg_u[o] = Store16<TK>::bits(sc[ch][g]);
-                p.dbg_c[o] = (int16_t)c[g];
-              }
+              const size_t o = (size_t(b) * p.H + h0 + g) * p.L_valid + n0 + ch * kChunkRows + lane;
+              p.dbg_u[o] = Store16<TK>::bits(uu[g]);
+              p.dbg_c[o] = (int16_t)c[g];
             }
-            // ---- compaction (reference :314-345): ascending row order -----
-            const bool flag = (c[0] + c[1] + c[2] + c[3]) > 0;
-            const uint32_t mask = __ballot_sync(0xffffffffu, flag);
-            if (flag) {
-              const int pos = n_emit + __popc(mask & ((1u << lane) - 1u));
-              em_row[pos] = (uint8_t)(ch * kChunkRows + lane);
-              em_cnt[pos] = make_uint2((uint32_t)c[0] | ((uint32_t)c[1] << 16), (uint32_t)c[2] | ((uint32_t)c[3] << 16));
-              if (p.rowmask != nullptr)
-                p.rowmask[(size_t(b) * p.KVH + kv) * p.L_valid + n0 + ch * kChunkRows + lane] = 1;
-            }
-            n_emit += __popc(mask);
           }
+          // ---- compaction (reference :314-345): ascending row order -------
+          const bool flag = (c[0] + c[1] + c[2] + c[3]) > 0;
+          const uint32_t mask = __ballot_sync(0xffffffffu, flag);
+          __syncwarp();
+          if (flag) {
+            const int pos = n_emit + __popc(mask & ((1u << lane) - 1u));
+            emit[pos] = make_uint4((uint32_t)c[0] | ((uint32_t)c[1] << 16), (uint32_t)c[2] | ((uint32_t)c[3] << 16),
+                                   (uint32_t)(ch * kChunkRows + lane), 0u);
+            if (p.rowmask != nullptr)
+              p.rowmask[(size_t(b) * p.KVH + kv) * p.L_valid + n0 + ch * kChunkRows + lane] = 1;
+          }
+          n_emit += __popc(mask);
         }
         vrow_count += n_emit;
         if (p.dbg_m != nullptr && lane < kGH) {
-          // select without dynamic register indexing
           float mv = m[0], ev = ell[0];
 #pragma unroll
           for (int g = 1; g < kGH; ++g) {
@@ -229,27 +278,29 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
         }
         __syncwarp();
 
-        // ---- sparse sum of c*V (reference :347-379), 8 rows in flight ----
+        // ---- sparse sum of c*V (reference :347-379), 4 rows in flight ----
         float o[kGH][4];
 #pragma unroll
         for (int g = 0; g < kGH; ++g)
 #pragma unroll
           for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
-        for (int i0 = 0; i0 < n_emit; i0 += 8) {
-          uint2 vv[8];
+#pragma unroll 1
+        for (int i0 = 0; i0 < n_emit; i0 += 4) {
+          uint4 en[4];
+          uint2 vv[4];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
+          for (int k = 0; k < 4; ++k) {
             if (i0 + k < n_emit) {
-              const int n = n0 + em_row[i0 + k];
-              vv[k] = __ldg(reinterpret_cast<const uint2*>(vcol + size_t(n) * row_stride) + lane);
+              en[k] = emit[i0 + k];
+              vv[k] = __ldg(reinterpret_cast<const uint2*>(vcol + size_t(n0 + (int)en[k].z) * row_stride) + lane);
             }
           }
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
+          for (int k = 0; k < 4; ++k) {
             if (i0 + k < n_emit) {
-              const uint2 cw = em_cnt[i0 + k];
               const float2 va = Store16<TK>::unpack(vv[k].x), vb = Store16<TK>::unpack(vv[k].y);
-              const int cg4[kGH] = {int(cw.x & 0xffffu), int(cw.x >> 16), int(cw.y & 0xffffu), int(cw.y >> 16)};
+              const int cg4[kGH] = {int(en[k].x & 0xffffu), int(en[k].x >> 16), int(en[k].y & 0xffffu),
+                                    int(en[k].y >> 16)};
 #pragma unroll
               for (int g = 0; g < kGH; ++g) {
                 if (cg4[g] != 0) {
@@ -279,7 +330,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
       }  // tiles
 
       // ---- publish this warp's partial -----------------------------------
-      float* ps = p.partials + (size_t(slot) * kWarpsPerCta + warp) * (kGH * kPartialStride);
+      float* ps = p.partials + (size_t(slot) * kGroupWarps + warp) * (kGH * kPartialStride);
 #pragma unroll
       for (int g = 0; g < kGH; ++g) {
         reinterpret_cast<float4*>(ps + g * kPartialStride)[lane] = make_float4(A[g][0], A[g][1], A[g][2], A[g][3]);
@@ -288,83 +339,142 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 1) flash_decode_kernel(cons
           ps[g * kPartialStride + kD + 1] = Z[g];
         }
       }
-      if (lane == 0) p.partial_vrows[slot * kWarpsPerCta + warp] = vrow_count;
+      if (lane == 0) p.partial_vrows[slot * kGroupWarps + warp] = vrow_count;
     }  // active
-
-    // ---- last CTA of the column group merges -------------------------------
-    __threadfence();
-    __syncthreads();
-    const int cta_first = cta_of_item((long long)cg * p.T_c, p.items, gridDim.x);
-    const int cta_last = cta_of_item((long long)(cg + 1) * p.T_c - 1, p.items, gridDim.x);
-    if (threadIdx.x == 0) {
-      const unsigned expected = unsigned(cta_last - cta_first + 1);
-      const unsigned old = atomicAdd(&p.tickets[cg], 1u);
-      s_last = (old == expected - 1u);
-      if (s_last) p.tickets[cg] = 0u;  // leave the workspace ready for the next call
-    }
-    __syncthreads();
-    if (s_last && active) {
-      __threadfence();
-      const int b = col / p.KVH;
-      const int kv = col - b * p.KVH;
-      int vr = 0;
-#pragma unroll
-      for (int g = 0; g < kGH; ++g) {
-        const int h = kv * kGH + g;
-        float ms = -CUDART_INF_F;
-        for (int c = cta_first; c <= cta_last; ++c) {
-          const float* ps = p.partials + ((size_t(c + cg) * kWarpsPerCta + warp) * kGH + g) * kPartialStride;
-          ms = fmaxf(ms, __ldcg(ps + kD));
-        }
-        float zs = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = cta_first; c <= cta_last; ++c) {
-          const float* ps = p.partials + ((size_t(c + cg) * kWarpsPerCta + warp) * kGH + g) * kPartialStride;
-          const float e = __expf(__ldcg(ps + kD) - ms);
-          const float4 a = __ldcg(reinterpret_cast<const float4*>(ps) + lane);
-          zs += e * __ldcg(ps + kD + 1);
-          acc.x += e * a.x;
-          acc.y += e * a.y;
-          acc.z += e * a.z;
-          acc.w += e * a.w;
-        }
-        const size_t bh = size_t(b) * p.H + h;
-        if (p.partial_out != nullptr) {
-          // raw merged partial for a cross-device combine: A[128], m, Z
-          float* po = p.partial_out + bh * (kD + 2);
-          po[4 * lane + 0] = acc.x;
-          po[4 * lane + 1] = acc.y;
-          po[4 * lane + 2] = acc.z;
-          po[4 * lane + 3] = acc.w;
-          if (lane == 0) {
-            po[kD] = ms;
-            po[kD + 1] = zs;
-          }
-        }
-        if (p.out != nullptr) {
-          const float inv = (p.S_per_tile > 0 && zs > 0.f) ? 1.0f / (zs * (float)p.S_per_tile) : 0.f;
-          TK* op = static_cast<TK*>(p.out) + bh * kD + 4 * lane;
-          uint2 w;
-          w.x = uint32_t(Store16<TK>::bits(acc.x * inv)) | (uint32_t(Store16<TK>::bits(acc.y * inv)) << 16);
-          w.y = uint32_t(Store16<TK>::bits(acc.z * inv)) | (uint32_t(Store16<TK>::bits(acc.w * inv)) << 16);
-          *reinterpret_cast<uint2*>(op) = w;
-        }
-        if (lane == 0 && p.m_star != nullptr) p.m_star[bh] = ms;
-      }
-      if (p.vrows != nullptr) {
-        for (int c = cta_first + lane; c <= cta_last; c += 32) vr += __ldcg(p.partial_vrows + (c + cg) * kWarpsPerCta + warp);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) vr += __shfl_xor_sync(0xffffffffu, vr, off);
-        if (lane == 0) p.vrows[b * p.KVH + kv] = vr;
-      }
-    }
-    __syncthreads();  // s_last is reused by the next segment
     it += (t_hi - t_lo);
   }
 }
 
+
+// Folds the partials of one (column, head) pair.  Launched as a programmatic
+// dependent of flash_decode_kernel: it may become resident early and waits for
+// the producer grid before touching its results.
+//   m* = max_v m_v;  w_v = exp(m_v - m*);  Z = sum_v w_v Z_v;  A = sum_v w_v A_v;
+//   out = A / (Z * S_per_tile)            (reference :436-468 over all tiles)
+template <typename TK>
+__global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams p) {
+  cudaGridDependencySynchronize();
+  __shared__ float s_w[2 * kMaxCtas + 8];
+  __shared__ float s_red[4];
+  __shared__ int s_redi[4];
+  __shared__ float4 s_acc[4][32];
+
+  const int col = blockIdx.x >> 2;
+  const int g = blockIdx.x & 3;
+  const int cg = col / kGroupWarps;
+  const int w = col - cg * kGroupWarps;
+  const int b = col / p.KVH;
+  const int kv = col - b * p.KVH;
+  const int tid = threadIdx.x, lane = tid & 31, wq = tid >> 5;
+
+  const int v_first = group_of_item((long long)cg * p.T_c, p.items, p.ctas);
+  const int v_last = group_of_item((long long)(cg + 1) * p.T_c - 1, p.items, p.ctas);
+  const int nv = v_last - v_first + 1;
+  auto partial = [&](int v) {
+    return p.partials + ((size_t(v + cg) * kGroupWarps + w) * kGH + g) * kPartialStride;
+  };
+
+  // phase 1: m* (groups with an empty range wrote nothing and are skipped)
+  float mloc = -CUDART_INF_F;
+  for (int i = tid; i < nv; i += 128) {
+    long long lo, hi;
+    group_range(v_first + i, p.items, p.ctas, &lo, &hi);
+    const bool has = hi > lo;
+    const float mv = has ? __ldcg(partial(v_first + i) + kD) : -CUDART_INF_F;
+    s_w[i] = has ? mv : CUDART_NAN_F;  // NaN marks "no partial"
+    mloc = fmaxf(mloc, mv);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
+  if (lane == 0) s_red[wq] = mloc;
+  __syncthreads();
+  const float ms = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+  __syncthreads();
+
+  // phase 2: weights, Z, gathered-row count
+  float zloc = 0.f;
+  int vloc = 0;
+  for (int i = tid; i < nv; i += 128) {
+    const float mv = s_w[i];
+    float e = 0.f;
+    if (mv == mv) {
+      e = __expf(mv - ms);
+      zloc += e * __ldcg(partial(v_first + i) + kD + 1);
+      if (g == 0 && p.vrows != nullptr) vloc += __ldcg(p.partial_vrows + (v_first + i + cg) * kGroupWarps + w);
+    }
+    s_w[i] = e;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    zloc += __shfl_xor_sync(0xffffffffu, zloc, off);
+    vloc += __shfl_xor_sync(0xffffffffu, vloc, off);
+  }
+  if (lane == 0) {
+    s_red[wq] = zloc;
+    s_redi[wq] = vloc;
+  }
+  __syncthreads();
+  const float zs = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
+
+  // phase 3: A, four partials in flight per warp
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i0 = wq; i0 < nv; i0 += 16) {
+    float e[4];
+    float4 a[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = i0 + 4 * k;
+      e[k] = (i < nv) ? s_w[i] : 0.f;
+      if (e[k] != 0.f) a[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (e[k] != 0.f) {
+        acc.x += e[k] * a[k].x;
+        acc.y += e[k] * a[k].y;
+        acc.z += e[k] * a[k].z;
+        acc.w += e[k] * a[k].w;
+      }
+    }
+  }
+  s_acc[wq][lane] = acc;
+  __syncthreads();
+  if (wq == 0) {
+    const float4 a1 = s_acc[1][lane], a2 = s_acc[2][lane], a3 = s_acc[3][lane];
+    acc.x = (acc.x + a1.x) + (a2.x + a3.x);
+    acc.y = (acc.y + a1.y) + (a2.y + a3.y);
+    acc.z = (acc.z + a1.z) + (a2.z + a3.z);
+    acc.w = (acc.w + a1.w) + (a2.w + a3.w);
+    const size_t bh = size_t(b) * p.H + kv * kGH + g;
+    if (p.partial_out != nullptr) {
+      // raw merged partial for a cross-device combine: A[128], m, Z
+      float* po = p.partial_out + bh * (kD + 2);
+      po[4 * lane + 0] = acc.x;
+      po[4 * lane + 1] = acc.y;
+      po[4 * lane + 2] = acc.z;
+      po[4 * lane + 3] = acc.w;
+      if (lane == 0) {
+        po[kD] = ms;
+        po[kD + 1] = zs;
+      }
+    }
+    if (p.out != nullptr) {
+      const float inv = (p.S_per_tile > 0 && zs > 0.f) ? 1.0f / (zs * (float)p.S_per_tile) : 0.f;
+      TK* op = static_cast<TK*>(p.out) + bh * kD + 4 * lane;
+      uint2 wv;
+      wv.x = uint32_t(Store16<TK>::bits(acc.x * inv)) | (uint32_t(Store16<TK>::bits(acc.y * inv)) << 16);
+      wv.y = uint32_t(Store16<TK>::bits(acc.z * inv)) | (uint32_t(Store16<TK>::bits(acc.w * inv)) << 16);
+      *reinterpret_cast<uint2*>(op) = wv;
+    }
+    if (lane == 0) {
+      if (p.m_star != nullptr) p.m_star[bh] = ms;
+      if (g == 0 && p.vrows != nullptr) p.vrows[b * p.KVH + kv] = (s_redi[0] + s_redi[1]) + (s_redi[2] + s_redi[3]);
+    }
+  }
+}
+
 template <typename TK, int BN>
-static cudaError_t launch_one(const FlashParams& p, int grid, cudaStream_t stream) {
+static cudaError_t launch_one(const FlashParams& p, const FlashMergeParams& mp, int grid, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -374,19 +484,33 @@ static cudaError_t launch_one(const FlashParams& p, int grid, cudaStream_t strea
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  flash_decode_kernel<TK, BN><<<grid, kWarpsPerCta * 32, kFlashSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  flash_decode_kernel<TK, BN><<<grid, kCtaWarps * 32, kFlashSmemBytes, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(p.ncol) * kGH);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, flash_merge_kernel<TK>, mp);
 }
 
-cudaError_t launch_flash(const FlashParams& p, int dtype, int block_n, int grid, cudaStream_t stream) {
+cudaError_t launch_flash(const FlashParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,
+                         cudaStream_t stream) {
   if (dtype == 0) {
-    if (block_n == 32) return launch_one<__nv_bfloat16, 32>(p, grid, stream);
-    if (block_n == 64) return launch_one<__nv_bfloat16, 64>(p, grid, stream);
-    return launch_one<__nv_bfloat16, 256>(p, grid, stream);
+    if (block_n == 32) return launch_one<__nv_bfloat16, 32>(p, mp, grid, stream);
+    if (block_n == 64) return launch_one<__nv_bfloat16, 64>(p, mp, grid, stream);
+    return launch_one<__nv_bfloat16, 256>(p, mp, grid, stream);
   }
-  if (block_n == 32) return launch_one<__half, 32>(p, grid, stream);
-  if (block_n == 64) return launch_one<__half, 64>(p, grid, stream);
-  return launch_one<__half, 256>(p, grid, stream);
+  if (block_n == 32) return launch_one<__half, 32>(p, mp, grid, stream);
+  if (block_n == 64) return launch_one<__half, 64>(p, mp, grid, stream);
+  return launch_one<__half, 256>(p, mp, grid, stream);
 }
 
 }  // namespace santa

@@ -2,6 +2,7 @@
 // to the kernel launchers of each translation unit.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -10,6 +11,7 @@
 namespace santa {
 
 struct FlashParams {
+  CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,16,1}
   const void* q;  // [B,H,128]
   const void* K;  // [B,L_storage,KVH,128]
   const void* V;
@@ -22,16 +24,10 @@ struct FlashParams {
   int batch_offset, tile_offset;
   int ncol;         // B*KVH columns
   long long items;  // column groups * T_c
-  // workspace
-  unsigned* tickets;   // [column groups], zero between calls
+  // workspace (written here, read by the merge kernel)
   int* status;         // one word
-  float* partials;     // [(grid + column groups)][8][4][kPartialStride]
-  int* partial_vrows;  // [(grid + column groups)][8]
-  // outputs
-  void* out;           // [B,H,128] storage dtype or nullptr
-  float* m_star;       // [B,H] or nullptr
-  int* vrows;          // [B,KVH] or nullptr
-  float* partial_out;  // [B,H,130] or nullptr
+  float* partials;     // [2*grid + column groups][8][4][kPartialStride]
+  int* partial_vrows;  // [2*grid + column groups][8]
   // trace
   float* dbg_m;
   float* dbg_ell;
@@ -40,6 +36,19 @@ struct FlashParams {
   int* rowmask;
 };
 
-cudaError_t launch_flash(const FlashParams& p, int dtype, int block_n, int grid, cudaStream_t stream);
+struct FlashMergeParams {
+  int H, KVH, T_c, S_per_tile;
+  long long items;
+  int ctas;  // grid of the decode kernel
+  const float* partials;
+  const int* partial_vrows;
+  void* out;           // [B,H,128] storage dtype or nullptr
+  float* m_star;       // [B,H] or nullptr
+  int* vrows;          // [B,KVH] or nullptr
+  float* partial_out;  // [B,H,130] or nullptr
+};
+
+cudaError_t launch_flash(const FlashParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,
+                         cudaStream_t stream);
 
 }  // namespace santa

@@ -1,6 +1,6 @@
 // stream_scores.cuh -- the K-streaming front end shared by the Flash kernel and
-// Prop's first pass: a warp stages 32-row chunks of one kv-head's K rows in
-// shared memory with bulk asynchronous copies and forms the four query heads'
+// Prop's first pass: a warp stages 16-row pieces of one kv-head's K rows in
+// shared memory with tiled TMA loads (cp.async.bulk.tensor) and forms the four query heads'
 // scores for every row in the reference's exact floating-point order.
 //
 // Score order being reproduced (flash_style_fused_santa_fixed_tile_budgets/
@@ -10,12 +10,13 @@
 // q = fp32(q16)*q_scale; the row's score is the shfl_down tree
 //   a_i=p_i+p_{i+16}, b_i=a_i+a_{i+8}, c_i=b_i+b_{i+4}, d_i=c_i+c_{i+2}, s=d_0+d_1.
 //
-// Mapping used here: 8 threads per row (4 rows per warp step).  Thread j of a
-// row group owns the reference lanes j, j+8, j+16, j+24, so the first two tree
-// levels are register adds and the last three are xor-shuffles inside the
-// 8-thread group (addition commutes, so the butterfly yields the same bits as
-// the one-sided tree).  The two partials of a register pair are computed by
-// one packed fma.rn.f32x2, which is IEEE-identical to two scalar fmas.
+// Mapping used here: 8 threads per row.  Thread j of a row group owns the
+// reference lanes j, j+8, j+16, j+24, so the first two tree levels are register
+// adds; the eight b_j of a row then go through a small shared-memory exchange
+// and one thread per (row, head) finishes the tree (7 adds) -- cheaper than
+// three shuffle levels per head.  The two partials of a register pair are
+// computed by one packed fma.rn.f32x2, which is IEEE-identical to two scalar
+// fmas; addition commutes, so operand order never changes a bit.
 //
 // Shared-memory banks: rows are 256 B apart, so the two row groups of a
 // half-warp would hit the same banks.  Odd row groups therefore visit the
@@ -27,6 +28,9 @@
 #include "common.cuh"
 
 namespace santa {
+
+constexpr int kRedStride = 36;                  // floats per row in the exchange buffer (bank-conflict free)
+constexpr int kRedFloats = 8 * kRedStride;      // 8 rows per exchange
 
 // Query registers of one thread: qp[g][h][i] = (q[g][slot 2h][i], q[g][slot 2h+1][i])
 // where slot s of this thread covers reference lane j + 8*(s ^ odd).
@@ -58,23 +62,23 @@ __device__ __forceinline__ void load_q(const TK* __restrict__ q_head0, float q_s
   }
 }
 
-// Scores of the 32 rows of one staged chunk: on return lane l holds the four
-// heads' scores of row l in s_out.  Rows that were not staged produce garbage
-// the caller masks.
+// Scores of 8 consecutive staged rows.  `rows` points at the first row in the
+// staging buffer, `red` at this warp's exchange buffer (kRedFloats floats) and
+// `score_out` at 32 floats laid out [row][head]; lane l writes element l.
+// Rows that were not staged produce garbage the caller masks.
 template <typename TK>
-__device__ __forceinline__ void score_chunk(const unsigned char* __restrict__ stage, const QRegs& Q,
-                                            int lane, float (&s_out)[kGH]) {
+__device__ __forceinline__ void score_rows8(const unsigned char* __restrict__ rows, const QRegs& Q,
+                                            float* __restrict__ red, float* __restrict__ score_out, int lane) {
   const int j = lane & 7;
   const int rr = lane >> 3;
   const int odd = rr & 1;
-  const unsigned char* pA = stage + (8 * rr) * kRowBytes + j * 8 + odd * 64;
-  const unsigned char* pB = stage + (8 * rr) * kRowBytes + j * 8 + (odd ^ 1) * 64;
 #pragma unroll
-  for (int ii = 0; ii < 8; ++ii) {
-    const uint2 w0 = *reinterpret_cast<const uint2*>(pA + ii * kRowBytes);
-    const uint2 w1 = *reinterpret_cast<const uint2*>(pB + ii * kRowBytes);
-    const uint2 w2 = *reinterpret_cast<const uint2*>(pA + ii * kRowBytes + 128);
-    const uint2 w3 = *reinterpret_cast<const uint2*>(pB + ii * kRowBytes + 128);
+  for (int half = 0; half < 2; ++half) {
+    const unsigned char* rp = rows + (4 * half + rr) * kRowBytes + j * 8;
+    const uint2 w0 = *reinterpret_cast<const uint2*>(rp + odd * 64);
+    const uint2 w1 = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64);
+    const uint2 w2 = *reinterpret_cast<const uint2*>(rp + odd * 64 + 128);
+    const uint2 w3 = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64 + 128);
     const float2 k0a = Store16<TK>::unpack(w0.x), k0b = Store16<TK>::unpack(w0.y);
     const float2 k1a = Store16<TK>::unpack(w1.x), k1b = Store16<TK>::unpack(w1.y);
     const float2 k2a = Store16<TK>::unpack(w2.x), k2b = Store16<TK>::unpack(w2.y);
@@ -88,6 +92,7 @@ __device__ __forceinline__ void score_chunk(const unsigned char* __restrict__ st
     kp[1][1] = make_float2(k2a.y, k3a.y);
     kp[1][2] = make_float2(k2b.x, k3b.x);
     kp[1][3] = make_float2(k2b.y, k3b.y);
+    float b[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
       float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
@@ -97,21 +102,30 @@ __device__ __forceinline__ void score_chunk(const unsigned char* __restrict__ st
         a23 = __ffma2_rn(Q.qp[g][1][i], kp[1][i], a23);
       }
       const float2 t = __fadd2_rn(a01, a23);  // (a_j, a_{j+8}) in either order
-      float b = __fadd_rn(t.x, t.y);
-      b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 4));
-      b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 2));
-      b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 1));
-      if (ii == j) s_out[g] = b;
+      b[g] = __fadd_rn(t.x, t.y);             // b_j
     }
+    *reinterpret_cast<float4*>(red + (4 * half + rr) * kRedStride + 4 * j) = make_float4(b[0], b[1], b[2], b[3]);
   }
+  __syncwarp();
+  {
+    const float* rd = red + (lane >> 2) * kRedStride + (lane & 3);
+    const float c0 = __fadd_rn(rd[0], rd[16]);
+    const float c1 = __fadd_rn(rd[4], rd[20]);
+    const float c2 = __fadd_rn(rd[8], rd[24]);
+    const float c3 = __fadd_rn(rd[12], rd[28]);
+    const float d0 = __fadd_rn(c0, c2);
+    const float d1 = __fadd_rn(c1, c3);
+    score_out[lane] = __fadd_rn(d0, d1);
+  }
+  __syncwarp();
 }
 
-// Per-warp staging ring: kStages chunks of 32 rows x 256 B, one mbarrier each.
+// Per-warp staging ring: kStages pieces of kStageRows rows x 256 B, one mbarrier each.
 template <int kStages>
 struct WarpRing {
   unsigned char* data;  // kStages * kStageBytes, 128-byte aligned
   uint32_t bar0;        // shared address of the first of kStages barriers
-  uint32_t count;       // chunks consumed so far by this warp (selects stage and parity)
+  uint32_t count;       // stages consumed so far by this warp (selects slot and parity)
 
   __device__ __forceinline__ void init(unsigned char* d, uint64_t* bars, int lane) {
     data = d;
@@ -123,21 +137,18 @@ struct WarpRing {
       mbar_fence_init();
     }
   }
-  // Stage rows [row0, row0+32) of a K column whose rows lie `row_stride` bytes
-  // apart into the stage that global chunk number `g` maps to.  Rows at or
-  // beyond `row_end` are not copied.
-  __device__ __forceinline__ void issue(uint32_t g, const unsigned char* col_base, size_t row_stride,
-                                        int row0, int row_end, int lane) {
-    const uint32_t st = g % kStages;
-    const int row = row0 + lane;
-    const bool v = row < row_end;
-    const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, v));
-    const uint32_t bar = bar0 + 8 * st;
-    if (lane == 0) mbar_arrive_expect_tx(bar, nvalid * kRowBytes);
-    __syncwarp();
-    if (v)
-      bulk_g2s(smem_u32(data + st * kStageBytes + lane * kRowBytes), col_base + size_t(row) * row_stride,
-               kRowBytes, bar);
+  // Stage rows [row0, row0+kStageRows) of K column (b, kv) into the slot that
+  // global stage number `g` maps to: one tiled TMA load of a {128, 1, 16, 1}
+  // box from the [B][L_storage][KVH][128] tensor `tmap` describes.  Rows past
+  // the end of the storage read as zeros; the caller masks rows past the valid
+  // length.
+  __device__ __forceinline__ void issue(uint32_t g, const void* tmap, int b, int kv, int row0, int lane) {
+    if (lane == 0) {
+      const uint32_t st = g % kStages;
+      const uint32_t bar = bar0 + 8 * st;
+      mbar_arrive_expect_tx(bar, kStageBytes);
+      tma_load_4d(smem_u32(data + st * kStageBytes), tmap, 0, kv, row0, b, bar);
+    }
   }
   __device__ __forceinline__ const unsigned char* stage_ptr(uint32_t g) const {
     return data + (g % kStages) * kStageBytes;
