@@ -93,7 +93,7 @@ int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
   pl->items = (long long)pl->ncg * pl->T_c;
   if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
   pl->grid = int(pl->items < (long long)sms ? pl->items : (long long)sms);  // one persistent CTA per SM
-  const size_t slots = size_t(santa::kGroupsPerCta) * pl->grid + size_t(pl->ncg);
+  const size_t slots = size_t(pl->grid) + size_t(pl->ncg);
   pl->off_pvrows = 256;
   pl->off_partials = pl->off_pvrows + align_up(slots * santa::kGroupWarps * 4, 256);
   pl->total = pl->off_partials +

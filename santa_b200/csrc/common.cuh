@@ -25,7 +25,6 @@ constexpr int kChunkRows = 32;      // rows per sampler chunk (one row per lane,
 constexpr int kStageRows = 16;      // rows staged per pipeline slot
 constexpr int kStageBytes = kStageRows * kRowBytes;
 constexpr int kGroupWarps = 8;      // one warp per kv-head column of a column group
-constexpr int kGroupsPerCta = 2;    // independent warp groups per CTA (one CTA per SM)
 constexpr int kMaxCtas = 256;       // upper bound on persistent CTAs (>= SM count)
 constexpr int kPartialStride = 132; // floats per (slot, warp, head): A[128], m, Z, pad
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -33,7 +32,8 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 // status word values (0 = ok)
 enum : int {
   kStatusOk = 0,
-  kStatusStageTimeout = 1,  // a staged K chunk never arrived
+  kStatusStageTimeout = 1,    // a staged K piece never arrived
+  kStatusHandoffTimeout = 2,  // a score buffer was never handed over between the warps of a column
 };
 
 // ---------------------------------------------------------------- RNG
@@ -149,20 +149,4 @@ __host__ __device__ __forceinline__ long long range_lo(long long i, long long it
 __host__ __device__ __forceinline__ int cta_of_item(long long x, long long items, long long ctas) {
   return int(((x + 1) * ctas - 1) / items);
 }
-// Each CTA runs two independent warp groups; group v = 2*cta + half owns the
-// first ceil(n/2) (half 0) or the remaining floor(n/2) (half 1) items of its
-// CTA's range.  A half-1 range is empty when the CTA owns a single item.
-__host__ __device__ __forceinline__ void group_range(int v, long long items, long long ctas, long long* lo,
-                                                     long long* hi) {
-  const long long a = range_lo(v >> 1, items, ctas), b = range_lo((v >> 1) + 1, items, ctas);
-  const long long mid = a + (b - a + 1) / 2;
-  *lo = (v & 1) ? mid : a;
-  *hi = (v & 1) ? b : mid;
-}
-__host__ __device__ __forceinline__ int group_of_item(long long x, long long items, long long ctas) {
-  const int i = cta_of_item(x, items, ctas);
-  const long long a = range_lo(i, items, ctas), b = range_lo(i + 1, items, ctas);
-  return 2 * i + (x >= a + (b - a + 1) / 2 ? 1 : 0);
-}
-
 }  // namespace santa

@@ -1,11 +1,12 @@
 // flash_kernels.cu -- S2ANTA-Flash decode attention (fixed per-tile sample
 // budget) for sm_100a.  Two launches on one stream, chained with programmatic
 // dependent launch:
-//   flash_decode_kernel  persistent; streams K once through TMA, samples rows by
-//                        systematic resampling inside every tile, gathers the
-//                        sampled V rows and folds tiles into a running
-//                        log-sum-exp state; every warp group writes one partial
-//                        (A[128], m, Z per head) per column group it touched;
+//   flash_decode_kernel  persistent, one CTA per SM; streams K once through TMA,
+//                        samples rows by systematic resampling inside every
+//                        tile, gathers the sampled V rows and folds tiles into
+//                        a running log-sum-exp state; every CTA writes one
+//                        partial (A[128], m, Z per head) per column group it
+//                        touched;
 //   flash_merge_kernel   one small CTA per (batch, head) folds the partials into
 //                        out / m_star / vrows (or an unnormalised partial for a
 //                        cross-device combine).
@@ -21,13 +22,19 @@
 // flush-to-zero ex2, which the sampled counts depend on.
 //
 // Work layout.  A "column" is one (batch, kv-head) pair; eight consecutive
-// columns form a column group handled by the eight warps of a warp group, so
-// that the eight 256-byte K rows of a token are fetched together.  Work items
-// are (column group, tile) pairs; CTA i (one per SM) owns a contiguous balanced
-// range of them and splits it between its two warp groups.  Each warp is
-// autonomous: it owns a staging ring fed by its own TMA loads, a score buffer
-// and an exchange buffer, and never synchronises with any other warp.  All hot
-// loops are rolled so that the instruction footprint stays small.
+// columns form a column group, so that the eight 256-byte K rows of a token are
+// fetched together.  Work items are (column group, tile) pairs; CTA i owns a
+// contiguous balanced range of them.  A CTA has sixteen warps, two per column:
+//   * the SCORE warp of a column owns a TMA staging ring, streams the column's
+//     K rows and writes the four heads' scores of a tile into one of two score
+//     buffers;
+//   * the SAMPLER warp of the column turns a finished score buffer into tile
+//     statistics, sampled counts, the sparse sum of V rows and the running
+//     log-sum-exp state.
+// The two warps hand buffers over through a full/empty pair of mbarriers per
+// buffer, so K keeps streaming while the previous tile is being sampled.  No
+// warp ever synchronises with another column.  All hot loops are rolled so that
+// the instruction footprint stays small; every wait is bounded.
 
 #include <cooperative_groups.h>
 
@@ -36,12 +43,17 @@
 
 namespace santa {
 
-constexpr int kFlashStages = 2;
+constexpr int kFlashStages = 4;
 constexpr int kMaxTileRows = 256;
-constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // per warp: scores, then u, then the emit list
-constexpr int kWarpSmem = kFlashStages * kStageBytes + kScoreBytes + kRedFloats * 4;
-constexpr int kCtaWarps = kGroupWarps * kGroupsPerCta;
-constexpr size_t kFlashSmemBytes = size_t(kCtaWarps) * kWarpSmem + size_t(kCtaWarps) * kFlashStages * 8;
+constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // one score buffer: scores, then u, then the emit list
+constexpr int kColSmem = kFlashStages * kStageBytes + 2 * kScoreBytes + kRedFloats * 4;
+constexpr int kColBars = kFlashStages + 4;           // ring + full[2] + empty[2]
+constexpr int kCtaWarps = 2 * kGroupWarps;
+constexpr size_t kFlashSmemBytes = size_t(kGroupWarps) * kColSmem + size_t(kGroupWarps) * kColBars * 8;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 
 template <typename TK, int BN>
 __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const __grid_constant__ FlashParams p) {
@@ -51,25 +63,37 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
   extern __shared__ __align__(128) unsigned char smem[];
   const int cta_warp = threadIdx.x >> 5;
   const int warp = cta_warp & (kGroupWarps - 1);  // column within the column group
+  const bool is_sampler = cta_warp >= kGroupWarps;
   const int lane = threadIdx.x & 31;
-  const int vgroup = blockIdx.x * kGroupsPerCta + (cta_warp / kGroupWarps);
 
-  unsigned char* wbase = smem + size_t(cta_warp) * kWarpSmem;
-  float* scorebuf = reinterpret_cast<float*>(wbase + kFlashStages * kStageBytes);
-  float* red = reinterpret_cast<float*>(wbase + kFlashStages * kStageBytes + kScoreBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kCtaWarps) * kWarpSmem) + cta_warp * kFlashStages;
+  unsigned char* cbase = smem + size_t(warp) * kColSmem;
+  float* scorebufs = reinterpret_cast<float*>(cbase + kFlashStages * kStageBytes);
+  float* red = reinterpret_cast<float*>(cbase + kFlashStages * kStageBytes + 2 * kScoreBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kGroupWarps) * kColSmem) + warp * kColBars;
+  const uint32_t bar_full = smem_u32(bars + kFlashStages);       // [2]
+  const uint32_t bar_empty = smem_u32(bars + kFlashStages + 2);  // [2]
 
   WarpRing<kFlashStages> ring;
-  ring.init(wbase, bars, lane);
+  if (!is_sampler) {
+    ring.init(cbase, bars, lane);
+    if (lane == 0) {
+      mbar_init(bar_full, 1);
+      mbar_init(bar_full + 8, 1);
+      mbar_init(bar_empty, 1);
+      mbar_init(bar_empty + 8, 1);
+      mbar_fence_init();
+    }
+  }
   __syncthreads();
 
   const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
   const unsigned char* __restrict__ Vg = static_cast<const unsigned char*>(p.V);
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
 
-  long long lo, hi;
-  group_range(vgroup, p.items, gridDim.x, &lo, &hi);
-  bool dead = false;  // set when a staged piece never arrived
+  const long long lo = range_lo(blockIdx.x, p.items, gridDim.x);
+  const long long hi = range_lo(blockIdx.x + 1, p.items, gridDim.x);
+  bool dead = false;     // set when a wait ran out; the status word then says why
+  uint32_t handoff = 0;  // tiles handed over so far on this column (selects buffer and parity)
 
   long long it = lo;
   while (it < hi) {
@@ -78,16 +102,15 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
     const int t_hi = (hi - it < (long long)(p.T_c - t_lo)) ? t_lo + int(hi - it) : p.T_c;
     const int col = cg * kGroupWarps + warp;
     const bool active = col < p.ncol;
-    const int slot = vgroup + cg;  // distinct for every (warp group, column group) pair that occurs
+    const int slot = blockIdx.x + cg;  // distinct for every (CTA, column group) pair that occurs
+    const int b = active ? col / p.KVH : 0;
+    const int kv = col - b * p.KVH;
+    const int h0 = kv * kGH;
 
-    if (active) {
-      const int b = col / p.KVH;
-      const int kv = col - b * p.KVH;
-      const int h0 = kv * kGH;
+    if (active && !is_sampler) {
+      // =========================== SCORE warp ===============================
       QRegs Q;
       load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
-      const unsigned char* vcol = Vg + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
-
       const int row_base = t_lo * BN;
       const int row_end = (t_hi * BN < p.L_valid) ? t_hi * BN : p.L_valid;
       const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
@@ -95,23 +118,17 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
       for (; issued < kFlashStages && issued < npieces; ++issued)
         ring.issue(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
 
-      float M[kGH], Z[kGH], A[kGH][4];
-#pragma unroll
-      for (int g = 0; g < kGH; ++g) {
-        M[g] = -CUDART_INF_F;
-        Z[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) A[g][i] = 0.f;
-      }
-      int vrow_count = 0;
-
 #pragma unroll 1
-      for (int t = t_lo; t < t_hi; ++t) {
+      for (int t = t_lo; t < t_hi; ++t, ++handoff) {
         const int n0 = t * BN;
         const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
-        const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
-
-        // ---- stream the tile: scores of row r land in scorebuf[4r..4r+3] ----
+        const uint32_t buf = handoff & 1u;
+        float* scorebuf = scorebufs + buf * (kScoreBytes / 4);
+        // wait until the sampler has released this buffer (passes at once the first two times)
+        if (!dead && !mbar_wait_bounded(bar_empty + 8 * buf, ((handoff >> 1) & 1u) ^ 1u)) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
+        }
         const int npc = (tile_len + kStageRows - 1) / kStageRows;
 #pragma unroll 1
         for (int pc = 0; pc < npc; ++pc) {
@@ -127,6 +144,33 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
             ++issued;
           }
           ++ring.count;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full + 8 * buf);
+      }
+    } else if (active) {
+      // ========================== SAMPLER warp ==============================
+      const unsigned char* vcol = Vg + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
+      float M[kGH], Z[kGH], A[kGH][4];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        M[g] = -CUDART_INF_F;
+        Z[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) A[g][i] = 0.f;
+      }
+      int vrow_count = 0;
+
+#pragma unroll 1
+      for (int t = t_lo; t < t_hi; ++t, ++handoff) {
+        const int n0 = t * BN;
+        const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+        const uint32_t buf = handoff & 1u;
+        float* scorebuf = scorebufs + buf * (kScoreBytes / 4);
+        if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u)) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
         const float4* sb4 = reinterpret_cast<const float4*>(scorebuf);
         float4* sb4w = reinterpret_cast<float4*>(scorebuf);
@@ -327,9 +371,10 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
           for (int i = 0; i < 4; ++i) A[g][i] = A[g][i] * so + st * o[g][i];
           M[g] = m_new;
         }
+        if (lane == 0) mbar_arrive(bar_empty + 8 * buf);  // the __syncwarp above ordered every lane's reads
       }  // tiles
 
-      // ---- publish this warp's partial -----------------------------------
+      // ---- publish this column's partial ---------------------------------
       float* ps = p.partials + (size_t(slot) * kGroupWarps + warp) * (kGH * kPartialStride);
 #pragma unroll
       for (int g = 0; g < kGH; ++g) {
@@ -340,11 +385,12 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
         }
       }
       if (lane == 0) p.partial_vrows[slot * kGroupWarps + warp] = vrow_count;
-    }  // active
+    } else {
+      handoff += uint32_t(t_hi - t_lo);
+    }
     it += (t_hi - t_lo);
   }
 }
-
 
 // Folds the partials of one (column, head) pair.  Launched as a programmatic
 // dependent of flash_decode_kernel: it may become resident early and waits for
@@ -354,7 +400,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) flash_decode_kernel(const _
 template <typename TK>
 __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams p) {
   cudaGridDependencySynchronize();
-  __shared__ float s_w[2 * kMaxCtas + 8];
+  __shared__ float s_w[kMaxCtas];
   __shared__ float s_red[4];
   __shared__ int s_redi[4];
   __shared__ float4 s_acc[4][32];
@@ -367,21 +413,18 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
   const int kv = col - b * p.KVH;
   const int tid = threadIdx.x, lane = tid & 31, wq = tid >> 5;
 
-  const int v_first = group_of_item((long long)cg * p.T_c, p.items, p.ctas);
-  const int v_last = group_of_item((long long)(cg + 1) * p.T_c - 1, p.items, p.ctas);
+  const int v_first = cta_of_item((long long)cg * p.T_c, p.items, p.ctas);
+  const int v_last = cta_of_item((long long)(cg + 1) * p.T_c - 1, p.items, p.ctas);
   const int nv = v_last - v_first + 1;
   auto partial = [&](int v) {
     return p.partials + ((size_t(v + cg) * kGroupWarps + w) * kGH + g) * kPartialStride;
   };
 
-  // phase 1: m* (groups with an empty range wrote nothing and are skipped)
+  // phase 1: m*
   float mloc = -CUDART_INF_F;
   for (int i = tid; i < nv; i += 128) {
-    long long lo, hi;
-    group_range(v_first + i, p.items, p.ctas, &lo, &hi);
-    const bool has = hi > lo;
-    const float mv = has ? __ldcg(partial(v_first + i) + kD) : -CUDART_INF_F;
-    s_w[i] = has ? mv : CUDART_NAN_F;  // NaN marks "no partial"
+    const float mv = __ldcg(partial(v_first + i) + kD);
+    s_w[i] = mv;
     mloc = fmaxf(mloc, mv);
   }
 #pragma unroll
@@ -395,13 +438,9 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
   float zloc = 0.f;
   int vloc = 0;
   for (int i = tid; i < nv; i += 128) {
-    const float mv = s_w[i];
-    float e = 0.f;
-    if (mv == mv) {
-      e = __expf(mv - ms);
-      zloc += e * __ldcg(partial(v_first + i) + kD + 1);
-      if (g == 0 && p.vrows != nullptr) vloc += __ldcg(p.partial_vrows + (v_first + i + cg) * kGroupWarps + w);
-    }
+    const float e = __expf(s_w[i] - ms);
+    zloc += e * __ldcg(partial(v_first + i) + kD + 1);
+    if (g == 0 && p.vrows != nullptr) vloc += __ldcg(p.partial_vrows + (v_first + i + cg) * kGroupWarps + w);
     s_w[i] = e;
   }
 #pragma unroll
@@ -425,16 +464,15 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
     for (int k = 0; k < 4; ++k) {
       const int i = i0 + 4 * k;
       e[k] = (i < nv) ? s_w[i] : 0.f;
-      if (e[k] != 0.f) a[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
+      a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < nv) a[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      if (e[k] != 0.f) {
-        acc.x += e[k] * a[k].x;
-        acc.y += e[k] * a[k].y;
-        acc.z += e[k] * a[k].z;
-        acc.w += e[k] * a[k].w;
-      }
+      acc.x += e[k] * a[k].x;
+      acc.y += e[k] * a[k].y;
+      acc.z += e[k] * a[k].z;
+      acc.w += e[k] * a[k].w;
     }
   }
   s_acc[wq][lane] = acc;

@@ -26,8 +26,8 @@ struct FlashParams {
   long long items;  // column groups * T_c
   // workspace (written here, read by the merge kernel)
   int* status;         // one word
-  float* partials;     // [2*grid + column groups][8][4][kPartialStride]
-  int* partial_vrows;  // [2*grid + column groups][8]
+  float* partials;     // [grid + column groups][8][4][kPartialStride]
+  int* partial_vrows;  // [grid + column groups][8]
   // trace
   float* dbg_m;
   float* dbg_ell;

@@ -1,0 +1,117 @@
+// torch_flash.cpp -- the `santa_flash_batch_cuda` Python module: a thin
+// pybind11/ATen shim over the C ABI of libsanta_b200.so.
+//
+// Same names, argument order, defaults, tensor layouts, return tuple and error
+// messages as the reference module of that name
+// (flash_style_fused_santa_fixed_tile_budgets/santa_cuda.cpp:123-360), so that
+// tutorial_code/attention_backends.py (SantaFlashBackend, :513-515) imports and
+// calls it unchanged.  ATen supplies tensors, the current stream and the
+// caching allocator; all arithmetic is in the CUDA library.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "santa_b200.h"
+
+namespace py = pybind11;
+
+namespace {
+
+struct ShapeInfo {
+  bool batched;
+  int B, H, D, L_storage, KVH;
+};
+
+ShapeInfo check_inputs(const at::Tensor& q_h, const at::Tensor& K_g, const at::Tensor& V_g) {
+  TORCH_CHECK(q_h.is_cuda(), "q_h must be CUDA");
+  TORCH_CHECK(K_g.is_cuda() && V_g.is_cuda(), "K_g and V_g must be CUDA");
+  TORCH_CHECK(q_h.scalar_type() == at::kBFloat16 || q_h.scalar_type() == at::kHalf, "q_h must be bf16 or f16");
+  TORCH_CHECK(K_g.scalar_type() == at::kBFloat16 || K_g.scalar_type() == at::kHalf, "K_g must be bf16 or f16");
+  TORCH_CHECK(K_g.scalar_type() == V_g.scalar_type(), "K_g and V_g must have the same dtype");
+  TORCH_CHECK(q_h.scalar_type() == K_g.scalar_type(), "q_h dtype must match K_g/V_g dtype");
+  TORCH_CHECK(q_h.device() == K_g.device() && q_h.device() == V_g.device(), "device mismatch");
+  TORCH_CHECK(K_g.is_contiguous() && V_g.is_contiguous(),
+              "K_g/V_g must be contiguous. Expected [L,KVH,D] for single or [B,L,KVH,D] for batch.");
+  ShapeInfo s{};
+  if (q_h.dim() == 2) {
+    TORCH_CHECK(K_g.dim() == 3 && V_g.dim() == 3, "Single-request path expects q_h [H,D], K_g/V_g [L,KVH,D]");
+    TORCH_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+    TORCH_CHECK(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))");
+    s = {false, 1, (int)q_h.size(0), (int)q_h.size(1), (int)K_g.size(0), (int)K_g.size(1)};
+    return s;
+  }
+  TORCH_CHECK(q_h.dim() == 3 && K_g.dim() == 4 && V_g.dim() == 4,
+              "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
+  TORCH_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+  TORCH_CHECK(q_h.size(0) == K_g.size(0), "Batch mismatch between q_h and K_g/V_g");
+  TORCH_CHECK(q_h.size(2) == K_g.size(3), "D mismatch (q_h.size(2) vs K_g.size(3))");
+  s = {true, (int)q_h.size(0), (int)q_h.size(1), (int)q_h.size(2), (int)K_g.size(1), (int)K_g.size(2)};
+  return s;
+}
+
+// One scratch tensor per (device, stream): calls on a stream are ordered, so
+// they can share it.  Grown on demand; the old tensor goes back to the caching
+// allocator, which keeps stream order.
+at::Tensor& workspace_for(const at::Tensor& like, cudaStream_t stream, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, at::Tensor> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  at::Tensor& ws = cache[{(int)like.get_device(), stream}];
+  if (!ws.defined() || (size_t)ws.numel() < bytes) {
+    const int64_t n = (int64_t)std::max<size_t>(bytes, size_t(4) << 20);
+    ws = at::zeros({n}, like.options().dtype(at::kByte));
+  }
+  return ws;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g,
+                                                                 int64_t S, uint64_t seed, int64_t block_n,
+                                                                 bool want_vrows, int64_t valid_len) {
+  const ShapeInfo info = check_inputs(q_h, K_g, V_g);
+  const c10::cuda::CUDAGuard guard(q_h.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_h.contiguous();
+
+  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
+  const int L = (valid_len > 0) ? (int)valid_len : L_storage;
+  TORCH_CHECK(L > 0, "valid_len must be > 0; got ", L);
+  TORCH_CHECK(L <= L_storage, "valid_len exceeds storage length: valid_len=", L, " storage=", L_storage);
+  TORCH_CHECK(D == 128, "This build supports only D=128. Got D=", D);
+  TORCH_CHECK(H % KVH == 0, "H must be divisible by KVH. Got H=", H, " KVH=", KVH);
+  TORCH_CHECK(H / KVH == 4, "This build supports only GH=4 (H/KVH). Got GH=", H / KVH, " (H=", H, " KVH=", KVH, ")");
+  const int bn = santa_block_n_rule(L, (int)block_n);
+  TORCH_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
+
+  auto optsF = q.options().dtype(at::kFloat);
+  auto optsI = q.options().dtype(at::kInt);
+  at::Tensor out = info.batched ? at::empty({B, H, D}, q.options()) : at::empty({H, D}, q.options());
+  at::Tensor m_star = info.batched ? at::empty({B, H}, optsF) : at::empty({H}, optsF);
+  at::Tensor vrows = at::empty({0}, optsI);
+  if (want_vrows) vrows = info.batched ? at::empty({B, KVH}, optsI) : at::empty({KVH}, optsI);
+
+  const size_t ws_bytes = santa_flash_workspace_bytes(B, KVH, L, bn);
+  TORCH_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+
+  const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
+                                    q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, B, H, KVH,
+                                    D, L, L_storage, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
+                                    want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(),
+                                    nullptr, (void*)stream.stream());
+  TORCH_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+  return std::make_tuple(out, m_star, vrows);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("decode_systematic_scalar", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),
+        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1);
+  m.def("decode_systematic_batched", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),
+        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1);
+}
