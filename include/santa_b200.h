@@ -90,6 +90,9 @@ typedef struct santa_flash_ext {
   uint16_t* u16;
   int16_t* counts;
   int32_t* rowmask;
+  /* [B,H,T_c] fp32 or NULL: the per-tile sampling step S_per_tile/ell_t as the device computed it
+   * (an approximate division, F.cu:279-280). */
+  float* invdel;
 } santa_flash_ext;
 
 /* Bytes of workspace santa_flash_decode needs on the current device for this problem. */
@@ -109,9 +112,9 @@ SANTA_API size_t santa_flash_workspace_bytes(int B, int KVH, int L_valid, int bl
  * Requires D == 128, H == 4*KVH, block_n in {0,32,64,256}, 16-byte aligned q/K/V/out.
  * S <= 0 is legal and yields zeros.
  *
- * workspace: santa_flash_workspace_bytes() bytes, 256-byte aligned.  It must be zero-filled once
- * before its first use; every successful call leaves it ready for the next.  Calls that share a
- * workspace must be ordered on one stream.  The first int32 after the call is a status word
+ * workspace: santa_flash_workspace_bytes() bytes, 256-byte aligned.  Zero-fill it once before its
+ * first use (only the status word has to start at 0).  Calls that share a workspace must be
+ * ordered on one stream.  The first int32 after the call is a status word
  * (santa_workspace_status()).
  */
 SANTA_API int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
@@ -119,9 +122,69 @@ SANTA_API int santa_flash_decode(const void* q, const void* K, const void* V, in
                        float* m_star, int32_t* vrows, void* workspace, size_t workspace_bytes,
                        const santa_flash_ext* ext, void* stream);
 
-/* Device address of the int32 status word inside a workspace (0 = ok, 1 = a staged K chunk never
- * arrived and the result is invalid).  Read it after synchronising the stream. */
+/* Device address of the int32 status word inside a workspace (0 = ok; 1 = a staged K piece never
+ * arrived, 2 = a score buffer was never handed over: the result is invalid).  Read it after synchronising the stream. */
 SANTA_API int32_t* santa_workspace_status(void* workspace);
+
+/* ---- Prop decode ----------------------------------------------------------- */
+
+typedef struct santa_prop_ext {
+  /* First-pass kernel choice, the reference's SANTA_PASS1 switch (P.cpp:39-51): 0 = auto (streaming
+   * vec kernel when block_n == 256, tensor-core kernel otherwise), 1 = force the tensor-core kernel,
+   * 2 = force the vec kernel (block_n <= 0 then means 256; any other block_n is an error). */
+  int pass1_mode;
+  /* Rounding choices of the budget step that the reference leaves to its compiler: bit0 = the 1e-7
+   * jitter is added with one fused multiply-add, bit1 = the per-thread partial sums of Z use a fused
+   * multiply-add.  The default (no ext) is 3. */
+  int flags;
+  /* Trace outputs, each may be NULL; when given they are used instead of workspace memory.
+   * m_tiles, ell_tiles: [H,T_c] fp32; u16: [H,L] storage-type bits of the rounded tile-local weights
+   * (the reference's u_stash, transposed); counts: [H,L] int16 sampled row counts; rowmask: [KVH,L]
+   * int32 set to 1 on gathered rows (caller zero-fills); S_tiles: [H,T_c] int32 per-tile budgets;
+   * invdelta, a0: [H,T_c] fp32 per-tile step and offset. */
+  float* m_tiles;
+  float* ell_tiles;
+  uint16_t* u16;
+  int16_t* counts;
+  int32_t* rowmask;
+  int32_t* S_tiles;
+  float* invdelta;
+  float* a0;
+} santa_prop_ext;
+
+/* Bytes of workspace santa_prop_decode needs on the current device for this problem. */
+SANTA_API size_t santa_prop_workspace_bytes(int H, int KVH, int D, int L, int block_n);
+
+/*
+ * S2ANTA-Prop decode attention for ONE sequence.  Replaces the launch sequence of
+ * decode_systematic_scalar, P.cpp:270-352 (launch_pass1_tiles_{vec,wmma}_gqa_{bf16,f16},
+ * launch_tile_budgets, launch_pass2_grouped_fused_atomic_{bf16,f16}, launch_cast_scale_out_{bf16,f16},
+ * launch_reduce_vrows; declared P.cpp:81-138).
+ *
+ *   q      [H,D]       storage dtype, contiguous
+ *   K, V   [L,KVH,D]   storage dtype, contiguous (every row is used)
+ *   out    [H,D]       storage dtype
+ *   m_star [H]         fp32
+ *   vrows  [KVH] int32 or NULL
+ * Requires D == 128, H == 4*KVH, block_n <= 0 (auto) or a multiple of 16 up to 256.
+ * The output is summed in a fixed order, so repeated calls give identical bits (the reference
+ * accumulates with atomics and does not).  Workspace rules as for santa_flash_decode.
+ */
+SANTA_API int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, int H, int KVH, int D, int L,
+                      int64_t S, uint64_t seed, int block_n, void* out, float* m_star, int32_t* vrows,
+                      void* workspace, size_t workspace_bytes, const santa_prop_ext* ext, void* stream);
+
+/* ---- split-KV combine ------------------------------------------------------- */
+
+/*
+ * Combine G unnormalised Flash partials (santa_flash_ext.partial_out of G calls over disjoint tile
+ * sets of the same sequences): partials is [G][BH][130] fp32 -- A[128], m, Z.  Writes
+ * out [BH,128] (storage dtype) = sum_r e^{m_r-m*} A_r / (S_per_tile * sum_r e^{m_r-m*} Z_r) and
+ * m_star [BH] (may be NULL).  This is the reference's finalize (F.cu:386-470) over the union of the
+ * tiles; the reference itself has no multi-device path.
+ */
+SANTA_API int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_tile, int dtype, void* out,
+                      float* m_star, void* stream);
 
 #ifdef __cplusplus
 }

@@ -84,31 +84,33 @@ EXT_MODULES = {
 
 
 def build_extensions(verbose: bool = False) -> None:
-    """Build the two pybind11/ATen modules into ``santa_b200/lib``."""
+    """Build the two pybind11/ATen modules into ``santa_b200/lib`` with one g++ call each."""
+    import sysconfig
+
+    import torch
     from torch.utils import cpp_extension
 
+    cxx = os.environ.get("CXX", "g++")
+    inc = [INCLUDE, sysconfig.get_paths()["include"]] + cpp_extension.include_paths("cuda")
+    libdirs = cpp_extension.library_paths("cuda")
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     for name, src in EXT_MODULES.items():
         path = os.path.join(CSRC, src)
         if not os.path.exists(path):
             continue
         sofile = os.path.join(LIBDIR, name + ".so")
-        if _newer(sofile, [path, LIB_PATH] + _headers()):
+        if _newer(sofile, [path, LIB_PATH, os.path.join(INCLUDE, "santa_b200.h")]):
             continue
-        build_dir = os.path.join(OBJDIR, name)
-        os.makedirs(build_dir, exist_ok=True)
-        cpp_extension.load(
-            name=name,
-            sources=[path],
-            extra_cflags=["-O2", "-std=c++17"],
-            extra_include_paths=[INCLUDE, os.path.join(cpp_extension.CUDA_HOME, "include")],
-            extra_ldflags=[f"-L{LIBDIR}", "-lsanta_b200", "-Wl,-rpath,$ORIGIN"],
-            build_directory=build_dir,
-            with_cuda=True,
-            is_python_module=False,
-            verbose=verbose,
-        )
-        built = os.path.join(build_dir, name + ".so")
-        os.replace(built, sofile)
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", path, "-o", sofile,
+               f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+               f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
+        cmd += [f"-I{d}" for d in inc]
+        cmd += [f"-L{d}" for d in libdirs] + [f"-L{LIBDIR}"]
+        cmd += ["-lsanta_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+                "-Wl,-rpath,$ORIGIN"] + [f"-Wl,-rpath,{d}" for d in libdirs if "torch" in d]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.check_call(cmd)
 
 
 def build_all(verbose: bool = False) -> None:

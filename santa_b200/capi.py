@@ -38,6 +38,7 @@ class FlashExt(C.Structure):
         ("u16", C.c_void_p),
         ("counts", C.c_void_p),
         ("rowmask", C.c_void_p),
+        ("invdel", C.c_void_p),
     ]
 
 

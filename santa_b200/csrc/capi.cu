@@ -73,9 +73,35 @@ int encode_k_map(CUtensorMap* tm, const void* K, int B, int L_storage, int KVH) 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Deal (column group, tile) items to the 8 column slots of each persistent CTA.
+// Narrower column groups give more, smaller items; the widest group whose
+// per-slot item count is minimal wins (wide groups fetch whole token rows).
+santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid) {
+  santa::WorkSplit best{};
+  long long best_per = -1;
+  for (int gw = santa::kGroupWarps; gw >= 1; gw >>= 1) {
+    const long long ncg = (ncol + gw - 1) / gw;
+    const long long items = ncg * T_c;
+    const long long slots = (long long)sms * (santa::kGroupWarps / gw);
+    const long long nvg = items < slots ? items : slots;
+    const long long per = (items + nvg - 1) / nvg;
+    if (best_per < 0 || per < best_per) {
+      best_per = per;
+      best.gw = gw;
+      best.nvg = int(nvg);
+      best.T_c = T_c;
+      best.ncol = ncol;
+      best.items = items;
+    }
+  }
+  const int spc = santa::kGroupWarps / best.gw;
+  *grid = (best.nvg + spc - 1) / spc;
+  return best;
+}
+
 struct FlashPlan {
-  int block_n, T_c, ncol, ncg, grid;
-  long long items;
+  int block_n, T_c, grid;
+  santa::WorkSplit ws;
   size_t off_pvrows, off_partials, total;
 };
 
@@ -86,18 +112,49 @@ int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
   if (bn != 32 && bn != 64 && bn != 256) return SANTA_E_BLOCK_N;
   int sms = 0;
   if (int rc = sm_count_of_current_device(&sms)) return rc;
+  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
   pl->block_n = bn;
   pl->T_c = (L_valid + bn - 1) / bn;
-  pl->ncol = B * KVH;
-  pl->ncg = (pl->ncol + santa::kGroupWarps - 1) / santa::kGroupWarps;
-  pl->items = (long long)pl->ncg * pl->T_c;
-  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
-  pl->grid = int(pl->items < (long long)sms ? pl->items : (long long)sms);  // one persistent CTA per SM
-  const size_t slots = size_t(pl->grid) + size_t(pl->ncg);
+  pl->ws = make_split(B * KVH, pl->T_c, sms, &pl->grid);
+  const size_t ncg = (size_t(B) * KVH + pl->ws.gw - 1) / pl->ws.gw;
+  const size_t slots = (size_t(pl->ws.nvg) + ncg) * pl->ws.gw;
   pl->off_pvrows = 256;
-  pl->off_partials = pl->off_pvrows + align_up(slots * santa::kGroupWarps * 4, 256);
-  pl->total = pl->off_partials +
-              slots * santa::kGroupWarps * santa::kGH * santa::kPartialStride * sizeof(float);
+  pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
+  pl->total = pl->off_partials + slots * santa::kGH * santa::kPartialStride * sizeof(float);
+  return SANTA_OK;
+}
+
+struct PropPlan {
+  int block_n, T_c, grid, use_vec;
+  santa::WorkSplit ws;
+  size_t off_m, off_ell, off_S, off_inv, off_a0, off_stash, off_pvrows, off_partials, total;
+};
+
+int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPlan* pl) {
+  if (KVH <= 0 || D != santa::kD || H != santa::kGH * KVH) return SANTA_E_SHAPE;
+  if (L <= 0) return SANTA_E_LENGTH;
+  int bn = block_n;
+  if (bn <= 0) bn = (pass1_mode == 2) ? 256 : santa_block_n_rule(L, 0);  // P.cpp:69-77
+  if (bn % 16 != 0 || bn > 256) return SANTA_E_BLOCK_N;
+  if (pass1_mode == 2 && bn != 256) return SANTA_E_BLOCK_N;
+  int sms = 0;
+  if (int rc = sm_count_of_current_device(&sms)) return rc;
+  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
+  pl->block_n = bn;
+  pl->T_c = (L + bn - 1) / bn;
+  pl->use_vec = (bn == 256 && pass1_mode != 1) ? 1 : 0;  // P.cpp:215-229
+  pl->ws = make_split(KVH, pl->T_c, sms, &pl->grid);
+  const size_t ht = align_up(size_t(H) * pl->T_c * 4, 256);
+  pl->off_m = 256;
+  pl->off_ell = pl->off_m + ht;
+  pl->off_S = pl->off_ell + ht;
+  pl->off_inv = pl->off_S + ht;
+  pl->off_a0 = pl->off_inv + ht;
+  pl->off_stash = pl->off_a0 + ht;
+  pl->off_pvrows = pl->off_stash + align_up(size_t(H) * L * 2, 256);
+  const size_t slots = size_t(santa::prop_pass2_max_groups(sms)) + KVH;
+  pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
+  pl->total = pl->off_partials + slots * santa::kGH * santa::kD * sizeof(float);
   return SANTA_OK;
 }
 
@@ -152,6 +209,13 @@ size_t santa_flash_workspace_bytes(int B, int KVH, int L_valid, int block_n) {
   return pl.total;
 }
 
+size_t santa_prop_workspace_bytes(int H, int KVH, int D, int L, int block_n) {
+  PropPlan pl;
+  // the vec-forcing mode can only enlarge block_n, never the workspace
+  if (plan_prop(H, KVH, D, L, block_n, 0, &pl) != SANTA_OK) return 0;
+  return pl.total;
+}
+
 int32_t* santa_workspace_status(void* workspace) { return static_cast<int32_t*>(workspace); }
 
 int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
@@ -178,29 +242,27 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   if (ext && ext->s_per_tile_override >= 0) spt = ext->s_per_tile_override;
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
-  santa::FlashParams p{};
+  santa::StreamParams p{};
   if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH)) return rc;
   p.q = q;
-  p.K = K;
   p.V = V;
-  p.B = B;
   p.H = H;
   p.KVH = KVH;
   p.L_valid = L_valid;
   p.L_storage = L_storage;
-  p.T_c = pl.T_c;
+  p.ws = pl.ws;
   p.S_per_tile = spt;
   p.q_scale = 1.0f / std::sqrt((float)D);  // F.cpp:210
   p.seed = seed;
   p.batch_offset = ext ? ext->batch_offset : 0;
   p.tile_offset = ext ? ext->tile_offset : 0;
-  p.ncol = pl.ncol;
-  p.items = pl.items;
   p.status = reinterpret_cast<int*>(ws);
   p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
   p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
-  p.dbg_m = ext ? ext->m_tiles : nullptr;
-  p.dbg_ell = ext ? ext->ell_tiles : nullptr;
+  p.m_tiles = ext ? ext->m_tiles : nullptr;
+  p.ell_tiles = ext ? ext->ell_tiles : nullptr;
+  p.stash = nullptr;
+  p.dbg_invdel = (ext && ext->m_tiles) ? ext->invdel : nullptr;
   p.dbg_u = ext ? ext->u16 : nullptr;
   p.dbg_c = ext ? ext->counts : nullptr;
   p.rowmask = ext ? ext->rowmask : nullptr;
@@ -208,10 +270,8 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   santa::FlashMergeParams mp{};
   mp.H = H;
   mp.KVH = KVH;
-  mp.T_c = pl.T_c;
   mp.S_per_tile = spt;
-  mp.items = pl.items;
-  mp.ctas = pl.grid;
+  mp.ws = pl.ws;
   mp.partials = p.partials;
   mp.partial_vrows = p.partial_vrows;
   mp.out = out;
@@ -220,6 +280,70 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   mp.partial_out = want_partial ? ext->partial_out : nullptr;
 
   cudaError_t e = santa::launch_flash(p, mp, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, int H, int KVH, int D, int L, int64_t S,
+                      uint64_t seed, int block_n, void* out, float* m_star, int32_t* vrows, void* workspace,
+                      size_t workspace_bytes, const santa_prop_ext* ext, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!q || !K || !V || !out || !m_star) return SANTA_E_ARG;
+  if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
+  const int mode = ext ? ext->pass1_mode : 0;
+  if (mode < 0 || mode > 2) return SANTA_E_ARG;
+  PropPlan pl;
+  if (int rc = plan_prop(H, KVH, D, L, block_n, mode, &pl)) return rc;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
+    return SANTA_E_WORKSPACE;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+
+  santa::PropParams p{};
+  santa::StreamParams& sp = p.sp;
+  if (pl.use_vec)
+    if (int rc = encode_k_map(&sp.tmK, K, 1, L, KVH)) return rc;
+  sp.q = q;
+  sp.V = V;
+  sp.H = H;
+  sp.KVH = KVH;
+  sp.L_valid = L;
+  sp.L_storage = L;
+  sp.ws = pl.ws;
+  sp.S_per_tile = 0;
+  sp.q_scale = 1.0f / std::sqrt((float)D);  // P.cpp:208
+  sp.seed = seed;
+  sp.status = reinterpret_cast<int*>(ws);
+  sp.m_tiles = (ext && ext->m_tiles) ? ext->m_tiles : reinterpret_cast<float*>(ws + pl.off_m);
+  sp.ell_tiles = (ext && ext->ell_tiles) ? ext->ell_tiles : reinterpret_cast<float*>(ws + pl.off_ell);
+  sp.stash = (ext && ext->u16) ? ext->u16 : reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  p.K = K;
+  p.block_n = pl.block_n;
+  p.T_c = pl.T_c;
+  p.use_vec = pl.use_vec;
+  p.S = S > 2147483647LL ? 2147483647 : (S < -2147483647LL ? -2147483647 : int(S));
+  p.flags = ext ? ext->flags : 3;
+  p.S_tiles = (ext && ext->S_tiles) ? ext->S_tiles : reinterpret_cast<int*>(ws + pl.off_S);
+  p.invdelta = (ext && ext->invdelta) ? ext->invdelta : reinterpret_cast<float*>(ws + pl.off_inv);
+  p.a0 = (ext && ext->a0) ? ext->a0 : reinterpret_cast<float*>(ws + pl.off_a0);
+  p.m_star = m_star;
+  p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
+  p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.out = out;
+  p.vrows = vrows;
+  p.dbg_c = ext ? ext->counts : nullptr;
+  p.rowmask = ext ? ext->rowmask : nullptr;
+  cudaError_t e = santa::launch_prop(p, dtype, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_tile, int dtype, void* out,
+                      float* m_star, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!partials || !out || G <= 0 || BH <= 0) return SANTA_E_ARG;
+  if (D != santa::kD) return SANTA_E_SHAPE;
+  cudaError_t e = santa::launch_lse_combine(partials, G, BH, S_per_tile, dtype, out, m_star,
+                                            static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   return SANTA_OK;
 }

@@ -1,0 +1,52 @@
+// combine_kernels.cu -- log-sum-exp combine of unnormalised Flash partials that
+// were produced for disjoint tile sets of the same sequences, e.g. by the ranks
+// of a sequence-sharded decode after an all-gather.  Partial r holds, per
+// (batch, head): A_r[128], m_r, Z_r with
+//   A_r = sum_t exp(m_t - m_r) ell_t o_t,   Z_r = sum_t exp(m_t - m_r) ell_t,
+// and the combined result is the reference's finalize over the union of tiles
+// (flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:386-470):
+//   m* = max_r m_r,  out = sum_r e^{m_r-m*} A_r / (S_per_tile * sum_r e^{m_r-m*} Z_r).
+#include "common.cuh"
+#include "santa_abi_internal.h"
+
+namespace santa {
+
+template <typename TK>
+__global__ void __launch_bounds__(32) lse_combine_kernel(const float* __restrict__ partials, int G, int BH,
+                                                         int S_per_tile, TK* __restrict__ out,
+                                                         float* __restrict__ m_star) {
+  const int bh = blockIdx.x, lane = threadIdx.x;
+  constexpr int W = kD + 2;
+  float ms = -CUDART_INF_F;
+  for (int r = 0; r < G; ++r) ms = fmaxf(ms, partials[(size_t(r) * BH + bh) * W + kD]);
+  float zs = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < G; ++r) {
+    const float* p = partials + (size_t(r) * BH + bh) * W;
+    const float e = __expf(p[kD] - ms);
+    zs += e * p[kD + 1];
+    acc.x += e * p[4 * lane + 0];
+    acc.y += e * p[4 * lane + 1];
+    acc.z += e * p[4 * lane + 2];
+    acc.w += e * p[4 * lane + 3];
+  }
+  const float inv = (S_per_tile > 0 && zs > 0.f) ? 1.0f / (zs * (float)S_per_tile) : 0.f;
+  TK* op = out + size_t(bh) * kD + 4 * lane;
+  uint2 wv;
+  wv.x = uint32_t(Store16<TK>::bits(acc.x * inv)) | (uint32_t(Store16<TK>::bits(acc.y * inv)) << 16);
+  wv.y = uint32_t(Store16<TK>::bits(acc.z * inv)) | (uint32_t(Store16<TK>::bits(acc.w * inv)) << 16);
+  *reinterpret_cast<uint2*>(op) = wv;
+  if (lane == 0 && m_star != nullptr) m_star[bh] = ms;
+}
+
+cudaError_t launch_lse_combine(const float* partials, int G, int BH, int S_per_tile, int dtype, void* out,
+                               float* m_star, cudaStream_t stream) {
+  if (dtype == 0)
+    lse_combine_kernel<__nv_bfloat16><<<BH, 32, 0, stream>>>(partials, G, BH, S_per_tile,
+                                                            static_cast<__nv_bfloat16*>(out), m_star);
+  else
+    lse_combine_kernel<__half><<<BH, 32, 0, stream>>>(partials, G, BH, S_per_tile, static_cast<__half*>(out), m_star);
+  return cudaGetLastError();
+}
+
+}  // namespace santa

@@ -1,0 +1,508 @@
+// prop_kernels.cu -- S2ANTA-Prop decode attention (per-head sample budget split
+// over tiles in proportion to their softmax mass) for sm_100a.  Four launches on
+// one stream, each a programmatic dependent of the one before:
+//   pass 1   tile statistics m_t, ell_t and the stash of rounded tile-local
+//            weights u = exp(s - m_t): the persistent TMA-streaming kernel of
+//            stream_kernel.cuh when block_n == 256, else a tensor-core kernel;
+//   budgets  one CTA per head: m*, Z, largest-remainder apportionment of S over
+//            the tiles, per-tile step S_t/ell_t and offset;
+//   pass 2   systematic counts from the stash, row compaction, sparse V sum, one
+//            partial per warp;
+//   merge    sums the partials in a fixed order, scales by 1/S, casts.
+//
+// Replaces the reference's santa_fused_proportional_tile_budgets/
+// santa_cuda_kernel.cu kernels: pass1_tiles_kernel_vec_gqa_gh4_d128_bn256
+// (:278-441), pass1_tiles_kernel_wmma_gqa_x (:87-267), tile_budgets_kernel
+// (:577-726), pass2_grouped_tile_fused_atomic_kernel_x (:734-864),
+// cast_scale_out_kernel (:976-985) and reduce_vrows_kernel (:869-899).
+//
+// Compiled WITHOUT --use_fast_math, like the reference's Prop extension (its
+// setup.py:39-42): divisions here are IEEE.
+//
+// Determinism.  The reference sums Z with shared-memory atomics and the output
+// with global atomics, so it is not run-to-run reproducible.  This file fixes
+// one order for each (per-thread partials added thread 0..127 for Z; tiles in
+// ascending order per warp and warps in ascending order for the output).
+
+#include <cooperative_groups.h>
+
+#include "stream_kernel.cuh"
+
+namespace santa {
+
+// ------------------------------------------------------------------ pass 1, tensor-core path
+template <typename TK>
+struct MmaOp;
+template <>
+struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+};
+template <>
+struct MmaOp<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+};
+
+// One CTA per (tile, kv-head), one warp per 16 K rows.  The scores are formed
+// exactly like the reference's 16x16x16 WMMA steps (q*scale rounded to the
+// storage type, fp32 accumulation over 16-wide k steps in ascending order); a
+// 16x16x16 WMMA step is two m16n8k16 MMAs on the two 8-column halves.  Tile
+// statistics follow santa_cuda_kernel.cu:190-265: per warp and head a
+// sequential 16-term sum of u, warps added in ascending order.
+template <typename TK>
+__global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __restrict__ K, int H, int KVH, int L,
+                                      int bn, int T_c, float q_scale, float* __restrict__ m_tiles,
+                                      float* __restrict__ ell_tiles, uint16_t* __restrict__ stash) {
+  extern __shared__ float smf[];
+  const int t = blockIdx.x, kv = blockIdx.y;
+  const int NWARP = blockDim.x >> 5;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = t * bn;
+  float* Ct = smf + w * 256;                 // [16 heads][16 rows of K]
+  float* rowMax = smf + NWARP * 256;         // [16][NWARP]
+  float* rowEll = rowMax + 16 * NWARP;       // [16][NWARP]
+  float* mRow = rowEll + 16 * NWARP;         // [16]
+
+  const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  for (int k0 = 0; k0 < kD; k0 += 16) {
+    uint32_t a[4] = {0u, 0u, 0u, 0u};
+    if (r0 < kGH) {  // rows r0+8 are padding (GH == 4)
+      const TK* qp = Q + (size_t(kv) * kGH + r0) * kD + k0 + c0;
+      const float2 lo = Store16<TK>::unpack(*reinterpret_cast<const uint32_t*>(qp));
+      const float2 hi = Store16<TK>::unpack(*reinterpret_cast<const uint32_t*>(qp + 8));
+      a[0] = uint32_t(Store16<TK>::bits(lo.x * q_scale)) | (uint32_t(Store16<TK>::bits(lo.y * q_scale)) << 16);
+      a[2] = uint32_t(Store16<TK>::bits(hi.x * q_scale)) | (uint32_t(Store16<TK>::bits(hi.y * q_scale)) << 16);
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const int n = n0 + 16 * w + 8 * nb + r0;
+      uint32_t b[2] = {0u, 0u};
+      if (n < L) {
+        const TK* kp = K + (size_t(n) * KVH + kv) * kD + k0 + c0;
+        b[0] = *reinterpret_cast<const uint32_t*>(kp);
+        b[1] = *reinterpret_cast<const uint32_t*>(kp + 8);
+      }
+      MmaOp<TK>::mma(acc[nb], a, b);
+    }
+  }
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb) {
+    Ct[r0 * 16 + 8 * nb + c0] = acc[nb][0];
+    Ct[r0 * 16 + 8 * nb + c0 + 1] = acc[nb][1];
+    Ct[(r0 + 8) * 16 + 8 * nb + c0] = acc[nb][2];
+    Ct[(r0 + 8) * 16 + 8 * nb + c0 + 1] = acc[nb][3];
+  }
+  __syncthreads();
+  if (lane < 16) {
+    float mp = -CUDART_INF_F;
+    if (lane < kGH)
+      for (int j = 0; j < 16; ++j)
+        if (n0 + 16 * w + j < L) mp = fmaxf(mp, Ct[lane * 16 + j]);
+    rowMax[lane * NWARP + w] = mp;
+  }
+  __syncthreads();
+  if (w == 0 && lane < 16) {
+    float mv = -CUDART_INF_F;
+    for (int ww = 0; ww < NWARP; ++ww) mv = fmaxf(mv, rowMax[lane * NWARP + ww]);
+    mRow[lane] = (lane < kGH) ? mv : -CUDART_INF_F;
+  }
+  __syncthreads();
+  if (lane < 16) {
+    float ep = 0.f;
+    if (lane < kGH) {
+      const float mr = mRow[lane];
+      const int h = kv * kGH + lane;
+      for (int j = 0; j < 16; ++j) {
+        const int n = n0 + 16 * w + j;
+        if (n < L) {
+          const float u = __expf(Ct[lane * 16 + j] - mr);
+          ep = __fadd_rn(ep, u);
+          stash[size_t(h) * L + n] = Store16<TK>::bits(u);
+        }
+      }
+    }
+    rowEll[lane * NWARP + w] = ep;
+  }
+  __syncthreads();
+  if (w == 0 && lane < kGH) {
+    float e = 0.f;
+    for (int ww = 0; ww < NWARP; ++ww) e = __fadd_rn(e, rowEll[lane * NWARP + ww]);
+    const int h = kv * kGH + lane;
+    m_tiles[size_t(h) * T_c + t] = mRow[lane];
+    ell_tiles[size_t(h) * T_c + t] = e;
+  }
+}
+
+// ------------------------------------------------------------------ budgets
+// One CTA of 128 threads per head; restates tile_budgets_kernel
+// (santa_cuda_kernel.cu:577-726) step by step: m* = max_t m_t,
+// W_t = __expf(m_t - m*) * ell_t, Z, q_t = S * (W_t / Z), floor, fractional part
+// plus 1e-7*u01 jitter, the bitonic network (descending, virtual -inf padding
+// that is never stored), +1 for the first S - sum(floor) entries,
+// invdelta_t = S_t / ell_t, a0_t = u01(seed, h, t).
+// flags bit0: jitter added with one fma; bit1: thread partials of Z with fma.
+__global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restrict__ m_tiles,
+                                                           const float* __restrict__ ell_tiles, int T_c, int S,
+                                                           uint64_t seed, int flags, float* __restrict__ m_star,
+                                                           int* __restrict__ S_tiles, float* __restrict__ invdelta,
+                                                           float* __restrict__ a0_tile) {
+  cudaGridDependencySynchronize();
+  extern __shared__ unsigned char smraw[];
+  float* frac = reinterpret_cast<float*>(smraw);
+  int* idx = reinterpret_cast<int*>(frac + T_c);
+  __shared__ float s_part[128];
+  __shared__ float s_bcast;
+  __shared__ int s_ipart[128];
+  const int h = blockIdx.x, tid = threadIdx.x;
+  const float* mt = m_tiles + size_t(h) * T_c;
+  const float* el = ell_tiles + size_t(h) * T_c;
+
+  float lm = -3.402823466e+38f;
+  for (int t = tid; t < T_c; t += 128) {
+    const float v = mt[t];
+    frac[t] = v;
+    lm = fmaxf(lm, v);
+  }
+  s_part[tid] = lm;
+  __syncthreads();
+  if (tid == 0) {
+    float v = s_part[0];
+    for (int i = 1; i < 128; ++i) v = fmaxf(v, s_part[i]);
+    s_bcast = v;
+  }
+  __syncthreads();
+  const float mstar = s_bcast;
+  if (tid == 0 && m_star != nullptr) m_star[h] = mstar;
+
+  float zl = 0.f;
+  for (int t = tid; t < T_c; t += 128) {
+    const float e = __expf(frac[t] - mstar);
+    const float W = __fmul_rn(e, el[t]);
+    frac[t] = W;
+    zl = (flags & 2) ? __fmaf_rn(e, el[t], zl) : __fadd_rn(zl, W);
+  }
+  __syncthreads();
+  s_part[tid] = zl;
+  __syncthreads();
+  if (tid == 0) {
+    float z = 0.f;
+    for (int i = 0; i < 128; ++i) z = __fadd_rn(z, s_part[i]);
+    s_bcast = z;
+  }
+  __syncthreads();
+  const float Z = s_bcast;
+
+  if (S <= 0 || !(Z > 0.0f)) {
+    for (int t = tid; t < T_c; t += 128) {
+      S_tiles[size_t(h) * T_c + t] = 0;
+      invdelta[size_t(h) * T_c + t] = 0.0f;
+      a0_tile[size_t(h) * T_c + t] = u01_from_seed(seed, h, t);
+    }
+    return;
+  }
+
+  int bl = 0;
+  for (int t = tid; t < T_c; t += 128) {
+    const float q = __fmul_rn((float)S, __fdiv_rn(frac[t], Z));
+    const int b = (int)floorf(q);
+    S_tiles[size_t(h) * T_c + t] = b;
+    bl += b;
+    const float ft = __fsub_rn(q, (float)b);
+    const float u = u01_from_seed(seed, h, t);
+    frac[t] = (flags & 1) ? __fmaf_rn(1.0e-7f, u, ft) : __fadd_rn(ft, __fmul_rn(1.0e-7f, u));
+    idx[t] = t;
+  }
+  s_ipart[tid] = bl;
+  __syncthreads();
+  int sum_base = 0;
+  for (int i = 0; i < 128; ++i) sum_base += s_ipart[i];
+  int rem = S - sum_base;
+  rem = rem < 0 ? 0 : rem;
+  rem = rem > T_c ? T_c : rem;
+
+  int N = 1;
+  while (N < T_c) N <<= 1;
+  for (int k = 2; k <= N; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < N; i += 128) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const bool up = (i & k) != 0;
+          float ai = (i < T_c) ? frac[i] : -CUDART_INF_F;
+          float aj = (ixj < T_c) ? frac[ixj] : -CUDART_INF_F;
+          int ii = (i < T_c) ? idx[i] : -1;
+          int ij = (ixj < T_c) ? idx[ixj] : -1;
+          if ((ai > aj) == up) {
+            const float tf = ai; ai = aj; aj = tf;
+            const int ti = ii; ii = ij; ij = ti;
+          }
+          if (i < T_c) { frac[i] = ai; idx[i] = ii; }
+          if (ixj < T_c) { frac[ixj] = aj; idx[ixj] = ij; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int r = tid; r < rem; r += 128) {
+    const int best = idx[r];
+    if (best >= 0) S_tiles[size_t(h) * T_c + best] += 1;
+  }
+  __syncthreads();
+  for (int t = tid; t < T_c; t += 128) {
+    const float ell = el[t];
+    const int St = S_tiles[size_t(h) * T_c + t];
+    invdelta[size_t(h) * T_c + t] = (St > 0 && ell > 1e-20f) ? __fdiv_rn((float)St, ell) : 0.0f;
+    a0_tile[size_t(h) * T_c + t] = u01_from_seed(seed, h, t);
+  }
+}
+
+// ------------------------------------------------------------------ pass 2
+struct Pass2Params {
+  const void* V;            // [L,KVH,128]
+  const uint16_t* stash;    // [H][L]
+  const float* invdelta;    // [H,T_c]
+  const float* a0;          // [H,T_c]
+  int H, KVH, L, bn, T_c;
+  WorkSplit ws;             // gw == 1: one column (kv-head) per warp
+  float* partials;          // [nvg + KVH][4][128]
+  int* partial_vrows;       // [nvg + KVH]
+  int16_t* dbg_c;           // [H,L] or null
+  int* rowmask;             // [KVH,L] or null
+};
+
+constexpr int kPass2Warps = 8;
+
+// One warp per (kv-head, tile range): counts from the stash, compaction,
+// sparse V sum (santa_cuda_kernel.cu:771-863), tiles in ascending order.
+template <typename TK>
+__global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass2Params p) {
+  cudaGridDependencySynchronize();
+  __shared__ __align__(16) float4 s_buf[kPass2Warps][kMaxTileRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int vg = blockIdx.x * kPass2Warps + warp;
+  if (vg >= p.ws.nvg) return;
+  const long long lo = range_lo(vg, p.ws.items, p.ws.nvg), hi = range_lo(vg + 1, p.ws.items, p.ws.nvg);
+  float4* sb = s_buf[warp];
+  const size_t row_stride = size_t(p.KVH) * kRowBytes;
+
+  long long it = lo;
+  while (it < hi) {
+    const int kv = int(it / p.T_c);
+    const int t_lo = int(it - (long long)kv * p.T_c);
+    const int t_hi = (hi - it < (long long)(p.T_c - t_lo)) ? t_lo + int(hi - it) : p.T_c;
+    const int h0 = kv * kGH;
+    const unsigned char* vcol = static_cast<const unsigned char*>(p.V) + size_t(kv) * kRowBytes;
+    float acc[kGH][4];
+#pragma unroll
+    for (int g = 0; g < kGH; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[g][i] = 0.f;
+    int vrow_count = 0;
+
+#pragma unroll 1
+    for (int t = t_lo; t < t_hi; ++t) {
+      const int n0 = t * p.bn;
+      const int tile_len = (p.L - n0 < p.bn) ? (p.L - n0) : p.bn;
+      const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+#pragma unroll 1
+      for (int ch = 0; ch < nch; ++ch) {
+        const int r = ch * kChunkRows + lane;
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < tile_len) {
+          const uint16_t* sp = p.stash + size_t(h0) * p.L + n0 + r;
+          const uint32_t w01 = uint32_t(__ldcg(sp)) | (uint32_t(__ldcg(sp + p.L)) << 16);
+          const uint32_t w23 = uint32_t(__ldcg(sp + 2 * size_t(p.L))) | (uint32_t(__ldcg(sp + 3 * size_t(p.L))) << 16);
+          const float2 f01 = Store16<TK>::unpack(w01), f23 = Store16<TK>::unpack(w23);
+          u = make_float4(f01.x, f01.y, f23.x, f23.y);
+        }
+        sb[r] = u;
+      }
+      __syncwarp();
+      float invdel[kGH], a0[kGH];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        invdel[g] = __ldcg(p.invdelta + size_t(h0 + g) * p.T_c + t);
+        a0[g] = __ldcg(p.a0 + size_t(h0 + g) * p.T_c + t);
+      }
+      RowTrace tr;
+      tr.head_stride = size_t(p.L);
+      tr.u16 = nullptr;
+      tr.counts = p.dbg_c ? p.dbg_c + size_t(h0) * p.L + n0 : nullptr;
+      tr.rowmask = p.rowmask ? p.rowmask + size_t(kv) * p.L + n0 : nullptr;
+      const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
+      vrow_count += n_emit;
+      float o[kGH][4];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
+      gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o);
+      if (n_emit > 0) {
+#pragma unroll
+        for (int g = 0; g < kGH; ++g)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[g][i] = __fadd_rn(acc[g][i], o[g][i]);
+      }
+    }
+    const size_t pslot = size_t(vg) + kv;
+    float* ps = p.partials + pslot * (kGH * kD);
+#pragma unroll
+    for (int g = 0; g < kGH; ++g)
+      reinterpret_cast<float4*>(ps + g * kD)[lane] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    if (lane == 0) p.partial_vrows[pslot] = vrow_count;
+    it += (t_hi - t_lo);
+  }
+}
+
+// ------------------------------------------------------------------ merge
+struct PropMergeParams {
+  const float* partials;
+  const int* partial_vrows;
+  int KVH, T_c;
+  WorkSplit ws;
+  float scale;   // 1/S, or 0 when S <= 0 (santa_cuda.cpp:333)
+  void* out;     // [H,128]
+  int* vrows;    // [KVH] or null
+};
+
+// One warp per (kv-head, head): adds the warps' partial sums in ascending order.
+template <typename TK>
+__global__ void __launch_bounds__(32) prop_merge_kernel(const PropMergeParams p) {
+  cudaGridDependencySynchronize();
+  const int kv = blockIdx.x >> 2, g = blockIdx.x & 3, lane = threadIdx.x;
+  const int v_first = cta_of_item((long long)kv * p.T_c, p.ws.items, p.ws.nvg);
+  const int v_last = cta_of_item((long long)(kv + 1) * p.T_c - 1, p.ws.items, p.ws.nvg);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int vr = 0;
+  for (int v0 = v_first; v0 <= v_last; v0 += 4) {
+    float4 a[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (v0 + k <= v_last)
+        a[k] = __ldcg(reinterpret_cast<const float4*>(p.partials + (size_t(v0 + k + kv) * kGH + g) * kD) + lane);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc.x += a[k].x;
+      acc.y += a[k].y;
+      acc.z += a[k].z;
+      acc.w += a[k].w;
+    }
+  }
+  TK* op = static_cast<TK*>(p.out) + (size_t(kv) * kGH + g) * kD + 4 * lane;
+  uint2 wv;
+  wv.x = uint32_t(Store16<TK>::bits(acc.x * p.scale)) | (uint32_t(Store16<TK>::bits(acc.y * p.scale)) << 16);
+  wv.y = uint32_t(Store16<TK>::bits(acc.z * p.scale)) | (uint32_t(Store16<TK>::bits(acc.w * p.scale)) << 16);
+  *reinterpret_cast<uint2*>(op) = wv;
+  if (g == 0 && p.vrows != nullptr) {
+    for (int v = v_first + lane; v <= v_last; v += 32) vr += __ldcg(p.partial_vrows + v + kv);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) vr += __shfl_xor_sync(0xffffffffu, vr, off);
+    if (lane == 0) p.vrows[kv] = vr;
+  }
+}
+
+// ------------------------------------------------------------------ launch
+template <typename KernelT, typename... Args>
+static cudaError_t launch_dependent(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <typename TK>
+static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t e;
+  const int H = p.sp.H, KVH = p.sp.KVH, L = p.sp.L_valid;
+  if (p.use_vec) {
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)kStreamSmemBytes);
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
+    stream_kernel<TK, 256, kModePropPass1><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
+  } else {
+    const int nwarp = p.block_n / 16;
+    const size_t smem = size_t(nwarp * 256 + 2 * 16 * nwarp + 16) * sizeof(float);
+    prop_pass1_mma_kernel<TK><<<dim3(p.T_c, KVH), nwarp * 32, smem, stream>>>(
+        static_cast<const TK*>(p.sp.q), static_cast<const TK*>(p.K), H, KVH, L, p.block_n, p.T_c, p.sp.q_scale,
+        p.sp.m_tiles, p.sp.ell_tiles, p.sp.stash);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
+  e = launch_dependent(prop_budgets_kernel, dim3(H), dim3(128), size_t(p.T_c) * 8, stream,
+                       (const float*)p.sp.m_tiles, (const float*)p.sp.ell_tiles, p.T_c, p.S, p.sp.seed, p.flags,
+                       p.m_star, p.S_tiles, p.invdelta, p.a0);
+  if (e != cudaSuccess) return e;
+
+  Pass2Params p2{};
+  p2.V = p.sp.V;
+  p2.stash = p.sp.stash;
+  p2.invdelta = p.invdelta;
+  p2.a0 = p.a0;
+  p2.H = H;
+  p2.KVH = KVH;
+  p2.L = L;
+  p2.bn = p.block_n;
+  p2.T_c = p.T_c;
+  p2.ws.gw = 1;
+  p2.ws.T_c = p.T_c;
+  p2.ws.ncol = KVH;
+  p2.ws.items = (long long)KVH * p.T_c;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long max_warps = (long long)sms * 4 * kPass2Warps;
+  p2.ws.nvg = int(p2.ws.items < max_warps ? p2.ws.items : max_warps);
+  p2.partials = p.partials;
+  p2.partial_vrows = p.partial_vrows;
+  p2.dbg_c = p.dbg_c;
+  p2.rowmask = p.rowmask;
+  const int grid2 = (p2.ws.nvg + kPass2Warps - 1) / kPass2Warps;
+  e = launch_dependent(prop_pass2_kernel<TK>, dim3(grid2), dim3(kPass2Warps * 32), 0, stream, p2);
+  if (e != cudaSuccess) return e;
+
+  PropMergeParams pm{};
+  pm.partials = p.partials;
+  pm.partial_vrows = p.partial_vrows;
+  pm.KVH = KVH;
+  pm.T_c = p.T_c;
+  pm.ws = p2.ws;
+  pm.scale = (p.S > 0) ? (1.0f / (float)p.S) : 0.0f;
+  pm.out = p.out;
+  pm.vrows = p.vrows;
+  return launch_dependent(prop_merge_kernel<TK>, dim3(KVH * kGH), dim3(32), 0, stream, pm);
+}
+
+cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t stream) {
+  return dtype == 0 ? launch_prop_t<__nv_bfloat16>(p, grid, stream) : launch_prop_t<__half>(p, grid, stream);
+}
+
+// Upper bound on pass-2 warps for workspace sizing (must match launch_prop_t).
+int prop_pass2_max_groups(int sms) { return sms * 4 * kPass2Warps; }
+
+}  // namespace santa

@@ -1,0 +1,235 @@
+// sampler.cuh -- per-tile sampling steps executed by one warp on a tile whose
+// four heads' scores (or tile-local weights) sit in shared memory as one float4
+// per row: tile statistics, systematic counts with row compaction, and the
+// sparse sum of V rows.  Shared by the Flash kernel, Prop's first pass (tile
+// statistics) and Prop's second pass (counts and V).  Every step follows the
+// reference's floating-point order so that the sampled counts are identical.
+#pragma once
+
+#include "common.cuh"
+#include "santa_abi_internal.h"
+
+namespace santa {
+
+// Tile statistics, flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:223-273
+// (== santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:381-440).
+// In: sb[r] = scores of row r (4 heads).  Out: sb[r] = u = __expf(s - m) in fp32
+// (0 on rows >= tile_len of a started 32-row chunk), m[g] = max score,
+// ell[g] = sum of u in the reference's order: thread-strided partials (chunk
+// parity selects the 32-row half when the reference block has 8 warps), an
+// 8-row tree per reference warp, reference warps added in order.
+template <int NW>
+__device__ __forceinline__ void tile_stats(float4* sb, int tile_len, int lane, float (&m)[kGH], float (&ell)[kGH]) {
+  constexpr int NH = NW / 4;
+  const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+#pragma unroll
+  for (int g = 0; g < kGH; ++g) m[g] = -CUDART_INF_F;
+#pragma unroll 1
+  for (int ch = 0; ch < nch; ++ch) {
+    if (ch * kChunkRows + lane < tile_len) {
+      const float4 s = sb[ch * kChunkRows + lane];
+      m[0] = fmaxf(m[0], s.x);
+      m[1] = fmaxf(m[1], s.y);
+      m[2] = fmaxf(m[2], s.z);
+      m[3] = fmaxf(m[3], s.w);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kGH; ++g)
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m[g] = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], off));
+
+  float V0[kGH], V1[kGH];
+#pragma unroll
+  for (int g = 0; g < kGH; ++g) V0[g] = V1[g] = 0.f;
+#pragma unroll 1
+  for (int ch = 0; ch < nch; ++ch) {
+    const bool valid = ch * kChunkRows + lane < tile_len;
+    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid) {
+      const float4 s = sb[ch * kChunkRows + lane];
+      u.x = __expf(s.x - m[0]);
+      u.y = __expf(s.y - m[1]);
+      u.z = __expf(s.z - m[2]);
+      u.w = __expf(s.w - m[3]);
+    }
+    sb[ch * kChunkRows + lane] = u;
+    if (NH == 2 && (ch & 1)) {
+      V1[0] = __fadd_rn(V1[0], u.x);
+      V1[1] = __fadd_rn(V1[1], u.y);
+      V1[2] = __fadd_rn(V1[2], u.z);
+      V1[3] = __fadd_rn(V1[3], u.w);
+    } else {
+      V0[0] = __fadd_rn(V0[0], u.x);
+      V0[1] = __fadd_rn(V0[1], u.y);
+      V0[2] = __fadd_rn(V0[2], u.z);
+      V0[3] = __fadd_rn(V0[3], u.w);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kGH; ++g) {
+    float x0 = V0[g], x1 = V1[g];
+    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 4));
+    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 2));
+    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 1));
+    float e = __shfl_sync(0xffffffffu, x0, 0);
+    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 8));
+    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 16));
+    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 24));
+    if (NH == 2) {
+      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 4));
+      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 2));
+      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 1));
+      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 0));
+      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 8));
+      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 16));
+      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 24));
+    }
+    ell[g] = e;
+  }
+}
+
+// Optional per-row trace targets of tile_counts (all may be null).
+struct RowTrace {
+  uint16_t* u16;    // storage bits of u for head g at u16[g * head_stride + row]; needs counts too
+  int16_t* counts;  // same indexing
+  int* rowmask;     // + row index
+  size_t head_stride;
+};
+
+// Systematic counts and row compaction of one tile,
+// flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:275-345
+// (== santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:771-838).
+// In: sb[r] = u (fp32, or already rounded to the storage type), invdel[g], a0[g].
+// Out: the emit list overwrites sb in place -- entry i (16 bytes: four 16-bit
+// counts, row index within the tile) describes the i-th gathered row in
+// ascending row order and lands on row i, which has been consumed by then.
+// Returns the number of gathered rows.
+template <typename TK>
+__device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, const float (&invdel)[kGH],
+                                           const float (&a0)[kGH], const RowTrace& tr) {
+  const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+  float carry[kGH];
+#pragma unroll
+  for (int g = 0; g < kGH; ++g) carry[g] = 0.f;
+  int n_emit = 0;
+  uint4* emit = reinterpret_cast<uint4*>(sb);
+#pragma unroll 1
+  for (int ch = 0; ch < nch; ++ch) {
+    const int remain = tile_len - ch * kChunkRows;
+    const int last_lane = remain > 32 ? 31 : remain - 1;
+    const bool valid = lane < remain;
+    const float4 u4 = sb[ch * kChunkRows + lane];
+    const float uu[kGH] = {u4.x, u4.y, u4.z, u4.w};
+    int c[kGH];
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
+      const float u16v = Store16<TK>::round(uu[g]);
+      const float xv = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
+      float res = xv;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float nb = __shfl_up_sync(0xffffffffu, res, off);
+        if (lane >= off) res = __fadd_rn(res, nb);
+      }
+      const float pre = __fsub_rn(res, xv);
+      const float pre_g = __fadd_rn(carry[g], pre);
+      const float cum_g = __fadd_rn(pre_g, xv);
+      const float f_prev = floorf(__fadd_rn(a0[g], pre_g));
+      const float f_curr = floorf(__fadd_rn(a0[g], cum_g));
+      int cc = (int)__fsub_rn(f_curr, f_prev);
+      cc = cc < 0 ? 0 : cc;
+      cc = cc > 32767 ? 32767 : cc;
+      c[g] = valid ? cc : 0;
+      const float chunk_total = __shfl_sync(0xffffffffu, __fadd_rn(pre, xv), last_lane);
+      carry[g] = __fadd_rn(carry[g], chunk_total);
+    }
+    if (tr.counts != nullptr && valid) {
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        const size_t o = size_t(g) * tr.head_stride + ch * kChunkRows + lane;
+        if (tr.u16 != nullptr) tr.u16[o] = Store16<TK>::bits(uu[g]);
+        tr.counts[o] = (int16_t)c[g];
+      }
+    }
+    const bool flag = (c[0] + c[1] + c[2] + c[3]) > 0;
+    const uint32_t mask = __ballot_sync(0xffffffffu, flag);
+    __syncwarp();
+    if (flag) {
+      const int pos = n_emit + __popc(mask & ((1u << lane) - 1u));
+      emit[pos] = make_uint4((uint32_t)c[0] | ((uint32_t)c[1] << 16), (uint32_t)c[2] | ((uint32_t)c[3] << 16),
+                             (uint32_t)(ch * kChunkRows + lane), 0u);
+      if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
+    }
+    n_emit += __popc(mask);
+  }
+  __syncwarp();
+  return n_emit;
+}
+
+// Sparse sum of c*V over the emit list, ascending rows, fp32 fma per head
+// (flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:347-379,
+// santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:843-857).
+// Lane l accumulates dims 4l..4l+3 of each head; four rows are in flight.
+// `vrow0` points at the V row of the tile's first row for this kv-head.
+template <typename TK>
+__device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const unsigned char* __restrict__ vrow0,
+                                            size_t row_stride, int lane, float (&o)[kGH][4]) {
+  const uint4* emit = reinterpret_cast<const uint4*>(sb);
+#pragma unroll 1
+  for (int i0 = 0; i0 < n_emit; i0 += 4) {
+    uint4 en[4];
+    uint2 vv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (i0 + k < n_emit) {
+        en[k] = emit[i0 + k];
+        vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(en[k].z) * row_stride) + lane);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (i0 + k < n_emit) {
+        const float2 va = Store16<TK>::unpack(vv[k].x), vb = Store16<TK>::unpack(vv[k].y);
+        const int cg4[kGH] = {int(en[k].x & 0xffffu), int(en[k].x >> 16), int(en[k].y & 0xffffu), int(en[k].y >> 16)};
+#pragma unroll
+        for (int g = 0; g < kGH; ++g) {
+          if (cg4[g] != 0) {
+            const float cf = (float)cg4[g];
+            o[g][0] = fmaf(cf, va.x, o[g][0]);
+            o[g][1] = fmaf(cf, va.y, o[g][1]);
+            o[g][2] = fmaf(cf, vb.x, o[g][2]);
+            o[g][3] = fmaf(cf, vb.y, o[g][3]);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// ---------------------------------------------------------------- work split over column slots
+// A CTA has kGroupWarps column slots.  With group width gw (a power of two
+// <= 8) the slots form 8/gw virtual groups of gw columns; virtual group
+// vg = cta*(8/gw) + slot/gw owns a contiguous balanced range of the
+// (column group, tile) items, column groups being gw consecutive columns.
+struct WarpWork {
+  int vg, col_in_group;
+  long long lo, hi;
+};
+
+__device__ __forceinline__ WarpWork warp_work(const WorkSplit& w, int cta, int slot) {
+  WarpWork r;
+  const int spc = kGroupWarps / w.gw;
+  r.vg = cta * spc + slot / w.gw;
+  r.col_in_group = slot % w.gw;
+  if (r.vg < w.nvg) {
+    r.lo = range_lo(r.vg, w.items, w.nvg);
+    r.hi = range_lo(r.vg + 1, w.items, w.nvg);
+  } else {
+    r.lo = r.hi = 0;
+  }
+  return r;
+}
+
+}  // namespace santa

@@ -10,36 +10,46 @@
 
 namespace santa {
 
-struct FlashParams {
+// how (column group, tile) items are dealt to the column slots of the CTAs
+struct WorkSplit {
+  int gw;           // columns per column group (1, 2, 4 or 8)
+  int nvg;          // virtual groups that own work
+  int T_c;          // tiles per column
+  int ncol;         // columns = sequences * kv-heads
+  long long items;  // column groups * T_c
+};
+
+// Streaming kernels: Flash decode and Prop's first pass.
+struct StreamParams {
   CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,16,1}
-  const void* q;  // [B,H,128]
-  const void* K;  // [B,L_storage,KVH,128]
-  const void* V;
-  int B, H, KVH;
+  const void* q;    // [B,H,128]
+  const void* V;    // [B,L_storage,KVH,128]
+  int H, KVH;
   int L_valid, L_storage;
-  int T_c;         // tiles per sequence in this call
-  int S_per_tile;  // fixed per-tile budget
+  WorkSplit ws;
+  int S_per_tile;  // Flash: fixed per-tile budget
   float q_scale;
   uint64_t seed;
   int batch_offset, tile_offset;
-  int ncol;         // B*KVH columns
-  long long items;  // column groups * T_c
-  // workspace (written here, read by the merge kernel)
-  int* status;         // one word
-  float* partials;     // [grid + column groups][8][4][kPartialStride]
-  int* partial_vrows;  // [grid + column groups][8]
-  // trace
-  float* dbg_m;
-  float* dbg_ell;
-  uint16_t* dbg_u;
-  int16_t* dbg_c;
-  int* rowmask;
+  int* status;  // one word
+  // Flash: per (virtual group, column group) partials, read by the merge kernel
+  float* partials;     // [nvg + column groups][gw][4][kPartialStride]
+  int* partial_vrows;  // [nvg + column groups][gw]
+  // Prop pass 1 outputs / Flash trace ([B,H,T_c]); Flash: may be null
+  float* m_tiles;
+  float* ell_tiles;
+  // Prop pass 1: rounded tile-local weights, [H][L_valid] 16-bit
+  uint16_t* stash;
+  // Flash trace (may be null)
+  float* dbg_invdel;  // [B,H,T_c]
+  uint16_t* dbg_u;    // [B,H,L_valid]
+  int16_t* dbg_c;     // [B,H,L_valid]
+  int* rowmask;       // [B,KVH,L_valid]
 };
 
 struct FlashMergeParams {
-  int H, KVH, T_c, S_per_tile;
-  long long items;
-  int ctas;  // grid of the decode kernel
+  int H, KVH, S_per_tile;
+  WorkSplit ws;
   const float* partials;
   const int* partial_vrows;
   void* out;           // [B,H,128] storage dtype or nullptr
@@ -48,7 +58,38 @@ struct FlashMergeParams {
   float* partial_out;  // [B,H,130] or nullptr
 };
 
-cudaError_t launch_flash(const FlashParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,
+cudaError_t launch_flash(const StreamParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,
                          cudaStream_t stream);
+
+// Prop: pass 1 (vec streaming or tensor-core), budgets, pass 2, merge.
+struct PropParams {
+  StreamParams sp;      // pass 1 (vec path) -- also carries q, V, H, KVH, L, ws, status, stash, m/ell tiles
+  const void* K;        // [L,KVH,128]
+  int block_n, T_c;
+  int use_vec;          // 1: streaming vec pass 1, 0: tensor-core pass 1
+  int S;
+  int flags;            // bit0/bit1: fma contraction choices of the budget step
+  // workspace tables [H,T_c]
+  int* S_tiles;
+  float* invdelta;
+  float* a0;
+  float* m_star;        // [H] output
+  // pass 2 partials
+  float* partials;      // [nvg + column groups][gw][4][128]
+  int* partial_vrows;
+  // outputs
+  void* out;            // [H,128] storage dtype
+  int* vrows;           // [KVH] or nullptr
+  // trace (may be null)
+  int16_t* dbg_c;       // [H,L]
+  int* rowmask;         // [KVH,L]
+};
+
+cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t stream);
+int prop_pass2_max_groups(int sms);
+
+// Cross-device combine of G unnormalised partials [G][BH][130].
+cudaError_t launch_lse_combine(const float* partials, int G, int BH, int S_per_tile, int dtype, void* out,
+                               float* m_star, cudaStream_t stream);
 
 }  // namespace santa

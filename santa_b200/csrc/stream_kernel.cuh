@@ -1,0 +1,251 @@
+// stream_kernel.cuh -- the persistent K-streaming kernel behind Flash decode and
+// Prop's first pass (vec path).  One CTA per SM, sixteen warps, two per column
+// slot:
+//   * the SCORE warp of a slot owns a TMA staging ring, streams its column's K
+//     rows and writes the four heads' scores of a tile into one of two score
+//     buffers (stream_scores.cuh);
+//   * the SAMPLER warp of the slot turns a finished score buffer into tile
+//     statistics and -- Flash -- sampled counts, the sparse sum of V rows and a
+//     running log-sum-exp state, or -- Prop pass 1 -- the stashed tile-local
+//     weights (sampler.cuh).
+// The two warps hand buffers over through a full/empty pair of mbarriers per
+// buffer, so K keeps streaming while the previous tile is being sampled.  No
+// warp ever synchronises with another slot.  All hot loops are rolled so that
+// the instruction footprint stays small; every wait is bounded and reports
+// through the status word instead of hanging.
+//
+// Included by flash_kernels.cu (compiled with --use_fast_math) and
+// prop_kernels.cu (compiled without); each instantiates only its own mode.
+#pragma once
+
+#include "sampler.cuh"
+#include "stream_scores.cuh"
+
+namespace santa {
+
+constexpr int kModeFlash = 0;
+constexpr int kModePropPass1 = 1;
+
+constexpr int kStreamStages = 4;
+constexpr int kMaxTileRows = 256;
+constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // one score buffer: scores, then u, then the emit list
+constexpr int kSlotSmem = kStreamStages * kStageBytes + 2 * kScoreBytes + kRedFloats * 4;
+constexpr int kSlotBars = kStreamStages + 4;  // ring + full[2] + empty[2]
+constexpr int kCtaWarps = 2 * kGroupWarps;
+constexpr size_t kStreamSmemBytes = size_t(kGroupWarps) * kSlotSmem + size_t(kGroupWarps) * kSlotBars * 8;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <typename TK, int BN, int MODE>
+__global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_constant__ StreamParams p) {
+  constexpr int NW = (BN == 256) ? 8 : 4;  // warps of the reference block (fixes the ell order)
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int cta_warp = threadIdx.x >> 5;
+  const int slot = cta_warp & (kGroupWarps - 1);
+  const bool is_sampler = cta_warp >= kGroupWarps;
+  const int lane = threadIdx.x & 31;
+
+  unsigned char* sbase = smem + size_t(slot) * kSlotSmem;
+  float* scorebufs = reinterpret_cast<float*>(sbase + kStreamStages * kStageBytes);
+  float* red = reinterpret_cast<float*>(sbase + kStreamStages * kStageBytes + 2 * kScoreBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kGroupWarps) * kSlotSmem) + slot * kSlotBars;
+  const uint32_t bar_full = smem_u32(bars + kStreamStages);       // [2]
+  const uint32_t bar_empty = smem_u32(bars + kStreamStages + 2);  // [2]
+
+  WarpRing<kStreamStages> ring;
+  if (!is_sampler) {
+    ring.init(sbase, bars, lane);
+    if (lane == 0) {
+      mbar_init(bar_full, 1);
+      mbar_init(bar_full + 8, 1);
+      mbar_init(bar_empty, 1);
+      mbar_init(bar_empty + 8, 1);
+      mbar_fence_init();
+    }
+  }
+  __syncthreads();
+
+  const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
+  const unsigned char* __restrict__ Vg = static_cast<const unsigned char*>(p.V);
+  const size_t row_stride = size_t(p.KVH) * kRowBytes;
+  const WarpWork ww = warp_work(p.ws, blockIdx.x, slot);
+
+  bool dead = false;     // set when a wait ran out; the status word then says why
+  uint32_t handoff = 0;  // tiles handed over so far on this slot (selects buffer and parity)
+
+  long long it = ww.lo;
+  while (it < ww.hi) {
+    const int cg = int(it / p.ws.T_c);
+    const int t_lo = int(it - (long long)cg * p.ws.T_c);
+    const int t_hi = (ww.hi - it < (long long)(p.ws.T_c - t_lo)) ? t_lo + int(ww.hi - it) : p.ws.T_c;
+    const int col = cg * p.ws.gw + ww.col_in_group;
+    const bool active = col < p.ws.ncol;
+    const int b = active ? col / p.KVH : 0;
+    const int kv = col - b * p.KVH;
+    const int h0 = kv * kGH;
+
+    if (active && !is_sampler) {
+      // =========================== SCORE warp ===============================
+      QRegs Q;
+      load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
+      const int row_base = t_lo * BN;
+      const int row_end = (t_hi * BN < p.L_valid) ? t_hi * BN : p.L_valid;
+      const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
+      int issued = 0;
+      for (; issued < kStreamStages && issued < npieces; ++issued)
+        ring.issue(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
+
+#pragma unroll 1
+      for (int t = t_lo; t < t_hi; ++t, ++handoff) {
+        const int n0 = t * BN;
+        const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const uint32_t buf = handoff & 1u;
+        float* scorebuf = scorebufs + buf * (kScoreBytes / 4);
+        // wait until the sampler has released this buffer (passes at once the first two times)
+        if (!dead && !mbar_wait_bounded(bar_empty + 8 * buf, ((handoff >> 1) & 1u) ^ 1u)) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
+        }
+        const int npc = (tile_len + kStageRows - 1) / kStageRows;
+#pragma unroll 1
+        for (int pc = 0; pc < npc; ++pc) {
+          if (!dead && !ring.wait(ring.count)) {
+            dead = true;
+            if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
+          }
+          const unsigned char* st = ring.stage_ptr(ring.count);
+          score_rows8<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+          score_rows8<TK>(st + 8 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 8) * kGH, lane);
+          if (issued < npieces && !dead) {
+            ring.issue(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
+            ++issued;
+          }
+          ++ring.count;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full + 8 * buf);
+      }
+    } else if (active) {
+      // ========================== SAMPLER warp ==============================
+      const unsigned char* vcol = Vg + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
+      float M[kGH], Z[kGH], A[kGH][4];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        M[g] = -CUDART_INF_F;
+        Z[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) A[g][i] = 0.f;
+      }
+      int vrow_count = 0;
+
+#pragma unroll 1
+      for (int t = t_lo; t < t_hi; ++t, ++handoff) {
+        const int n0 = t * BN;
+        const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const uint32_t buf = handoff & 1u;
+        float4* sb = reinterpret_cast<float4*>(scorebufs + buf * (kScoreBytes / 4));
+        if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u)) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
+        }
+
+        float m[kGH], ell[kGH];
+        tile_stats<NW>(sb, tile_len, lane, m, ell);
+        const size_t bh0 = size_t(b) * p.H + h0;
+
+        if (MODE == kModePropPass1) {
+          // tile statistics and the stash of rounded weights for the second pass
+          // (santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:404-440)
+          const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+#pragma unroll 1
+          for (int ch = 0; ch < nch; ++ch) {
+            const int r = ch * kChunkRows + lane;
+            if (r < tile_len) {
+              const float4 u = sb[r];
+              uint16_t* sp = p.stash + bh0 * p.L_valid + n0 + r;
+              sp[0] = Store16<TK>::bits(u.x);
+              sp[size_t(p.L_valid)] = Store16<TK>::bits(u.y);
+              sp[2 * size_t(p.L_valid)] = Store16<TK>::bits(u.z);
+              sp[3 * size_t(p.L_valid)] = Store16<TK>::bits(u.w);
+            }
+          }
+          __syncwarp();
+        }
+        float invdel[kGH];
+#pragma unroll
+        for (int g = 0; g < kGH; ++g)
+          invdel[g] = (p.S_per_tile > 0 && ell[g] > 1e-20f) ? ((float)p.S_per_tile / ell[g]) : 0.0f;
+        if (p.m_tiles != nullptr && lane < kGH) {
+          float mv = m[0], ev = ell[0], iv = invdel[0];
+#pragma unroll
+          for (int g = 1; g < kGH; ++g) {
+            mv = (lane == g) ? m[g] : mv;
+            ev = (lane == g) ? ell[g] : ev;
+            iv = (lane == g) ? invdel[g] : iv;
+          }
+          const size_t o = (bh0 + lane) * p.ws.T_c + t;
+          p.m_tiles[o] = mv;
+          p.ell_tiles[o] = ev;
+          if (p.dbg_invdel != nullptr) p.dbg_invdel[o] = iv;
+        }
+
+        if (MODE == kModeFlash) {
+          // systematic counts, compaction, sparse V sum, running merge
+          float a0[kGH];
+#pragma unroll
+          for (int g = 0; g < kGH; ++g)
+            a0[g] = u01_from_seed(p.seed, (p.batch_offset + b) * p.H + h0 + g, p.tile_offset + t);
+          RowTrace tr;
+          tr.head_stride = size_t(p.L_valid);
+          tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.L_valid + n0 : nullptr;
+          tr.counts = p.dbg_c ? p.dbg_c + bh0 * p.L_valid + n0 : nullptr;
+          tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * p.L_valid + n0 : nullptr;
+          const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
+          vrow_count += n_emit;
+
+          float o[kGH][4];
+#pragma unroll
+          for (int g = 0; g < kGH; ++g)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
+          gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o);
+
+#pragma unroll
+          for (int g = 0; g < kGH; ++g) {
+            const float m_new = fmaxf(M[g], m[g]);
+            const float so = __expf(M[g] - m_new);
+            const float st = __expf(m[g] - m_new) * ell[g];
+            Z[g] = Z[g] * so + st;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) A[g][i] = A[g][i] * so + st * o[g][i];
+            M[g] = m_new;
+          }
+        }
+        if (lane == 0) mbar_arrive(bar_empty + 8 * buf);  // every lane's reads were ordered by a __syncwarp
+      }  // tiles
+
+      if (MODE == kModeFlash) {
+        // ---- publish this column's partial -------------------------------
+        const size_t pslot = size_t(ww.vg + cg) * p.ws.gw + ww.col_in_group;
+        float* ps = p.partials + pslot * (kGH * kPartialStride);
+#pragma unroll
+        for (int g = 0; g < kGH; ++g) {
+          reinterpret_cast<float4*>(ps + g * kPartialStride)[lane] = make_float4(A[g][0], A[g][1], A[g][2], A[g][3]);
+          if (lane == 0) {
+            ps[g * kPartialStride + kD] = M[g];
+            ps[g * kPartialStride + kD + 1] = Z[g];
+          }
+        }
+        if (lane == 0) p.partial_vrows[pslot] = vrow_count;
+      }
+    } else {
+      handoff += uint32_t(t_hi - t_lo);
+    }
+    it += (t_hi - t_lo);
+  }
+}
+
+}  // namespace santa

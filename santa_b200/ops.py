@@ -58,6 +58,7 @@ class FlashTrace:
     u16: torch.Tensor        # [B,H,L] int16 view of storage bits
     counts: torch.Tensor     # [B,H,L] int16
     rowmask: torch.Tensor    # [B,KVH,L] int32
+    invdel: torch.Tensor     # [B,H,T_c] fp32
 
 
 def _check_flash_inputs(q_h, K_g, V_g):
@@ -127,7 +128,9 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
                             torch.empty((B, H, T_c), **fopt), torch.empty((B, H, T_c), **fopt),
                             torch.zeros((B, H, L), device=dev, dtype=torch.int16),
                             torch.zeros((B, H, L), device=dev, dtype=torch.int16),
-                            torch.zeros((B, KVH, L), device=dev, dtype=torch.int32))
+                            torch.zeros((B, KVH, L), device=dev, dtype=torch.int32),
+                            torch.empty((B, H, T_c), **fopt))
+            ext.invdel = tr.invdel.data_ptr()
             ext.m_tiles, ext.ell_tiles = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr()
             ext.u16, ext.counts, ext.rowmask = tr.u16.data_ptr(), tr.counts.data_ptr(), tr.rowmask.data_ptr()
         rc = lib.santa_flash_decode(
@@ -150,3 +153,110 @@ def workspace_status(kind: str, device: torch.device) -> int:
         return 0
     torch.cuda.synchronize(device)
     return int(ws[:4].view(torch.int32).item())
+
+
+@dataclass
+class PropTrace:
+    """Intermediates of one Prop call (parity tests)."""
+    block_n: int
+    T_c: int
+    m_tiles: torch.Tensor    # [H,T_c] fp32
+    ell_tiles: torch.Tensor  # [H,T_c] fp32
+    u16: torch.Tensor        # [H,L] int16 view of storage bits
+    counts: torch.Tensor     # [H,L] int16
+    rowmask: torch.Tensor    # [KVH,L] int32
+    S_tiles: torch.Tensor    # [H,T_c] int32
+    invdelta: torch.Tensor   # [H,T_c] fp32
+    a0: torch.Tensor         # [H,T_c] fp32
+
+
+_PASS1_MODES = {"auto": 0, "gqa": 1, "perhead": 1, "vec": 2, "gqa_vec": 2}
+
+
+def _pass1_mode_from_env() -> int:
+    # santa_fused_proportional_tile_budgets/santa_cuda.cpp:39-51
+    return _PASS1_MODES.get(os.environ.get("SANTA_PASS1", "").lower(), 0)
+
+
+def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace=False, flags=None,
+                pass1_mode=None):
+    """S2ANTA-Prop decode of one sequence: ``q_h [H,D]``, ``K_g/V_g [L,KVH,D]``.
+    Returns ``(out [H,D], m_star [H], vrows [KVH] or empty)`` (+ ``PropTrace``)."""
+    # messages follow santa_fused_proportional_tile_budgets/santa_cuda.cpp:141-167
+    _check(q_h.is_cuda, "q_h must be CUDA")
+    _check(K_g.is_cuda and V_g.is_cuda, "K_g and V_g must be CUDA")
+    _check(q_h.dtype in (torch.bfloat16, torch.float16), "q_h must be bf16 or f16")
+    _check(K_g.dtype in (torch.bfloat16, torch.float16) and K_g.dtype == V_g.dtype,
+           "K_g/V_g must be bf16 or f16 and match")
+    _check(q_h.dtype == K_g.dtype, "q_h dtype must match K_g/V_g")
+    _check(q_h.dim() == 2 and K_g.dim() == 3 and V_g.dim() == 3, "bad ranks")
+    _check(q_h.device == K_g.device and q_h.device == V_g.device, "device mismatch")
+    _check(K_g.shape == V_g.shape, "K_g and V_g must have the same shape")
+    _check(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))")
+    _check(q_h.size(0) % K_g.size(1) == 0, "H must be divisible by KVH (expected KVH == K_g.size(1) for NHD)")
+    _check(K_g.is_contiguous() and V_g.is_contiguous(), "K_g/V_g must be contiguous with layout [L, KVH, D] (NHD)")
+    if seed < 0:
+        raise TypeError("seed must be a non-negative 64-bit integer")
+    q = q_h.contiguous()
+    H, D = q.shape
+    L, KVH = K_g.size(0), K_g.size(1)
+    mode = _pass1_mode_from_env() if pass1_mode is None else int(pass1_mode)
+    _check(D == 128 and H // KVH == 4,
+           f"This build supports only D=128 and GH=4 (H/KVH). Got D={D} GH={H // KVH}")
+    bn = int(block_n)
+    if bn <= 0:
+        bn = 256 if mode == 2 else capi.block_n_rule(L, 0)
+    _check(mode != 2 or bn == 256, f"SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH={H // KVH} D={D} block_n={bn}")
+    _check(bn % 16 == 0, f"Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D={D} block_n={bn}")
+    _check(bn <= 256, f"This build supports block_n up to 256. Got block_n={bn}")
+    T_c = (L + bn - 1) // bn
+    dev = q.device
+    with torch.cuda.device(dev):
+        lib = capi.lib()
+        nbytes = lib.santa_prop_workspace_bytes(H, KVH, D, L, bn)
+        ws = _workspace("prop", dev, nbytes)
+        out = torch.empty((H, D), device=dev, dtype=q.dtype)
+        m_star = torch.empty((H,), device=dev, dtype=torch.float32)
+        vrows = torch.empty((KVH,) if want_vrows else (0,), device=dev, dtype=torch.int32)
+        ext = capi.PropExt(pass1_mode=mode, flags=3 if flags is None else int(flags))
+        tr = None
+        if trace:
+            f32 = dict(device=dev, dtype=torch.float32)
+            tr = PropTrace(bn, T_c, torch.empty((H, T_c), **f32), torch.empty((H, T_c), **f32),
+                           torch.zeros((H, L), device=dev, dtype=torch.int16),
+                           torch.zeros((H, L), device=dev, dtype=torch.int16),
+                           torch.zeros((KVH, L), device=dev, dtype=torch.int32),
+                           torch.empty((H, T_c), device=dev, dtype=torch.int32),
+                           torch.empty((H, T_c), **f32), torch.empty((H, T_c), **f32))
+            ext.m_tiles, ext.ell_tiles, ext.u16 = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr(), tr.u16.data_ptr()
+            ext.counts, ext.rowmask = tr.counts.data_ptr(), tr.rowmask.data_ptr()
+            ext.S_tiles, ext.invdelta, ext.a0 = tr.S_tiles.data_ptr(), tr.invdelta.data_ptr(), tr.a0.data_ptr()
+        rc = lib.santa_prop_decode(
+            q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), _dtype_code(q), H, KVH, D, L, int(S),
+            int(seed) & (2**64 - 1), bn, out.data_ptr(), m_star.data_ptr(),
+            vrows.data_ptr() if want_vrows else None, ws.data_ptr(), ws.numel(), C.byref(ext),
+            torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    res = (out, m_star, vrows)
+    return res + (tr,) if trace else res
+
+
+def lse_combine(partials: torch.Tensor, S_per_tile: int, dtype: torch.dtype):
+    """Combine ``partials [G,B,H,130]`` (or ``[G,BH,130]``) fp32 into ``(out [B,H,128], m_star [B,H])``."""
+    _check(partials.is_cuda and partials.dtype == torch.float32 and partials.is_contiguous(),
+           "partials must be a contiguous CUDA fp32 tensor")
+    G = partials.size(0)
+    lead = tuple(partials.shape[1:-1])
+    BH = 1
+    for d in lead:
+        BH *= d
+    dev = partials.device
+    with torch.cuda.device(dev):
+        out = torch.empty(lead + (128,), device=dev, dtype=dtype)
+        m_star = torch.empty(lead, device=dev, dtype=torch.float32)
+        rc = capi.lib().santa_lse_combine(partials.data_ptr(), G, BH, 128, int(S_per_tile),
+                                          capi.SANTA_DTYPE_BF16 if dtype == torch.bfloat16 else capi.SANTA_DTYPE_F16,
+                                          out.data_ptr(), m_star.data_ptr(),
+                                          torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    return out, m_star

@@ -1,0 +1,70 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/santa_b200.h declares;
+its host-side rules agree with the oracle; the host mirrors reject bad input like the reference."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import santa_oracle as so
+from santa_b200 import capi, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "santa_b200.h")).read()
+    return sorted(set(re.findall(r"SANTA_API[^;(]*?\b(santa_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    syms = declared_symbols()
+    assert len(syms) >= 9
+    for s in syms:
+        assert hasattr(lib, s), f"{s} is declared in santa_b200.h but not exported"
+    assert sorted(capi.EXPORTS) == syms
+
+
+def test_host_rules_match_oracle():
+    for L in (1, 16, 1536, 1537, 3072, 3073, 4096, 32768, 32769, 524288):
+        for bn in (0, 32, 64, 256):
+            assert capi.block_n_rule(L, bn) == so.block_n_rule(L, bn)
+        bn = capi.block_n_rule(L)
+        for S in (0, 1, 32, 256, 2048):
+            assert capi.flash_budget(L, bn, S) == so.flash_budget(L, bn, S)
+    rng = np.random.default_rng(2)
+    for _ in range(100):
+        seed, h, t = int(rng.integers(0, 2**62)), int(rng.integers(0, 1024)), int(rng.integers(0, 1 << 16))
+        assert np.float32(capi.u01(seed, h, t)) == so.u01(seed, h, t)
+
+
+def test_strerror_and_version():
+    lib = capi.lib()
+    assert lib.santa_abi_version() >= 1
+    assert b"block_n" in lib.santa_strerror(-4)
+    assert lib.santa_strerror(0) == b"ok"
+
+
+def test_argument_validation_needs_no_gpu():
+    """Bad arguments are rejected before any CUDA call."""
+    lib = capi.lib()
+    rc = lib.santa_flash_decode(None, None, None, 0, 1, 32, 8, 128, 16, 16, 4, 1, 0, None, None, None, None, 0, None, None)
+    assert rc == -8
+    rc = lib.santa_flash_decode(256, 256, 256, 7, 1, 32, 8, 128, 16, 16, 4, 1, 0, 256, 256, None, None, 0, None, None)
+    assert rc == -1
+    rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 64, 16, 16, 4, 1, 0, 256, 256, None, None, 0, None, None)
+    assert rc == -2
+    rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 128, 17, 16, 4, 1, 0, 256, 256, None, None, 0, None, None)
+    assert rc == -3
+
+
+def test_host_mirror_rejects_like_the_reference():
+    q = torch.zeros(2, 32, 128, dtype=torch.bfloat16)
+    K = torch.zeros(2, 16, 8, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="q_h must be CUDA"):
+        ops.flash_decode(q, K, K, 4)
+    with pytest.raises(RuntimeError, match="q_h must be CUDA"):
+        ops.prop_decode(q[0], K[0], K[0], 4)
