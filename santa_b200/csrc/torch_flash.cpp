@@ -13,7 +13,10 @@
 
 #include <map>
 #include <mutex>
+#include <stdexcept>
+#include <string>
 #include <tuple>
+#include <type_traits>
 
 #include "santa_b200.h"
 
@@ -21,34 +24,56 @@ namespace py = pybind11;
 
 namespace {
 
+// Argument errors surface in Python as RuntimeError with the reference's
+// message text (the reference raises them through TORCH_CHECK).
+inline void cat_into(std::string&) {}
+template <typename T, typename... Rest>
+inline void cat_into(std::string& s, const T& v, const Rest&... rest) {
+  if constexpr (std::is_arithmetic_v<T>)
+    s += std::to_string(v);
+  else
+    s += v;
+  cat_into(s, rest...);
+}
+template <typename... Args>
+[[noreturn]] inline void fail(const Args&... args) {
+  std::string msg;
+  cat_into(msg, args...);
+  throw std::runtime_error(msg);
+}
+#define SANTA_CHECK(cond, ...) \
+  do {                         \
+    if (!(cond)) fail(__VA_ARGS__); \
+  } while (0)
+
 struct ShapeInfo {
   bool batched;
   int B, H, D, L_storage, KVH;
 };
 
 ShapeInfo check_inputs(const at::Tensor& q_h, const at::Tensor& K_g, const at::Tensor& V_g) {
-  TORCH_CHECK(q_h.is_cuda(), "q_h must be CUDA");
-  TORCH_CHECK(K_g.is_cuda() && V_g.is_cuda(), "K_g and V_g must be CUDA");
-  TORCH_CHECK(q_h.scalar_type() == at::kBFloat16 || q_h.scalar_type() == at::kHalf, "q_h must be bf16 or f16");
-  TORCH_CHECK(K_g.scalar_type() == at::kBFloat16 || K_g.scalar_type() == at::kHalf, "K_g must be bf16 or f16");
-  TORCH_CHECK(K_g.scalar_type() == V_g.scalar_type(), "K_g and V_g must have the same dtype");
-  TORCH_CHECK(q_h.scalar_type() == K_g.scalar_type(), "q_h dtype must match K_g/V_g dtype");
-  TORCH_CHECK(q_h.device() == K_g.device() && q_h.device() == V_g.device(), "device mismatch");
-  TORCH_CHECK(K_g.is_contiguous() && V_g.is_contiguous(),
+  SANTA_CHECK(q_h.is_cuda(), "q_h must be CUDA");
+  SANTA_CHECK(K_g.is_cuda() && V_g.is_cuda(), "K_g and V_g must be CUDA");
+  SANTA_CHECK(q_h.scalar_type() == at::kBFloat16 || q_h.scalar_type() == at::kHalf, "q_h must be bf16 or f16");
+  SANTA_CHECK(K_g.scalar_type() == at::kBFloat16 || K_g.scalar_type() == at::kHalf, "K_g must be bf16 or f16");
+  SANTA_CHECK(K_g.scalar_type() == V_g.scalar_type(), "K_g and V_g must have the same dtype");
+  SANTA_CHECK(q_h.scalar_type() == K_g.scalar_type(), "q_h dtype must match K_g/V_g dtype");
+  SANTA_CHECK(q_h.device() == K_g.device() && q_h.device() == V_g.device(), "device mismatch");
+  SANTA_CHECK(K_g.is_contiguous() && V_g.is_contiguous(),
               "K_g/V_g must be contiguous. Expected [L,KVH,D] for single or [B,L,KVH,D] for batch.");
   ShapeInfo s{};
   if (q_h.dim() == 2) {
-    TORCH_CHECK(K_g.dim() == 3 && V_g.dim() == 3, "Single-request path expects q_h [H,D], K_g/V_g [L,KVH,D]");
-    TORCH_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
-    TORCH_CHECK(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))");
+    SANTA_CHECK(K_g.dim() == 3 && V_g.dim() == 3, "Single-request path expects q_h [H,D], K_g/V_g [L,KVH,D]");
+    SANTA_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+    SANTA_CHECK(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))");
     s = {false, 1, (int)q_h.size(0), (int)q_h.size(1), (int)K_g.size(0), (int)K_g.size(1)};
     return s;
   }
-  TORCH_CHECK(q_h.dim() == 3 && K_g.dim() == 4 && V_g.dim() == 4,
+  SANTA_CHECK(q_h.dim() == 3 && K_g.dim() == 4 && V_g.dim() == 4,
               "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
-  TORCH_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
-  TORCH_CHECK(q_h.size(0) == K_g.size(0), "Batch mismatch between q_h and K_g/V_g");
-  TORCH_CHECK(q_h.size(2) == K_g.size(3), "D mismatch (q_h.size(2) vs K_g.size(3))");
+  SANTA_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+  SANTA_CHECK(q_h.size(0) == K_g.size(0), "Batch mismatch between q_h and K_g/V_g");
+  SANTA_CHECK(q_h.size(2) == K_g.size(3), "D mismatch (q_h.size(2) vs K_g.size(3))");
   s = {true, (int)q_h.size(0), (int)q_h.size(1), (int)q_h.size(2), (int)K_g.size(1), (int)K_g.size(2)};
   return s;
 }
@@ -72,19 +97,20 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
                                                                  int64_t S, uint64_t seed, int64_t block_n,
                                                                  bool want_vrows, int64_t valid_len) {
   const ShapeInfo info = check_inputs(q_h, K_g, V_g);
+  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
+  const int L = (valid_len > 0) ? (int)valid_len : L_storage;
+  SANTA_CHECK(L > 0, "valid_len must be > 0; got ", L);
+  SANTA_CHECK(L <= L_storage, "valid_len exceeds storage length: valid_len=", L, " storage=", L_storage);
+  SANTA_CHECK(D == 128, "This build supports only D=128. Got D=", D);
+  SANTA_CHECK(H % KVH == 0, "H must be divisible by KVH. Got H=", H, " KVH=", KVH);
+  SANTA_CHECK(H / KVH == 4, "This build supports only GH=4 (H/KVH). Got GH=", H / KVH, " (H=", H, " KVH=", KVH, ")");
+  const int bn = santa_block_n_rule(L, (int)block_n);
+  SANTA_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
+
+  // argument errors are raised above, before any device state is touched
   const c10::cuda::CUDAGuard guard(q_h.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   auto q = q_h.contiguous();
-
-  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
-  const int L = (valid_len > 0) ? (int)valid_len : L_storage;
-  TORCH_CHECK(L > 0, "valid_len must be > 0; got ", L);
-  TORCH_CHECK(L <= L_storage, "valid_len exceeds storage length: valid_len=", L, " storage=", L_storage);
-  TORCH_CHECK(D == 128, "This build supports only D=128. Got D=", D);
-  TORCH_CHECK(H % KVH == 0, "H must be divisible by KVH. Got H=", H, " KVH=", KVH);
-  TORCH_CHECK(H / KVH == 4, "This build supports only GH=4 (H/KVH). Got GH=", H / KVH, " (H=", H, " KVH=", KVH, ")");
-  const int bn = santa_block_n_rule(L, (int)block_n);
-  TORCH_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
 
   auto optsF = q.options().dtype(at::kFloat);
   auto optsI = q.options().dtype(at::kInt);
@@ -94,7 +120,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
   if (want_vrows) vrows = info.batched ? at::empty({B, KVH}, optsI) : at::empty({KVH}, optsI);
 
   const size_t ws_bytes = santa_flash_workspace_bytes(B, KVH, L, bn);
-  TORCH_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
 
   const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
@@ -102,7 +128,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
                                     D, L, L_storage, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
                                     want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(),
                                     nullptr, (void*)stream.stream());
-  TORCH_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
               ")");
   return std::make_tuple(out, m_star, vrows);
 }

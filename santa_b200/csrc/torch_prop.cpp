@@ -1,0 +1,136 @@
+// torch_prop.cpp -- the `santa_prop_batch_cuda` Python module: a thin
+// pybind11/ATen shim over the C ABI of libsanta_b200.so.
+//
+// Same name, argument order, defaults, tensor layouts, return tuple and error
+// messages as the reference module of that name
+// (santa_fused_proportional_tile_budgets/santa_cuda.cpp:141-359).  Like the
+// reference it exposes ONLY decode_systematic_scalar, takes a single sequence
+// (q_h [H,D]) and has no valid_len argument: tutorial_code/attention_backends.py
+// (:476-500) relies on the batched call failing with a TypeError that names
+// valid_len and then loops over the batch.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <algorithm>
+#include <cctype>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <string>
+#include <stdexcept>
+#include <string>
+#include <tuple>
+#include <type_traits>
+
+#include "santa_b200.h"
+
+namespace py = pybind11;
+
+namespace {
+
+// Argument errors surface in Python as RuntimeError with the reference's
+// message text (the reference raises them through TORCH_CHECK).
+inline void cat_into(std::string&) {}
+template <typename T, typename... Rest>
+inline void cat_into(std::string& s, const T& v, const Rest&... rest) {
+  if constexpr (std::is_arithmetic_v<T>)
+    s += std::to_string(v);
+  else
+    s += v;
+  cat_into(s, rest...);
+}
+template <typename... Args>
+[[noreturn]] inline void fail(const Args&... args) {
+  std::string msg;
+  cat_into(msg, args...);
+  throw std::runtime_error(msg);
+}
+#define SANTA_CHECK(cond, ...) \
+  do {                         \
+    if (!(cond)) fail(__VA_ARGS__); \
+  } while (0)
+
+// SANTA_PASS1 = auto | gqa (perhead) | vec (gqa_vec), santa_cuda.cpp:39-51
+int pass1_mode_from_env() {
+  const char* env = std::getenv("SANTA_PASS1");
+  if (!env) return 0;
+  std::string s(env);
+  std::transform(s.begin(), s.end(), s.begin(), [](unsigned char c) { return (char)std::tolower(c); });
+  if (s == "gqa" || s == "perhead") return 1;
+  if (s == "vec" || s == "gqa_vec") return 2;
+  return 0;
+}
+
+at::Tensor& workspace_for(const at::Tensor& like, cudaStream_t stream, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, at::Tensor> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  at::Tensor& ws = cache[{(int)like.get_device(), stream}];
+  if (!ws.defined() || (size_t)ws.numel() < bytes) {
+    const int64_t n = (int64_t)std::max<size_t>(bytes, size_t(8) << 20);
+    ws = at::zeros({n}, like.options().dtype(at::kByte));
+  }
+  return ws;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tensor q_h, at::Tensor K_g,
+                                                                        at::Tensor V_g, int64_t S, uint64_t seed,
+                                                                        int64_t block_n, bool want_vrows) {
+  SANTA_CHECK(q_h.is_cuda(), "q_h must be CUDA");
+  SANTA_CHECK(K_g.is_cuda() && V_g.is_cuda(), "K_g and V_g must be CUDA");
+  SANTA_CHECK(q_h.scalar_type() == at::kBFloat16 || q_h.scalar_type() == at::kHalf, "q_h must be bf16 or f16");
+  SANTA_CHECK((K_g.scalar_type() == at::kBFloat16 || K_g.scalar_type() == at::kHalf) &&
+                  K_g.scalar_type() == V_g.scalar_type(),
+              "K_g/V_g must be bf16 or f16 and match");
+  SANTA_CHECK(q_h.scalar_type() == K_g.scalar_type(), "q_h dtype must match K_g/V_g");
+  SANTA_CHECK(q_h.dim() == 2 && K_g.dim() == 3 && V_g.dim() == 3, "bad ranks");
+  SANTA_CHECK(q_h.device() == K_g.device() && q_h.device() == V_g.device(), "device mismatch");
+  SANTA_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+  SANTA_CHECK(q_h.size(1) == K_g.size(2), "D mismatch (q_h.size(1) vs K_g.size(2))");
+  SANTA_CHECK(q_h.size(0) % K_g.size(1) == 0, "H must be divisible by KVH (expected KVH == K_g.size(1) for NHD)");
+  SANTA_CHECK(K_g.is_contiguous() && V_g.is_contiguous(), "K_g/V_g must be contiguous with layout [L, KVH, D] (NHD)");
+
+  const int H = (int)q_h.size(0), D = (int)q_h.size(1), L = (int)K_g.size(0), KVH = (int)K_g.size(1);
+  SANTA_CHECK(D == 128 && H / KVH == 4, "This build supports only D=128 and GH=4 (H/KVH). Got D=", D,
+              " GH=", H / KVH);
+  const int mode = pass1_mode_from_env();
+  int bn = (int)block_n;
+  if (bn <= 0) bn = (mode == 2) ? 256 : santa_block_n_rule(L, 0);
+  SANTA_CHECK(mode != 2 || bn == 256, "SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH=", H / KVH,
+              " D=", D, " block_n=", bn);
+  SANTA_CHECK(bn % 16 == 0, "Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D=", D,
+              " block_n=", bn);
+  SANTA_CHECK(bn <= 256, "This build supports block_n up to 256. Got block_n=", bn);
+
+  // argument errors are raised above, before any device state is touched
+  const c10::cuda::CUDAGuard guard(q_h.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_h.contiguous();
+
+  at::Tensor out = at::empty({H, D}, q.options());
+  at::Tensor m_star = at::empty({H}, q.options().dtype(at::kFloat));
+  at::Tensor vrows = at::empty({want_vrows ? (int64_t)KVH : (int64_t)0}, q.options().dtype(at::kInt));
+
+  const size_t ws_bytes = santa_prop_workspace_bytes(H, KVH, D, L, bn);
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  santa_prop_ext ext{};
+  ext.pass1_mode = mode;
+  ext.flags = 3;
+  const int rc = santa_prop_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
+                                   q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, H, KVH, D,
+                                   L, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
+                                   want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(),
+                                   &ext, (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+  return std::make_tuple(out, m_star, vrows);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("decode_systematic_scalar", &decode_systematic_scalar, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
+        py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false);
+}

@@ -1,0 +1,336 @@
+"""GPU parity tests of the CUDA path (through the C ABI) against the reference's own kernels
+(oracle/_ref), the golden fixtures and the CPU oracle.  Integer results are compared bit-for-bit;
+attention outputs within max-abs 2e-2 / mean-abs 2e-3 (the tolerance the task states for bf16)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import ref_gpu
+from oracle import santa_oracle as so
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+HAVE_REF = ref_gpu.available()
+needs_ref = pytest.mark.skipif(not HAVE_REF, reason="oracle/_ref not built (needs the reference tree)")
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def ops():
+    from santa_b200 import ops as _ops
+    return _ops
+
+
+def bits_eq(a, b):
+    return bool((a.view(torch.int32) == b.view(torch.int32)).all())
+
+
+def close(a, b):
+    d = (a.float() - b.float()).abs()
+    return d.max().item() <= MAX_ABS and d.mean().item() <= MEAN_ABS
+
+
+def dense_counts(g, shape):
+    c = np.zeros(int(np.prod(shape)), np.int16)
+    c[g["ref_counts_idx"]] = g["ref_counts_val"]
+    return c.reshape(shape)
+
+
+def flash_eval_torch(counts, V, m_tiles, ell_tiles, bn, spt):
+    """fp32 torch evaluation of the Flash estimator over a given count table (on the GPU)."""
+    B, H, L = counts.shape
+    KVH = V.shape[2]
+    ms = m_tiles.max(-1, keepdim=True).values
+    w = torch.exp(m_tiles - ms) * ell_tiles                     # [B,H,T_c]
+    Z = w.sum(-1)
+    wrow = w.repeat_interleave(bn, dim=-1)[..., :L]             # [B,H,L]
+    cw = counts.float() * wrow
+    out = torch.zeros(B, H, 128, device=counts.device)
+    for kv in range(KVH):
+        Vk = V[:, :L, kv].float()                               # [B,L,128]
+        out[:, 4 * kv:4 * kv + 4] = torch.bmm(cw[:, 4 * kv:4 * kv + 4], Vk)
+    return out / (Z * spt).clamp_min(1e-30)[..., None] if spt > 0 else out * 0
+
+
+# ---------------------------------------------------------------- Flash
+FLASH_SHAPES = [  # B, L, Ls, KVH, S, seed, dtype, block_n
+    (1, 4096, 4096, 8, 32, 1690, "bf16", 0),
+    (2, 4096, 4096, 8, 2048, 7, "bf16", 0),
+    (3, 5000, 6000, 3, 300, 3, "bf16", 0),
+    (2, 1, 4, 2, 64, 11, "bf16", 0),
+    (2, 16, 16, 8, 2048, 11, "bf16", 0),
+    (2, 31, 40, 2, 64, 11, "bf16", 0),
+    (2, 33, 33, 2, 64, 11, "f16", 0),
+    (2, 255, 300, 2, 64, 11, "bf16", 0),
+    (2, 257, 257, 2, 64, 11, "bf16", 0),
+    (1, 1536, 1536, 2, 256, 12, "bf16", 0),
+    (1, 1537, 1537, 2, 256, 12, "f16", 0),
+    (1, 3072, 3072, 2, 256, 12, "bf16", 0),
+    (1, 3073, 3100, 2, 256, 12, "bf16", 0),
+    (1, 2000, 2000, 4, 100, 5, "bf16", 256),
+    (1, 9000, 9000, 8, 100, 5, "bf16", 32),
+    (2, 8200, 8200, 8, 0, 5, "bf16", 0),
+    (5, 7000, 7000, 1, 1, 5, "f16", 0),
+]
+
+
+@needs_ref
+@pytest.mark.parametrize("B,L,Ls,KVH,S,seed,dtype,block_n", FLASH_SHAPES)
+def test_flash_matches_reference_binary(B, L, Ls, KVH, S, seed, dtype, block_n):
+    q, K, V = cases.make_qkv(B, Ls, KVH, dtype, 100 + L, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True,
+                                                valid_len=L, trace=True)
+    ref_counts, _ = ref_gpu.flash_counts(q, K, S, seed=seed, block_n=block_n, valid_len=L)
+    r = ref_gpu.flash_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True, valid_len=L)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("flash", dev()) == 0
+    assert (tr.block_n, tr.T_c, tr.S_per_tile) == (r.block_n, r.T_c, r.S_per_tile)
+    assert (tr.counts.int() == ref_counts).all()            # sampled rows: bit-exact
+    assert bits_eq(tr.m_tiles, r.m_tiles) and bits_eq(tr.ell_tiles, r.ell_tiles)
+    assert bits_eq(m_star, r.m_star)
+    assert (vrows == r.vrows).all() and (tr.rowmask == r.rowmask).all()
+    assert close(out, r.out)
+    if S == 0:
+        assert (out == 0).all()
+
+
+@pytest.mark.parametrize("name", list(cases.FLASH_CASES))
+def test_flash_matches_golden_and_oracle(name):
+    """No reference build needed: golden fixtures (from the reference kernels) + CPU oracle."""
+    c = cases.FLASH_CASES[name]
+    g = np.load(os.path.join(GOLDEN, f"flash_{name}.npz"))
+    qc, Kc, Vc = cases.make_qkv(c["B"], c["Ls"], c["KVH"], c["dtype"], c["gen_seed"], c["kscale"], c["heavy"])
+    q, K, V = qc.to(dev()), Kc.to(dev()), Vc.to(dev())
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, c["S"], seed=c["seed"], block_n=c["block_n"],
+                                                want_vrows=True, valid_len=c["L"], trace=True)
+    torch.cuda.synchronize()
+    H = 4 * c["KVH"]
+    ref_counts = dense_counts(g, (c["B"], H, c["L"]))
+    assert (tr.counts.cpu().numpy() == ref_counts).all()
+    assert (tr.m_tiles.cpu().numpy().view(np.int32) == g["ref_m_tiles"].view(np.int32)).all()
+    assert (tr.ell_tiles.cpu().numpy().view(np.int32) == g["ref_ell_tiles"].view(np.int32)).all()
+    assert (tr.u16.cpu().numpy().view(np.uint16) == g["dev_u16"]).all()
+    assert (vrows.cpu().numpy() == g["ref_vrows"]).all()
+    assert (m_star.cpu().numpy().view(np.int32) == g["ref_m_star"].view(np.int32)).all()
+    isb = c["dtype"] == "bf16"
+    out_ref = torch.from_numpy(so.from16(g["ref_out"], isb))
+    assert close(out.cpu(), out_ref)
+    # CPU oracle fed with the device's approximate intermediates reproduces the device's counts
+    r = so.flash_decode(cases.bits(qc), cases.bits(Kc), cases.bits(Vc), c["S"], seed=c["seed"],
+                        block_n=c["block_n"], valid_len=c["L"], is_bf16=isb,
+                        inject_u16=tr.u16.cpu().numpy().view(np.uint16), inject_ell=tr.ell_tiles.cpu().numpy(),
+                        inject_invdel=tr.invdel.cpu().numpy())
+    assert (r.counts == tr.counts.cpu().numpy()).all()
+    assert (r.m_tiles.view(np.int32) == tr.m_tiles.cpu().numpy().view(np.int32)).all()
+    assert close(out.cpu(), torch.from_numpy(r.out))
+
+
+def test_flash_dropin_module_equals_c_abi_path():
+    import santa_b200
+    santa_b200.enable_dropin()
+    import santa_flash_batch_cuda as mod
+    q, K, V = cases.make_qkv(2, 5000, 8, "bf16", 9, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    a = ops().flash_decode(q, K, V, 256, seed=1690, want_vrows=True, valid_len=4500)
+    # the reference adapter's call: positional q,K,V,S then keywords (attention_backends.py:464-473)
+    b = mod.decode_systematic_batched(q.contiguous(), K, V, 256, seed=1690, want_vrows=True, valid_len=4500)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert b[0].shape == (2, 32, 128) and b[0].dtype == torch.bfloat16 and b[1].shape == (2, 32)
+    # scalar alias, single sequence, no vrows -> empty int32 tensor of shape [0]
+    c = mod.decode_systematic_scalar(q[0], K[0], V[0], 256, seed=1690, valid_len=4500)
+    assert c[0].shape == (32, 128) and c[2].shape == (0,) and c[2].dtype == torch.int32
+    s = ops().flash_decode(q[0], K[0], V[0], 256, seed=1690, valid_len=4500)
+    assert torch.equal(c[0], s[0])
+    # head index of the RNG key is b*H + h: sequence 0 of the batch equals the single call
+    assert torch.equal(c[0], b[0][0])
+    with pytest.raises(TypeError):
+        mod.decode_systematic_batched(q, K, V, 256, seed=-1)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        mod.decode_systematic_batched(q, K.transpose(1, 2), V.transpose(1, 2), 256)
+    with pytest.raises(RuntimeError, match="valid_len exceeds storage length"):
+        mod.decode_systematic_batched(q, K, V, 256, valid_len=6000)
+    with pytest.raises(RuntimeError, match="block_n must be 0"):
+        mod.decode_systematic_batched(q, K, V, 256, block_n=128)
+    with pytest.raises(RuntimeError, match="GH=4"):
+        mod.decode_systematic_batched(q[:, :16], K, V, 256)
+
+
+def test_flash_full_size_properties():
+    """Config 1 at full size (B=8, L=32768, S=256): size-independent properties."""
+    q, K, V = cases.make_qkv(8, 32768, 8, "bf16", 1690, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, 256, seed=1690, want_vrows=True, trace=True)
+    out2, _, vrows2 = ops().flash_decode(q, K, V, 256, seed=1690, want_vrows=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) and torch.equal(vrows, vrows2)          # deterministic
+    assert (tr.T_c, tr.S_per_tile) == (128, 2)
+    per_tile = tr.counts.view(8, 32, 128, 256).sum(-1)
+    assert per_tile.min() >= 1 and per_tile.max() <= 3                     # ~S_per_tile samples per (head, tile)
+    flagged = (tr.counts.view(8, 8, 4, 32768) > 0).any(2)                  # a row is gathered iff some head drew it
+    assert (flagged.sum(-1).int() == vrows).all()
+    assert ((tr.rowmask != 0) == flagged).all()
+    assert bits_eq(m_star, tr.m_tiles.max(-1).values)
+    ev = flash_eval_torch(tr.counts, V, tr.m_tiles, tr.ell_tiles, 256, 2)   # fp32 evaluation over the op's counts
+    assert close(out, ev)
+    # offsets: a0[b,h,t] only depends on (seed, b*H+h, t)
+    assert ops().workspace_status("flash", dev()) == 0
+    if HAVE_REF:
+        rc, _ = ref_gpu.flash_counts(q, K, 256, seed=1690)
+        assert (tr.counts.int() == rc).all()
+
+
+def test_flash_sharding_extensions():
+    """Sequence shards (global tile index, global budget) + LSE combine == unsharded; batch shards with
+    batch_offset == unsharded."""
+    q, K, V = cases.make_qkv(2, 8192, 8, "bf16", 21, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    S, seed = 512, 1690
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, S, seed=seed, want_vrows=True, trace=True)
+    for G in (2, 4, 8):
+        Lr = 8192 // G
+        parts, cnts, vr = [], [], 0
+        for r in range(G):
+            Kr, Vr = K[:, r * Lr:(r + 1) * Lr].contiguous(), V[:, r * Lr:(r + 1) * Lr].contiguous()
+            p_, _, v_, t_ = ops().flash_decode(q, Kr, Vr, S, seed=seed, block_n=tr.block_n, want_vrows=True,
+                                               partial=True, trace=True, tile_offset=r * (Lr // 256),
+                                               s_per_tile=tr.S_per_tile)
+            parts.append(p_)
+            cnts.append(t_.counts)
+            vr = vr + v_
+        assert torch.equal(torch.cat(cnts, dim=2), tr.counts)              # same samples as the unsharded call
+        assert torch.equal(vr, vrows)
+        o2, ms2 = ops().lse_combine(torch.stack(parts).contiguous(), tr.S_per_tile, torch.bfloat16)
+        assert bits_eq(ms2, m_star)
+        assert (o2.float() - out.float()).abs().max().item() <= 2 ** -7      # fp32 merge order + one bf16 rounding
+        # CPU oracle of the merge rule
+        oc, mc = so.merge_partials(torch.stack(parts)[:, 0].cpu().numpy(), tr.S_per_tile)
+        assert np.abs(oc - o2[0].float().cpu().numpy()).max() <= 2 ** -7
+    ob = [ops().flash_decode(q[b:b + 1], K[b:b + 1], V[b:b + 1], S, seed=seed, batch_offset=b)[0] for b in range(2)]
+    assert torch.equal(torch.cat(ob), out)
+
+
+# ---------------------------------------------------------------- Prop
+PROP_SHAPES = [  # L, KVH, S, seed, dtype, block_n
+    (4096, 8, 256, 1690, "bf16", 0), (3300, 2, 64, 7, "f16", 0), (600, 2, 48, 9, "bf16", 0),
+    (2000, 4, 100, 10, "bf16", 0), (16, 8, 2048, 3, "bf16", 0), (1, 2, 5, 3, "bf16", 0),
+    (257, 2, 64, 3, "bf16", 256), (1000, 2, 64, 3, "bf16", 128), (5000, 8, 0, 3, "bf16", 0),
+    (9000, 8, 256, 1690, "bf16", 48), (23132, 8, 256, 1690, "bf16", 0), (8769, 8, 256, 1690, "bf16", 0),
+]
+
+
+@needs_ref
+@pytest.mark.parametrize("L,KVH,S,seed,dtype,block_n", PROP_SHAPES)
+def test_prop_matches_reference_binary(L, KVH, S, seed, dtype, block_n):
+    q, K, V = cases.make_qkv(1, L, KVH, dtype, 200 + L, 1.0, True)
+    q, K, V = q[0].to(dev()), K[0].to(dev()), V[0].to(dev())
+    out, m_star, vrows, tr = ops().prop_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True, trace=True)
+    r = ref_gpu.prop_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("prop", dev()) == 0
+    assert (tr.block_n, tr.T_c) == (r.block_n, r.T_c)
+    assert bits_eq(tr.m_tiles, r.m_tiles) and bits_eq(tr.ell_tiles, r.ell_tiles)
+    assert (tr.u16 == r.u_stash.view(torch.int16).t()).all()
+    assert bits_eq(m_star, r.m_star) and bits_eq(tr.a0, r.a0)
+    # the reference sums Z with unordered atomics: budgets may differ by one sample on rare tiles
+    dS = (tr.S_tiles - r.S_tiles).abs()
+    assert dS.max().item() <= 1 and (dS != 0).float().mean().item() <= 0.01
+    if dS.max().item() == 0:
+        assert bits_eq(tr.invdelta, r.invdelta)
+        assert (vrows == r.vrows).all() and (tr.rowmask == r.rowmask).all()
+        if L <= 4096:
+            rc, _ = ref_gpu.prop_counts(q, K, S, seed=seed, block_n=block_n)
+            assert (tr.counts.int() == rc).all()
+    assert close(out, r.out)
+    if S == 0:
+        assert (out == 0).all()
+
+
+@pytest.mark.parametrize("name", list(cases.PROP_CASES))
+def test_prop_matches_golden_and_oracle(name):
+    c = cases.PROP_CASES[name]
+    g = np.load(os.path.join(GOLDEN, f"prop_{name}.npz"))
+    qc, Kc, Vc = cases.make_qkv(1, c["L"], c["KVH"], c["dtype"], c["gen_seed"], c["kscale"], c["heavy"], GH=c["GH"])
+    q, K, V = qc[0].to(dev()), Kc[0].to(dev()), Vc[0].to(dev())
+    out, m_star, vrows, tr = ops().prop_decode(q, K, V, c["S"], seed=c["seed"], block_n=c["block_n"],
+                                               want_vrows=True, trace=True)
+    torch.cuda.synchronize()
+    H = c["GH"] * c["KVH"]
+    assert (tr.m_tiles.cpu().numpy().view(np.int32) == g["ref_m_tiles"].view(np.int32)).all()
+    assert (tr.ell_tiles.cpu().numpy().view(np.int32) == g["ref_ell_tiles"].view(np.int32)).all()
+    assert (tr.u16.cpu().numpy().view(np.uint16) == g["ref_u_stash"].T).all()
+    assert (tr.S_tiles.cpu().numpy() == g["ref_S_tiles"]).all()
+    assert (tr.invdelta.cpu().numpy().view(np.int32) == g["ref_invdelta"].view(np.int32)).all()
+    assert (tr.a0.cpu().numpy().view(np.int32) == g["ref_a0"].view(np.int32)).all()
+    assert (tr.counts.cpu().numpy() == dense_counts(g, (H, c["L"]))).all()
+    assert (vrows.cpu().numpy() == g["ref_vrows"]).all()
+    isb = c["dtype"] == "bf16"
+    assert close(out.cpu(), torch.from_numpy(so.from16(g["ref_out"], isb)))
+    # CPU oracle downstream of the device's tile statistics
+    r = so.prop_decode(cases.bits(qc[0]), cases.bits(Kc[0]), cases.bits(Vc[0]), c["S"], seed=c["seed"],
+                       block_n=c["block_n"], is_bf16=isb, inject_u16=tr.u16.cpu().numpy().view(np.uint16),
+                       inject_ell=tr.ell_tiles.cpu().numpy(), inject_m=tr.m_tiles.cpu().numpy())
+    assert (r.S_tiles == tr.S_tiles.cpu().numpy()).all()
+    assert (r.counts == tr.counts.cpu().numpy()).all()
+    assert close(out.cpu(), torch.from_numpy(r.out))
+    ev = so.prop_eval_over_counts(tr.counts.cpu().numpy(), Vc[0].float().numpy(), c["S"])
+    assert close(out.cpu(), torch.from_numpy(ev).float())
+
+
+def test_prop_dropin_module_and_adapter_fallback():
+    import santa_b200
+    santa_b200.enable_dropin()
+    import santa_prop_batch_cuda as mod
+    assert not hasattr(mod, "decode_systematic_batched")
+    q, K, V = cases.make_qkv(3, 6000, 8, "bf16", 31, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    valid_len = 5000
+    # what _SantaBaseBackend.decode does (attention_backends.py:462-500)
+    with pytest.raises(TypeError) as ei:
+        mod.decode_systematic_scalar(q.contiguous(), K, V, 256, seed=7, want_vrows=False, valid_len=valid_len)
+    assert "valid_len" in str(ei.value)
+    outs = []
+    for b in range(3):
+        k_b, v_b = K[b, :valid_len].contiguous(), V[b, :valid_len].contiguous()
+        o = mod.decode_systematic_scalar(q[b].contiguous(), k_b, v_b, 256, seed=7, want_vrows=False)
+        assert o[2].shape == (0,) and o[1].shape == (32,)
+        outs.append(o[0])
+        o2 = ops().prop_decode(q[b], k_b, v_b, 256, seed=7)
+        assert torch.equal(o[0], o2[0]) and torch.equal(o[1], o2[1])
+    assert torch.stack(outs).shape == (3, 32, 128)
+    # two identical calls give identical bits (fixed summation order)
+    o3 = mod.decode_systematic_scalar(q[0].contiguous(), K[0, :valid_len].contiguous(), V[0, :valid_len].contiguous(),
+                                      256, seed=7, want_vrows=True)
+    assert torch.equal(o3[0], outs[0]) and o3[2].shape == (8,)
+    with pytest.raises(RuntimeError, match="bad ranks"):
+        mod.decode_systematic_scalar(q, K, V, 256)
+
+
+def test_prop_ragged_batch_properties():
+    """Config 2 lengths (seed-7 draw), S=256: budgets sum to S when the tile count is a power of two or
+    at least never exceed it, counts per tile follow the budgets, output equals the fp32 evaluation."""
+    lengths = torch.randint(8192, 65537, (16,), generator=torch.Generator().manual_seed(7)).tolist()
+    assert lengths[:4] == [23132, 8769, 40428, 11428] and sum(lengths) == 562962
+    for L in (lengths[1], lengths[5]):
+        q, K, V = cases.make_qkv(1, L, 8, "bf16", L, 1.0, True)
+        q, K, V = q[0].to(dev()), K[0].to(dev()), V[0].to(dev())
+        out, m_star, vrows, tr = ops().prop_decode(q, K, V, 256, seed=1690, want_vrows=True, trace=True)
+        torch.cuda.synchronize()
+        assert (tr.S_tiles.sum(1) <= 256).all() and (tr.S_tiles.sum(1) >= 256 - tr.T_c).all()
+        pad = tr.T_c * 256 - L
+        cnt = torch.nn.functional.pad(tr.counts, (0, pad)).view(32, tr.T_c, 256).sum(-1)
+        assert ((cnt - tr.S_tiles).abs() <= 1).all()
+        flagged = (tr.counts.view(8, 4, L) > 0).any(1)
+        assert (flagged.sum(-1).int() == vrows).all()
+        ev = torch.zeros(32, 128, device=dev())
+        for kv in range(8):
+            ev[4 * kv:4 * kv + 4] = tr.counts[4 * kv:4 * kv + 4].float() @ V[:, kv].float()
+        assert close(out, ev / 256)
