@@ -1,0 +1,79 @@
+"""Multi-GPU decode, one process per GPU over torch.distributed.
+
+* ``batch_sharded_flash_decode``: independent sequences, no communication.  The RNG key of the
+  Flash sampler contains the batch index (flash_style_fused_santa_fixed_tile_budgets/
+  santa_cuda_kernel.cu:281), so each rank passes its first global batch index as ``batch_offset``
+  and the union of the ranks' outputs equals the single-GPU call bit for bit.
+* ``seq_sharded_flash_decode``: ONE very long sequence (or batch of them) whose KV cache is split
+  along the sequence.  Each rank samples inside its own shard with the GLOBAL tile index and the
+  GLOBAL per-tile budget, producing an unnormalised partial per head; one all-gather of
+  ``[B,H,130]`` fp32 per rank (16.6 KB for 32 heads) follows, then every rank combines locally.
+  The reference has no multi-device path; the combine is its finalize step
+  (santa_cuda_kernel.cu:386-470) over the union of the shards' tiles.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import capi, ops
+
+
+def shard_plan(L_total: int, world: int, S: int, block_n: int = 0):
+    """Tile-aligned split of a length-``L_total`` sequence over ``world`` ranks.
+    Returns (block_n, T_c_global, S_per_tile_global, [(row0, row1, tile0)] per rank)."""
+    bn = capi.block_n_rule(L_total, block_n)
+    T_c, spt = capi.flash_budget(L_total, bn, S)
+    base, extra = divmod(T_c, world)
+    plan, t0 = [], 0
+    for r in range(world):
+        nt = base + (1 if r < extra else 0)
+        row0, row1 = t0 * bn, min(L_total, (t0 + nt) * bn)
+        plan.append((row0, row1, t0))
+        t0 += nt
+    return bn, T_c, spt, plan
+
+
+def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0, group=None,
+                             gather_buf: Optional[torch.Tensor] = None):
+    """q [B,H,128] (replicated), K_shard/V_shard [B,L_r,KVH,128]: this rank's rows of the cache, as
+    given by ``shard_plan``.  Returns (out [B,H,128], m_star [B,H]) on every rank."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    bn, T_c, spt, plan = shard_plan(L_total, world, S, block_n)
+    row0, row1, tile0 = plan[rank]
+    if K_shard.size(1) < row1 - row0:
+        raise RuntimeError(f"rank {rank}: shard holds {K_shard.size(1)} rows, plan needs {row1 - row0}")
+    B, H = q.size(0), q.size(1)
+    if row1 > row0:
+        part, _, _ = ops.flash_decode(q, K_shard, V_shard, S, seed=seed, block_n=bn, valid_len=row1 - row0,
+                                      tile_offset=tile0, s_per_tile=spt, partial=True)
+    else:  # more ranks than tiles: an empty shard contributes weight zero
+        part = torch.zeros(B, H, 130, device=q.device, dtype=torch.float32)
+        part[..., 128] = float("-inf")
+    if world == 1:
+        return ops.lse_combine(part.unsqueeze(0), spt, q.dtype)
+    if gather_buf is None:
+        gather_buf = torch.empty((world,) + tuple(part.shape), device=q.device, dtype=torch.float32)
+    dist.all_gather_into_tensor(gather_buf, part, group=group)
+    return ops.lse_combine(gather_buf, spt, q.dtype)
+
+
+def batch_sharded_flash_decode(q_local, K_local, V_local, S, seed, batch_offset, **kw):
+    """This rank's slice of a batch; ``batch_offset`` is the global index of its first sequence."""
+    return ops.flash_decode(q_local, K_local, V_local, S, seed=seed, batch_offset=batch_offset, **kw)
+
+
+def merge_partials_reference(parts: torch.Tensor, S_per_tile: int):
+    """The combine rule in plain torch (any device): used by the CPU/gloo tests of the host logic."""
+    A, m, Z = parts[..., :128].double(), parts[..., 128].double(), parts[..., 129].double()
+    ms = m.max(0).values
+    w = torch.exp(m - ms)
+    w = torch.where(torch.isnan(w), torch.zeros_like(w), w)
+    Zs = (w * Z).sum(0)
+    out = (w[..., None] * A).sum(0) / (Zs * S_per_tile).clamp_min(1e-300)[..., None]
+    if S_per_tile <= 0:
+        out = out * 0
+    return out.float(), ms.float()
