@@ -27,7 +27,7 @@ constexpr int kStageBytes = kStageRows * kRowBytes;
 constexpr int kGroupWarps = 8;      // one warp per kv-head column of a column group
 constexpr int kMaxCtas = 256;       // upper bound on persistent CTAs (>= SM count)
 constexpr int kPartialStride = 132; // floats per (slot, warp, head): A[128], m, Z, pad
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;  // polls; with the sleep between polls this is seconds
 
 // status word values (0 = ok)
 enum : int {
@@ -113,9 +113,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it)
+// Between polls the warp sleeps `backoff_ns`, so that a waiting warp does not
+// take issue slots from the warps it is waiting for.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t backoff_ns = 32) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(backoff_ns);
+  }
   return false;
 }
 // One bulk asynchronous copy global -> shared, completion counted on `bar`.

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         const uint32_t buf = handoff & 1u;
         float* scorebuf = scorebufs + buf * (kScoreBytes / 4);
         // wait until the sampler has released this buffer (passes at once the first two times)
-        if (!dead && !mbar_wait_bounded(bar_empty + 8 * buf, ((handoff >> 1) & 1u) ^ 1u)) {
+        if (!dead && !mbar_wait_bounded(bar_empty + 8 * buf, ((handoff >> 1) & 1u) ^ 1u, 128)) {
           dead = true;
           if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
@@ -117,8 +117,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
           }
           const unsigned char* st = ring.stage_ptr(ring.count);
-          score_rows8<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
-          score_rows8<TK>(st + 8 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 8) * kGH, lane);
+          if (!(p.tile_offset & (1 << 28))) score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
           if (issued < npieces && !dead) {
             ring.issue(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
             ++issued;
@@ -147,11 +146,12 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
         const uint32_t buf = handoff & 1u;
         float4* sb = reinterpret_cast<float4*>(scorebufs + buf * (kScoreBytes / 4));
-        if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u)) {
+        if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u, 256)) {
           dead = true;
           if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
 
+        if (p.tile_offset & (1 << 29)) { if (lane == 0) mbar_arrive(bar_empty + 8 * buf); continue; }
         float m[kGH], ell[kGH];
         tile_stats<NW>(sb, tile_len, lane, m, ell);
         const size_t bh0 = size_t(b) * p.H + h0;

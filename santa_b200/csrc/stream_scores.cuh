@@ -30,7 +30,7 @@
 namespace santa {
 
 constexpr int kRedStride = 36;                  // floats per row in the exchange buffer (bank-conflict free)
-constexpr int kRedFloats = 8 * kRedStride;      // 8 rows per exchange
+constexpr int kRedFloats = kStageRows * kRedStride;  // one exchange per staged piece
 
 // Query registers of one thread: qp[g][h][i] = (q[g][slot 2h][i], q[g][slot 2h+1][i])
 // where slot s of this thread covers reference lane j + 8*(s ^ odd).
@@ -62,60 +62,85 @@ __device__ __forceinline__ void load_q(const TK* __restrict__ q_head0, float q_s
   }
 }
 
-// Scores of 8 consecutive staged rows.  `rows` points at the first row in the
-// staging buffer, `red` at this warp's exchange buffer (kRedFloats floats) and
-// `score_out` at 32 floats laid out [row][head]; lane l writes element l.
-// Rows that were not staged produce garbage the caller masks.
-template <typename TK>
-__device__ __forceinline__ void score_rows8(const unsigned char* __restrict__ rows, const QRegs& Q,
-                                            float* __restrict__ red, float* __restrict__ score_out, int lane) {
+// Raw K words of one thread for one step of four rows (its four 8-byte slots).
+struct KRaw {
+  uint2 w[4];
+};
+
+__device__ __forceinline__ void load_k4(const unsigned char* __restrict__ rows, int step, int lane, KRaw& k) {
   const int j = lane & 7;
   const int rr = lane >> 3;
   const int odd = rr & 1;
+  const unsigned char* rp = rows + (4 * step + rr) * kRowBytes + j * 8;
+  k.w[0] = *reinterpret_cast<const uint2*>(rp + odd * 64);
+  k.w[1] = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64);
+  k.w[2] = *reinterpret_cast<const uint2*>(rp + odd * 64 + 128);
+  k.w[3] = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64 + 128);
+}
+
+// b_j of the thread's row for the four heads, written to the exchange buffer.
+template <typename TK>
+__device__ __forceinline__ void partial_rows4(const KRaw& k, const QRegs& Q, float* __restrict__ red, int step,
+                                              int lane) {
+  const int j = lane & 7;
+  const int rr = lane >> 3;
+  const float2 k0a = Store16<TK>::unpack(k.w[0].x), k0b = Store16<TK>::unpack(k.w[0].y);
+  const float2 k1a = Store16<TK>::unpack(k.w[1].x), k1b = Store16<TK>::unpack(k.w[1].y);
+  const float2 k2a = Store16<TK>::unpack(k.w[2].x), k2b = Store16<TK>::unpack(k.w[2].y);
+  const float2 k3a = Store16<TK>::unpack(k.w[3].x), k3b = Store16<TK>::unpack(k.w[3].y);
+  float2 kp[2][4];
+  kp[0][0] = make_float2(k0a.x, k1a.x);
+  kp[0][1] = make_float2(k0a.y, k1a.y);
+  kp[0][2] = make_float2(k0b.x, k1b.x);
+  kp[0][3] = make_float2(k0b.y, k1b.y);
+  kp[1][0] = make_float2(k2a.x, k3a.x);
+  kp[1][1] = make_float2(k2a.y, k3a.y);
+  kp[1][2] = make_float2(k2b.x, k3b.x);
+  kp[1][3] = make_float2(k2b.y, k3b.y);
+  float b[kGH];
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const unsigned char* rp = rows + (4 * half + rr) * kRowBytes + j * 8;
-    const uint2 w0 = *reinterpret_cast<const uint2*>(rp + odd * 64);
-    const uint2 w1 = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64);
-    const uint2 w2 = *reinterpret_cast<const uint2*>(rp + odd * 64 + 128);
-    const uint2 w3 = *reinterpret_cast<const uint2*>(rp + (odd ^ 1) * 64 + 128);
-    const float2 k0a = Store16<TK>::unpack(w0.x), k0b = Store16<TK>::unpack(w0.y);
-    const float2 k1a = Store16<TK>::unpack(w1.x), k1b = Store16<TK>::unpack(w1.y);
-    const float2 k2a = Store16<TK>::unpack(w2.x), k2b = Store16<TK>::unpack(w2.y);
-    const float2 k3a = Store16<TK>::unpack(w3.x), k3b = Store16<TK>::unpack(w3.y);
-    float2 kp[2][4];
-    kp[0][0] = make_float2(k0a.x, k1a.x);
-    kp[0][1] = make_float2(k0a.y, k1a.y);
-    kp[0][2] = make_float2(k0b.x, k1b.x);
-    kp[0][3] = make_float2(k0b.y, k1b.y);
-    kp[1][0] = make_float2(k2a.x, k3a.x);
-    kp[1][1] = make_float2(k2a.y, k3a.y);
-    kp[1][2] = make_float2(k2b.x, k3b.x);
-    kp[1][3] = make_float2(k2b.y, k3b.y);
-    float b[kGH];
+  for (int g = 0; g < kGH; ++g) {
+    float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int g = 0; g < kGH; ++g) {
-      float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        a01 = __ffma2_rn(Q.qp[g][0][i], kp[0][i], a01);
-        a23 = __ffma2_rn(Q.qp[g][1][i], kp[1][i], a23);
-      }
-      const float2 t = __fadd2_rn(a01, a23);  // (a_j, a_{j+8}) in either order
-      b[g] = __fadd_rn(t.x, t.y);             // b_j
+    for (int i = 0; i < 4; ++i) {
+      a01 = __ffma2_rn(Q.qp[g][0][i], kp[0][i], a01);
+      a23 = __ffma2_rn(Q.qp[g][1][i], kp[1][i], a23);
     }
-    *reinterpret_cast<float4*>(red + (4 * half + rr) * kRedStride + 4 * j) = make_float4(b[0], b[1], b[2], b[3]);
+    const float2 t = __fadd2_rn(a01, a23);  // (a_j, a_{j+8}) in either order
+    b[g] = __fadd_rn(t.x, t.y);             // b_j
   }
+  *reinterpret_cast<float4*>(red + (4 * step + rr) * kRedStride + 4 * j) = make_float4(b[0], b[1], b[2], b[3]);
+}
+
+// Scores of the 16 rows of one staged piece.  `rows` points at the piece in the
+// staging buffer, `red` at this slot's exchange buffer (kRedFloats floats) and
+// `score_out` at 64 floats laid out [row][head].  The K words of the next
+// four-row step are fetched while the current step is multiplied, and a single
+// exchange finishes all 16 rows.  Rows that were not staged produce garbage
+// the caller masks.
+template <typename TK>
+__device__ __forceinline__ void score_rows16(const unsigned char* __restrict__ rows, const QRegs& Q,
+                                             float* __restrict__ red, float* __restrict__ score_out, int lane) {
+  KRaw k0, k1;
+  load_k4(rows, 0, lane, k0);
+  load_k4(rows, 1, lane, k1);
+  partial_rows4<TK>(k0, Q, red, 0, lane);
+  load_k4(rows, 2, lane, k0);
+  partial_rows4<TK>(k1, Q, red, 1, lane);
+  load_k4(rows, 3, lane, k1);
+  partial_rows4<TK>(k0, Q, red, 2, lane);
+  partial_rows4<TK>(k1, Q, red, 3, lane);
   __syncwarp();
-  {
-    const float* rd = red + (lane >> 2) * kRedStride + (lane & 3);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float* rd = red + (8 * h + (lane >> 2)) * kRedStride + (lane & 3);
     const float c0 = __fadd_rn(rd[0], rd[16]);
     const float c1 = __fadd_rn(rd[4], rd[20]);
     const float c2 = __fadd_rn(rd[8], rd[24]);
     const float c3 = __fadd_rn(rd[12], rd[28]);
     const float d0 = __fadd_rn(c0, c2);
     const float d1 = __fadd_rn(c1, c3);
-    score_out[lane] = __fadd_rn(d0, d1);
+    score_out[32 * h + lane] = __fadd_rn(d0, d1);
   }
   __syncwarp();
 }

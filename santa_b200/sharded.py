@@ -57,7 +57,8 @@ def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0
         return ops.lse_combine(part.unsqueeze(0), spt, q.dtype)
     if gather_buf is None:
         gather_buf = torch.empty((world,) + tuple(part.shape), device=q.device, dtype=torch.float32)
-    dist.all_gather_into_tensor(gather_buf, part, group=group)
+    # concatenated layout ([world*B,H,130]) is accepted by every backend
+    dist.all_gather_into_tensor(gather_buf.view(world * part.size(0), *part.shape[1:]), part, group=group)
     return ops.lse_combine(gather_buf, spt, q.dtype)
 
 
