@@ -126,6 +126,30 @@ SANTA_API int santa_flash_decode(const void* q, const void* K, const void* V, in
  * arrived, 2 = a score buffer was never handed over: the result is invalid).  Read it after synchronising the stream. */
 SANTA_API int32_t* santa_workspace_status(void* workspace);
 
+/*
+ * The same decode as santa_flash_decode for callers that cannot hand over a workspace: inference
+ * servers that give all free device memory to their KV-cache pool at start-up and forbid any
+ * allocation on the decode path (cudaMalloc stalls the whole device and may fail once memory is
+ * fragmented), and plain C / cgo hosts that have no device allocator of their own.  The scratch
+ * lives in a fixed SANTA_NOALLOC_SCRATCH_BYTES array inside the library (every GPU that loads the
+ * library holds it until the process exits); the entry point calls no cudaMalloc, cudaFree or any
+ * allocating routine.  This entry point has no counterpart in the reference.
+ *
+ * Arguments, results and error codes are those of santa_flash_decode without the workspace pair.
+ * A problem whose scratch need (santa_flash_workspace_bytes) exceeds SANTA_NOALLOC_SCRATCH_BYTES is
+ * rejected with SANTA_E_TOO_LARGE before anything is launched; with 8 kv-heads that is roughly
+ * more than 100 sequences per call.
+ *
+ * The first call on a device looks up the device address of the array (with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array: the
+ * entry point clears the part that must start at zero on `stream` before launching, and two calls
+ * whose kernels may overlap on the GPU (different streams, no ordering) race on it -- order them.
+ */
+#define SANTA_NOALLOC_SCRATCH_BYTES (4u << 20)
+SANTA_API int santa_flash_decode_noalloc(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH,
+                               int D, int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
+                               float* m_star, int32_t* vrows, const santa_flash_ext* ext, void* stream);
+
 /* ---- Prop decode ----------------------------------------------------------- */
 
 typedef struct santa_prop_ext {

@@ -75,6 +75,7 @@ EXPORTS = (
     "santa_prop_workspace_bytes",
     "santa_prop_decode",
     "santa_lse_combine",
+    "santa_flash_decode_noalloc",
 )
 
 
@@ -119,6 +120,9 @@ def lib() -> C.CDLL:
             C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
             C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
         ]
+    if hasattr(L, "santa_flash_decode_noalloc"):
+        L.santa_flash_decode_noalloc.restype = C.c_int
+        L.santa_flash_decode_noalloc.argtypes = L.santa_flash_decode.argtypes[:16] + [C.POINTER(FlashExt), C.c_void_p]
     if hasattr(L, "santa_lse_combine"):
         L.santa_lse_combine.restype = C.c_int
         L.santa_lse_combine.argtypes = [

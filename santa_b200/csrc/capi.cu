@@ -348,4 +348,35 @@ int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_til
   return SANTA_OK;
 }
 
+// ---- no-allocation variant of the Flash decode ---------------------------------------------
+// Scratch for callers that cannot provide a workspace.  In host code this name is only a
+// stand-in for the device array: its device address comes from cudaGetSymbolAddress, once per
+// device, and is what the kernels receive.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SANTA_NOALLOC_SCRATCH_BYTES];
+
+int santa_flash_decode_noalloc(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
+                               int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
+                               float* m_star, int32_t* vrows, const santa_flash_ext* ext, void* stream) {
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return SANTA_E_ARG;
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);  // set-up: first call on this device
+    if (e != cudaSuccess) return cuda_fail(e);
+    scratch_of_device[dev] = ptr;
+  }
+  void* scratch = scratch_of_device[dev];
+  // sizes beyond the fixed array are refused; argument errors are left to the common path below
+  const size_t need = santa_flash_workspace_bytes(B, KVH, L_valid, block_n);
+  if (need > size_t(SANTA_NOALLOC_SCRATCH_BYTES)) return SANTA_E_TOO_LARGE;
+  // the array keeps the previous call's contents; only the status word has to start at zero
+  e = cudaMemsetAsync(scratch, 0, 256, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return santa_flash_decode(q, K, V, dtype, B, H, KVH, D, L_valid, L_storage, S, seed, block_n, out, m_star, vrows,
+                            scratch, size_t(SANTA_NOALLOC_SCRATCH_BYTES), ext, stream);
+}
+
 }  // extern "C"
