@@ -22,7 +22,7 @@ constexpr int kD = 128;             // head_dim of the vectorised kernels
 constexpr int kGH = 4;              // query heads per kv-head of the vectorised kernels
 constexpr int kRowBytes = kD * 2;   // one K/V row of one kv-head
 constexpr int kChunkRows = 32;      // rows per sampler chunk (one row per lane, as in the reference scan)
-constexpr int kStageRows = 16;      // rows staged per pipeline slot
+constexpr int kStageRows = 32;      // rows staged per pipeline slot
 constexpr int kStageBytes = kStageRows * kRowBytes;
 constexpr int kGroupWarps = 8;      // one warp per kv-head column of a column group
 constexpr int kMaxCtas = 256;       // upper bound on persistent CTAs (>= SM count)

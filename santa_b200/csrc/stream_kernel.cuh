@@ -26,7 +26,7 @@ namespace santa {
 constexpr int kModeFlash = 0;
 constexpr int kModePropPass1 = 1;
 
-constexpr int kStreamStages = 4;
+constexpr int kStreamStages = 2;
 constexpr int kMaxTileRows = 256;
 constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // one score buffer: scores, then u, then the emit list
 constexpr int kSlotSmem = kStreamStages * kStageBytes + 2 * kScoreBytes + kRedFloats * 4;
@@ -117,7 +117,10 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
           }
           const unsigned char* st = ring.stage_ptr(ring.count);
-          if (!(p.tile_offset & (1 << 28))) score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+          if (!(p.tile_offset & (1 << 28))) {
+            score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+            score_rows16<TK>(st + 16 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 16) * kGH, lane);
+          }
           if (issued < npieces && !dead) {
             ring.issue(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
             ++issued;

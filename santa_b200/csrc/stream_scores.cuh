@@ -30,7 +30,7 @@
 namespace santa {
 
 constexpr int kRedStride = 36;                  // floats per row in the exchange buffer (bank-conflict free)
-constexpr int kRedFloats = kStageRows * kRedStride;  // one exchange per staged piece
+constexpr int kRedFloats = 16 * kRedStride;         // one exchange per 16 rows
 
 // Query registers of one thread: qp[g][h][i] = (q[g][slot 2h][i], q[g][slot 2h+1][i])
 // where slot s of this thread covers reference lane j + 8*(s ^ odd).
