@@ -219,6 +219,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-seq-sharded", action="store_true", help="skip the 512k-context sequence-sharded extra")
+    ap.add_argument("--no-prop", action="store_true", help="skip the santa_prop ragged-batch extra")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -315,6 +316,38 @@ def main():
                             "(partial, m, Z) + local combine inside the timed step",
                 "steps_per_s": n3 / t3, "ms_per_step": t3 / n3 * 1e3, "k_gbs_total": kb / (t3 / n3) / 1e9,
                 "scaling": "strong"}
+
+    # ---- extra: santa_prop on the ragged batch (BASELINE configs[2]), scalar entry point per sequence -----
+    if not args.no_prop:
+        import santa_prop_batch_cuda as prop_mod
+
+        lengths = torch.randint(8192, 65537, (16,), generator=torch.Generator().manual_seed(7)).tolist()
+        qp2, K2, V2 = make_inputs(dev, SEED + 2 + rank, batch=1, length=sum(lengths))
+        offs = [0]
+        for n in lengths:
+            offs.append(offs[-1] + n)
+        Ks = [K2[0, offs[i]:offs[i + 1]] for i in range(16)]   # contiguous [L_b, KVH, D] views, as the adapter passes
+        Vs = [V2[0, offs[i]:offs[i + 1]] for i in range(16)]
+        vr2 = sum(int(prop_mod.decode_systematic_scalar(qp2[0][0], Ks[i], Vs[i], S, seed=SEED, want_vrows=True)[2]
+                      .sum().item()) for i in range(16))
+
+        def prop_step(i):
+            q = qp2[i % QPOOL][0]
+            for b in range(16):
+                prop_mod.decode_systematic_scalar(q, Ks[b], Vs[b], S, seed=SEED, want_vrows=False)
+
+        n2 = max(20, steps // 10)
+        t2 = timed_loop(prop_step, n2, 3, world, dev)
+        if rank == 0:
+            pb = sum(lengths) * KVH * D * 2 + vr2 * D * 2 + 16 * (2 * H * D * 2 + H * 4)
+            line["prop_ragged_config2"] = {
+                "workload": "santa_prop B=16 ragged L in [8192,65536] (seed-7 draw, sum 562962) S=256, one "
+                            "decode_systematic_scalar call per sequence (4 kernels each)",
+                "steps_per_s": world * n2 / t2, "ms_per_step": t2 / n2 * 1e3,
+                "sampled_kv_gbs_per_gpu": pb / (t2 / n2) / 1e9, "algorithmic_bytes_per_step": pb,
+                "scaling": "weak"}
+        del qp2, K2, V2, Ks, Vs
+        torch.cuda.empty_cache()
 
     if rank == 0:
         line["cpu_baseline"] = cpu_dense_baseline() if world == 1 else None

@@ -34,10 +34,15 @@ __device__ __forceinline__ void tile_stats(float4* sb, int tile_len, int lane, f
       m[3] = fmaxf(m[3], s.w);
     }
   }
+  // shuffles of the four heads are issued back to back so that their latencies overlap
 #pragma unroll
-  for (int g = 0; g < kGH; ++g)
+  for (int off = 16; off > 0; off >>= 1) {
+    float o[kGH];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) m[g] = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], off));
+    for (int g = 0; g < kGH; ++g) o[g] = __shfl_xor_sync(0xffffffffu, m[g], off);
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) m[g] = fmaxf(m[g], o[g]);
+  }
 
   float V0[kGH], V1[kGH];
 #pragma unroll
@@ -66,25 +71,35 @@ __device__ __forceinline__ void tile_stats(float4* sb, int tile_len, int lane, f
       V0[3] = __fadd_rn(V0[3], u.w);
     }
   }
+  // per-head value order (reference): 8-row tree (xor 4,2,1), then the reference warps in order
+  // (lane groups 0,8,16,24 of the even half, then of the odd half when the block has 8 warps).
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) {
+    float o0[kGH], o1[kGH];
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
+      o0[g] = __shfl_xor_sync(0xffffffffu, V0[g], off);
+      if (NH == 2) o1[g] = __shfl_xor_sync(0xffffffffu, V1[g], off);
+    }
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
+      V0[g] = __fadd_rn(V0[g], o0[g]);
+      if (NH == 2) V1[g] = __fadd_rn(V1[g], o1[g]);
+    }
+  }
+  float w[2 * 4][kGH];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
+      w[k][g] = __shfl_sync(0xffffffffu, V0[g], 8 * k);
+      if (NH == 2) w[4 + k][g] = __shfl_sync(0xffffffffu, V1[g], 8 * k);
+    }
 #pragma unroll
   for (int g = 0; g < kGH; ++g) {
-    float x0 = V0[g], x1 = V1[g];
-    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 4));
-    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 2));
-    x0 = __fadd_rn(x0, __shfl_xor_sync(0xffffffffu, x0, 1));
-    float e = __shfl_sync(0xffffffffu, x0, 0);
-    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 8));
-    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 16));
-    e = __fadd_rn(e, __shfl_sync(0xffffffffu, x0, 24));
-    if (NH == 2) {
-      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 4));
-      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 2));
-      x1 = __fadd_rn(x1, __shfl_xor_sync(0xffffffffu, x1, 1));
-      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 0));
-      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 8));
-      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 16));
-      e = __fadd_rn(e, __shfl_sync(0xffffffffu, x1, 24));
-    }
+    float e = w[0][g];
+#pragma unroll
+    for (int k = 1; k < 4 * NH; ++k) e = __fadd_rn(e, w[k][g]);
     ell[g] = e;
   }
 }
@@ -122,28 +137,42 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
     const float4 u4 = sb[ch * kChunkRows + lane];
     const float uu[kGH] = {u4.x, u4.y, u4.z, u4.w};
     int c[kGH];
+    float xv[kGH], res[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
       const float u16v = Store16<TK>::round(uu[g]);
-      const float xv = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
-      float res = xv;
+      xv[g] = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
+      res[g] = xv[g];
+    }
+    // inclusive Hillis-Steele scan; the four heads' shuffles are issued back to back
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float nb = __shfl_up_sync(0xffffffffu, res, off);
-        if (lane >= off) res = __fadd_rn(res, nb);
+    for (int off = 1; off < 32; off <<= 1) {
+      float nb[kGH];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) nb[g] = __shfl_up_sync(0xffffffffu, res[g], off);
+      if (lane >= off) {
+#pragma unroll
+        for (int g = 0; g < kGH; ++g) res[g] = __fadd_rn(res[g], nb[g]);
       }
-      const float pre = __fsub_rn(res, xv);
+    }
+    float tot[kGH];
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
+      const float pre = __fsub_rn(res[g], xv[g]);
+      tot[g] = __fadd_rn(pre, xv[g]);
       const float pre_g = __fadd_rn(carry[g], pre);
-      const float cum_g = __fadd_rn(pre_g, xv);
-      const float f_prev = floorf(__fadd_rn(a0[g], pre_g));
-      const float f_curr = floorf(__fadd_rn(a0[g], cum_g));
-      int cc = (int)__fsub_rn(f_curr, f_prev);
+      const float cum_g = __fadd_rn(pre_g, xv[g]);
+      // int(floorf(b) - floorf(a)) == floor-to-int(b) - floor-to-int(a): both floors are exact
+      // integers far below 2^24 (they are bounded by the tile budget plus one)
+      int cc = __float2int_rd(__fadd_rn(a0[g], cum_g)) - __float2int_rd(__fadd_rn(a0[g], pre_g));
       cc = cc < 0 ? 0 : cc;
       cc = cc > 32767 ? 32767 : cc;
       c[g] = valid ? cc : 0;
-      const float chunk_total = __shfl_sync(0xffffffffu, __fadd_rn(pre, xv), last_lane);
-      carry[g] = __fadd_rn(carry[g], chunk_total);
     }
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) tot[g] = __shfl_sync(0xffffffffu, tot[g], last_lane);
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) carry[g] = __fadd_rn(carry[g], tot[g]);
     if (tr.counts != nullptr && valid) {
 #pragma unroll
       for (int g = 0; g < kGH; ++g) {

@@ -117,10 +117,8 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
           }
           const unsigned char* st = ring.stage_ptr(ring.count);
-          if (!(p.tile_offset & (1 << 28))) {
-            score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
-            score_rows16<TK>(st + 16 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 16) * kGH, lane);
-          }
+          score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+          score_rows16<TK>(st + 16 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 16) * kGH, lane);
           if (issued < npieces && !dead) {
             ring.issue(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
             ++issued;
@@ -154,7 +152,6 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
 
-        if (p.tile_offset & (1 << 29)) { if (lane == 0) mbar_arrive(bar_empty + 8 * buf); continue; }
         float m[kGH], ell[kGH];
         tile_stats<NW>(sb, tile_len, lane, m, ell);
         const size_t bh0 = size_t(b) * p.H + h0;

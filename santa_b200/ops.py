@@ -132,7 +132,8 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
                             torch.empty((B, H, T_c), **fopt))
             ext.invdel = tr.invdel.data_ptr()
             ext.m_tiles, ext.ell_tiles = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr()
-            ext.u16, ext.counts, ext.rowmask = tr.u16.data_ptr(), tr.counts.data_ptr(), tr.rowmask.data_ptr()
+            if trace != "tiles":  # trace="tiles": per-tile statistics only, no per-row tables
+                ext.u16, ext.counts, ext.rowmask = tr.u16.data_ptr(), tr.counts.data_ptr(), tr.rowmask.data_ptr()
         rc = lib.santa_flash_decode(
             q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), _dtype_code(q), B, H, KVH, D, L, L_storage,
             int(S), int(seed) & (2**64 - 1), bn,
