@@ -74,28 +74,31 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Deal (column group, tile) items to the 8 column slots of each persistent CTA.
-// Narrower column groups give more, smaller items; the widest group whose
-// per-slot item count is minimal wins (wide groups fetch whole token rows).
+// Narrower column groups give more, smaller items.  The width that minimises
+// the busiest SM's load (in column-tiles) wins; on a tie the widest does, since
+// wide groups fetch whole token rows together.
 santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid) {
   santa::WorkSplit best{};
-  long long best_per = -1;
+  long long best_load = -1;
   for (int gw = santa::kGroupWarps; gw >= 1; gw >>= 1) {
     const long long ncg = (ncol + gw - 1) / gw;
     const long long items = ncg * T_c;
     const long long slots = (long long)sms * (santa::kGroupWarps / gw);
     const long long nvg = items < slots ? items : slots;
-    const long long per = (items + nvg - 1) / nvg;
-    if (best_per < 0 || per < best_per) {
-      best_per = per;
+    const long long per = (items + nvg - 1) / nvg;           // items of the busiest virtual group
+    const long long ctas = nvg < sms ? nvg : sms;
+    const long long groups_per_cta = (nvg + ctas - 1) / ctas;  // virtual groups on the busiest CTA
+    const long long load = per * groups_per_cta * gw;
+    if (best_load < 0 || load < best_load) {
+      best_load = load;
       best.gw = gw;
       best.nvg = int(nvg);
       best.T_c = T_c;
       best.ncol = ncol;
       best.items = items;
+      *grid = int(ctas);
     }
   }
-  const int spc = santa::kGroupWarps / best.gw;
-  *grid = (best.nvg + spc - 1) / spc;
   return best;
 }
 

@@ -239,18 +239,19 @@ __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const 
 
 // ---------------------------------------------------------------- work split over column slots
 // A CTA has kGroupWarps column slots.  With group width gw (a power of two
-// <= 8) the slots form 8/gw virtual groups of gw columns; virtual group
-// vg = cta*(8/gw) + slot/gw owns a contiguous balanced range of the
-// (column group, tile) items, column groups being gw consecutive columns.
+// <= 8) the slots form 8/gw slot groups of gw columns; slot group sg of CTA c
+// is virtual group vg = sg*ctas + c, which owns a contiguous balanced range
+// of the (column group, tile) items, column groups being gw consecutive columns.
 struct WarpWork {
   int vg, col_in_group;
   long long lo, hi;
 };
 
-__device__ __forceinline__ WarpWork warp_work(const WorkSplit& w, int cta, int slot) {
+__device__ __forceinline__ WarpWork warp_work(const WorkSplit& w, int cta, int ctas, int slot) {
   WarpWork r;
-  const int spc = kGroupWarps / w.gw;
-  r.vg = cta * spc + slot / w.gw;
+  // virtual groups are dealt round-robin to the CTAs, so that a problem with few groups still
+  // spreads over all SMs
+  r.vg = (slot / w.gw) * ctas + cta;
   r.col_in_group = slot % w.gw;
   if (r.vg < w.nvg) {
     r.lo = range_lo(r.vg, w.items, w.nvg);

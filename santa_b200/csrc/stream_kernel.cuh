@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
   const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
   const unsigned char* __restrict__ Vg = static_cast<const unsigned char*>(p.V);
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
-  const WarpWork ww = warp_work(p.ws, blockIdx.x, slot);
+  const WarpWork ww = warp_work(p.ws, blockIdx.x, gridDim.x, slot);
 
   bool dead = false;     // set when a wait ran out; the status word then says why
   uint32_t handoff = 0;  // tiles handed over so far on this slot (selects buffer and parity)
