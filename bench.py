@@ -360,8 +360,8 @@ def main():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from
-# the ncu capture summarised in profiles/stream_kernel_flash_config1.md (556.85 MB + 6.34 MB).
-TRAFFIC_BYTES_PER_LAUNCH = 563_184_128
+# the ncu capture summarised in profiles/stream_kernel_flash_config1.md (556.65 MB + 8.99 MB).
+TRAFFIC_BYTES_PER_LAUNCH = 565_636_864
 
 if __name__ == "__main__":
     main()
