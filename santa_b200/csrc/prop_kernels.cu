@@ -375,22 +375,26 @@ struct PropMergeParams {
   int* vrows;    // [KVH] or null
 };
 
-// One warp per (kv-head, head): adds the warps' partial sums in ascending order.
+// One CTA of 8 warps per (kv-head, head): warp w adds the partials v = first+w, first+w+8, ... in
+// ascending order, then the eight sums are added in warp order -- a fixed order, so repeated calls
+// give identical bits.
+constexpr int kMergeWarps = 8;
 template <typename TK>
-__global__ void __launch_bounds__(32) prop_merge_kernel(const PropMergeParams p) {
+__global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const PropMergeParams p) {
   cudaGridDependencySynchronize();
-  const int kv = blockIdx.x >> 2, g = blockIdx.x & 3, lane = threadIdx.x;
+  __shared__ float4 s_acc[kMergeWarps][32];
+  __shared__ int s_vr[kMergeWarps];
+  const int kv = blockIdx.x >> 2, g = blockIdx.x & 3, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int v_first = cta_of_item((long long)kv * p.T_c, p.ws.items, p.ws.nvg);
   const int v_last = cta_of_item((long long)(kv + 1) * p.T_c - 1, p.ws.items, p.ws.nvg);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int vr = 0;
-  for (int v0 = v_first; v0 <= v_last; v0 += 4) {
+  for (int v0 = v_first + w; v0 <= v_last; v0 += 4 * kMergeWarps) {
     float4 a[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (v0 + k <= v_last)
-        a[k] = __ldcg(reinterpret_cast<const float4*>(p.partials + (size_t(v0 + k + kv) * kGH + g) * kD) + lane);
+      const int v = v0 + k * kMergeWarps;
+      if (v <= v_last) a[k] = __ldcg(reinterpret_cast<const float4*>(p.partials + (size_t(v + kv) * kGH + g) * kD) + lane);
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -400,16 +404,33 @@ __global__ void __launch_bounds__(32) prop_merge_kernel(const PropMergeParams p)
       acc.w += a[k].w;
     }
   }
-  TK* op = static_cast<TK*>(p.out) + (size_t(kv) * kGH + g) * kD + 4 * lane;
-  uint2 wv;
-  wv.x = uint32_t(Store16<TK>::bits(acc.x * p.scale)) | (uint32_t(Store16<TK>::bits(acc.y * p.scale)) << 16);
-  wv.y = uint32_t(Store16<TK>::bits(acc.z * p.scale)) | (uint32_t(Store16<TK>::bits(acc.w * p.scale)) << 16);
-  *reinterpret_cast<uint2*>(op) = wv;
-  if (g == 0 && p.vrows != nullptr) {
-    for (int v = v_first + lane; v <= v_last; v += 32) vr += __ldcg(p.partial_vrows + v + kv);
+  int vr = 0;
+  if (g == 0 && p.vrows != nullptr)
+    for (int v = v_first + threadIdx.x; v <= v_last; v += kMergeWarps * 32) vr += __ldcg(p.partial_vrows + v + kv);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) vr += __shfl_xor_sync(0xffffffffu, vr, off);
-    if (lane == 0) p.vrows[kv] = vr;
+  for (int off = 16; off > 0; off >>= 1) vr += __shfl_xor_sync(0xffffffffu, vr, off);
+  s_acc[w][lane] = acc;
+  if (lane == 0) s_vr[w] = vr;
+  __syncthreads();
+  if (w == 0) {
+#pragma unroll
+    for (int k = 1; k < kMergeWarps; ++k) {
+      const float4 b = s_acc[k][lane];
+      acc.x += b.x;
+      acc.y += b.y;
+      acc.z += b.z;
+      acc.w += b.w;
+    }
+    TK* op = static_cast<TK*>(p.out) + (size_t(kv) * kGH + g) * kD + 4 * lane;
+    uint2 wv;
+    wv.x = uint32_t(Store16<TK>::bits(acc.x * p.scale)) | (uint32_t(Store16<TK>::bits(acc.y * p.scale)) << 16);
+    wv.y = uint32_t(Store16<TK>::bits(acc.z * p.scale)) | (uint32_t(Store16<TK>::bits(acc.w * p.scale)) << 16);
+    *reinterpret_cast<uint2*>(op) = wv;
+    if (g == 0 && p.vrows != nullptr && lane == 0) {
+      int t = 0;
+      for (int k = 0; k < kMergeWarps; ++k) t += s_vr[k];
+      p.vrows[kv] = t;
+    }
   }
 }
 
@@ -495,7 +516,7 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   pm.scale = (p.S > 0) ? (1.0f / (float)p.S) : 0.0f;
   pm.out = p.out;
   pm.vrows = p.vrows;
-  return launch_dependent(prop_merge_kernel<TK>, dim3(KVH * kGH), dim3(32), 0, stream, pm);
+  return launch_dependent(prop_merge_kernel<TK>, dim3(KVH * kGH), dim3(kMergeWarps * 32), 0, stream, pm);
 }
 
 cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t stream) {

@@ -199,28 +199,27 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
 // Sparse sum of c*V over the emit list, ascending rows, fp32 fma per head
 // (flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:347-379,
 // santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:843-857).
-// Lane l accumulates dims 4l..4l+3 of each head; four rows are in flight.
+// Lane l accumulates dims 4l..4l+3 of each head; eight rows are in flight.
 // `vrow0` points at the V row of the tile's first row for this kv-head.
 template <typename TK>
 __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const unsigned char* __restrict__ vrow0,
                                             size_t row_stride, int lane, float (&o)[kGH][4]) {
+  constexpr int kInFlight = 8;
   const uint4* emit = reinterpret_cast<const uint4*>(sb);
 #pragma unroll 1
-  for (int i0 = 0; i0 < n_emit; i0 += 4) {
-    uint4 en[4];
-    uint2 vv[4];
+  for (int i0 = 0; i0 < n_emit; i0 += kInFlight) {
+    uint2 vv[kInFlight];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (i0 + k < n_emit) {
-        en[k] = emit[i0 + k];
-        vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(en[k].z) * row_stride) + lane);
-      }
+    for (int k = 0; k < kInFlight; ++k) {
+      if (i0 + k < n_emit)
+        vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z) * row_stride) + lane);
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < kInFlight; ++k) {
       if (i0 + k < n_emit) {
+        const uint4 en = emit[i0 + k];
         const float2 va = Store16<TK>::unpack(vv[k].x), vb = Store16<TK>::unpack(vv[k].y);
-        const int cg4[kGH] = {int(en[k].x & 0xffffu), int(en[k].x >> 16), int(en[k].y & 0xffffu), int(en[k].y >> 16)};
+        const int cg4[kGH] = {int(en.x & 0xffffu), int(en.x >> 16), int(en.y & 0xffffu), int(en.y >> 16)};
 #pragma unroll
         for (int g = 0; g < kGH; ++g) {
           if (cg4[g] != 0) {
