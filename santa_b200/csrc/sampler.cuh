@@ -24,7 +24,7 @@ __device__ __forceinline__ void tile_stats(float4* sb, int tile_len, int lane, f
   const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
 #pragma unroll
   for (int g = 0; g < kGH; ++g) m[g] = -CUDART_INF_F;
-#pragma unroll 1
+#pragma unroll 4
   for (int ch = 0; ch < nch; ++ch) {
     if (ch * kChunkRows + lane < tile_len) {
       const float4 s = sb[ch * kChunkRows + lane];
@@ -47,7 +47,7 @@ __device__ __forceinline__ void tile_stats(float4* sb, int tile_len, int lane, f
   float V0[kGH], V1[kGH];
 #pragma unroll
   for (int g = 0; g < kGH; ++g) V0[g] = V1[g] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
   for (int ch = 0; ch < nch; ++ch) {
     const bool valid = ch * kChunkRows + lane < tile_len;
     float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -129,68 +129,107 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
   for (int g = 0; g < kGH; ++g) carry[g] = 0.f;
   int n_emit = 0;
   uint4* emit = reinterpret_cast<uint4*>(sb);
+  // Two chunks (A = ch, B = ch+1) per iteration: their scans are independent, so the shuffles of
+  // the eight (chunk, head) chains are issued back to back and their latencies overlap.  Only the
+  // final additions of B need A's chunk total (the carried prefix).
 #pragma unroll 1
-  for (int ch = 0; ch < nch; ++ch) {
-    const int remain = tile_len - ch * kChunkRows;
-    const int last_lane = remain > 32 ? 31 : remain - 1;
-    const bool valid = lane < remain;
-    const float4 u4 = sb[ch * kChunkRows + lane];
-    const float uu[kGH] = {u4.x, u4.y, u4.z, u4.w};
-    int c[kGH];
-    float xv[kGH], res[kGH];
+  for (int ch = 0; ch < nch; ch += 2) {
+    const int remainA = tile_len - ch * kChunkRows;
+    const int remainB = remainA - kChunkRows;  // <= 0 when chunk B does not exist
+    const bool hasB = remainB > 0;
+    const int lastA = remainA > 32 ? 31 : remainA - 1;
+    const int lastB = remainB > 32 ? 31 : (hasB ? remainB - 1 : 0);
+    const bool validA = lane < remainA;
+    const bool validB = lane < remainB;
+    const float4 uA4 = sb[ch * kChunkRows + lane];
+    const float4 uB4 = hasB ? sb[(ch + 1) * kChunkRows + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float uA[kGH] = {uA4.x, uA4.y, uA4.z, uA4.w};
+    const float uB[kGH] = {uB4.x, uB4.y, uB4.z, uB4.w};
+    float xA[kGH], xB[kGH], rA[kGH], rB[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
-      const float u16v = Store16<TK>::round(uu[g]);
-      xv[g] = (valid && invdel[g] > 0.f) ? __fmul_rn(u16v, invdel[g]) : 0.f;
-      res[g] = xv[g];
+      xA[g] = (validA && invdel[g] > 0.f) ? __fmul_rn(Store16<TK>::round(uA[g]), invdel[g]) : 0.f;
+      xB[g] = (validB && invdel[g] > 0.f) ? __fmul_rn(Store16<TK>::round(uB[g]), invdel[g]) : 0.f;
+      rA[g] = xA[g];
+      rB[g] = xB[g];
     }
-    // inclusive Hillis-Steele scan; the four heads' shuffles are issued back to back
+    // inclusive Hillis-Steele scans (offsets 1,2,4,8,16)
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-      float nb[kGH];
+      float nA[kGH], nB[kGH];
 #pragma unroll
-      for (int g = 0; g < kGH; ++g) nb[g] = __shfl_up_sync(0xffffffffu, res[g], off);
+      for (int g = 0; g < kGH; ++g) {
+        nA[g] = __shfl_up_sync(0xffffffffu, rA[g], off);
+        nB[g] = __shfl_up_sync(0xffffffffu, rB[g], off);
+      }
       if (lane >= off) {
 #pragma unroll
-        for (int g = 0; g < kGH; ++g) res[g] = __fadd_rn(res[g], nb[g]);
+        for (int g = 0; g < kGH; ++g) {
+          rA[g] = __fadd_rn(rA[g], nA[g]);
+          rB[g] = __fadd_rn(rB[g], nB[g]);
+        }
       }
     }
-    float tot[kGH];
+    float preA[kGH], preB[kGH], totA[kGH], totB[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
-      const float pre = __fsub_rn(res[g], xv[g]);
-      tot[g] = __fadd_rn(pre, xv[g]);
-      const float pre_g = __fadd_rn(carry[g], pre);
-      const float cum_g = __fadd_rn(pre_g, xv[g]);
+      preA[g] = __fsub_rn(rA[g], xA[g]);
+      preB[g] = __fsub_rn(rB[g], xB[g]);
+      totA[g] = __shfl_sync(0xffffffffu, __fadd_rn(preA[g], xA[g]), lastA);
+      totB[g] = __shfl_sync(0xffffffffu, __fadd_rn(preB[g], xB[g]), lastB);
+    }
+    int cA[kGH], cB[kGH];
+#pragma unroll
+    for (int g = 0; g < kGH; ++g) {
       // int(floorf(b) - floorf(a)) == floor-to-int(b) - floor-to-int(a): both floors are exact
       // integers far below 2^24 (they are bounded by the tile budget plus one)
-      int cc = __float2int_rd(__fadd_rn(a0[g], cum_g)) - __float2int_rd(__fadd_rn(a0[g], pre_g));
-      cc = cc < 0 ? 0 : cc;
-      cc = cc > 32767 ? 32767 : cc;
-      c[g] = valid ? cc : 0;
+      const float carryB = __fadd_rn(carry[g], totA[g]);
+      const float pgA = __fadd_rn(carry[g], preA[g]);
+      const float cgA = __fadd_rn(pgA, xA[g]);
+      const float pgB = __fadd_rn(carryB, preB[g]);
+      const float cgB = __fadd_rn(pgB, xB[g]);
+      int a = __float2int_rd(__fadd_rn(a0[g], cgA)) - __float2int_rd(__fadd_rn(a0[g], pgA));
+      int b = __float2int_rd(__fadd_rn(a0[g], cgB)) - __float2int_rd(__fadd_rn(a0[g], pgB));
+      a = a < 0 ? 0 : (a > 32767 ? 32767 : a);
+      b = b < 0 ? 0 : (b > 32767 ? 32767 : b);
+      cA[g] = validA ? a : 0;
+      cB[g] = validB ? b : 0;
+      carry[g] = hasB ? __fadd_rn(carryB, totB[g]) : carryB;
     }
-#pragma unroll
-    for (int g = 0; g < kGH; ++g) tot[g] = __shfl_sync(0xffffffffu, tot[g], last_lane);
-#pragma unroll
-    for (int g = 0; g < kGH; ++g) carry[g] = __fadd_rn(carry[g], tot[g]);
-    if (tr.counts != nullptr && valid) {
+    if (tr.counts != nullptr) {
 #pragma unroll
       for (int g = 0; g < kGH; ++g) {
         const size_t o = size_t(g) * tr.head_stride + ch * kChunkRows + lane;
-        if (tr.u16 != nullptr) tr.u16[o] = Store16<TK>::bits(uu[g]);
-        tr.counts[o] = (int16_t)c[g];
+        if (validA) {
+          if (tr.u16 != nullptr) tr.u16[o] = Store16<TK>::bits(uA[g]);
+          tr.counts[o] = (int16_t)cA[g];
+        }
+        if (validB) {
+          if (tr.u16 != nullptr) tr.u16[o + kChunkRows] = Store16<TK>::bits(uB[g]);
+          tr.counts[o + kChunkRows] = (int16_t)cB[g];
+        }
       }
     }
-    const bool flag = (c[0] + c[1] + c[2] + c[3]) > 0;
-    const uint32_t mask = __ballot_sync(0xffffffffu, flag);
+    // compaction in ascending row order: A's rows, then B's
+    const bool flagA = (cA[0] + cA[1] + cA[2] + cA[3]) > 0;
+    const bool flagB = (cB[0] + cB[1] + cB[2] + cB[3]) > 0;
+    const uint32_t maskA = __ballot_sync(0xffffffffu, flagA);
+    const uint32_t maskB = __ballot_sync(0xffffffffu, flagB);
     __syncwarp();
-    if (flag) {
-      const int pos = n_emit + __popc(mask & ((1u << lane) - 1u));
-      emit[pos] = make_uint4((uint32_t)c[0] | ((uint32_t)c[1] << 16), (uint32_t)c[2] | ((uint32_t)c[3] << 16),
-                             (uint32_t)(ch * kChunkRows + lane), 0u);
+    const uint32_t lt = (1u << lane) - 1u;
+    if (flagA) {
+      emit[n_emit + __popc(maskA & lt)] =
+          make_uint4((uint32_t)cA[0] | ((uint32_t)cA[1] << 16), (uint32_t)cA[2] | ((uint32_t)cA[3] << 16),
+                     (uint32_t)(ch * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
     }
-    n_emit += __popc(mask);
+    if (flagB) {
+      emit[n_emit + __popc(maskA) + __popc(maskB & lt)] =
+          make_uint4((uint32_t)cB[0] | ((uint32_t)cB[1] << 16), (uint32_t)cB[2] | ((uint32_t)cB[3] << 16),
+                     (uint32_t)((ch + 1) * kChunkRows + lane), 0u);
+      if (tr.rowmask != nullptr) tr.rowmask[(ch + 1) * kChunkRows + lane] = 1;
+    }
+    n_emit += __popc(maskA) + __popc(maskB);
   }
   __syncwarp();
   return n_emit;
