@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
   const uint32_t bar_full = smem_u32(bars + kStreamStages);       // [2]
   const uint32_t bar_empty = smem_u32(bars + kStreamStages + 2);  // [2]
 
+  if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tmK) : "memory");
   WarpRing<kStreamStages> ring;
   if (!is_sampler) {
     ring.init(sbase, bars, lane);
@@ -89,14 +90,14 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 
     if (active && !is_sampler) {
       // =========================== SCORE warp ===============================
-      QRegs Q;
-      load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
       const int row_base = t_lo * BN;
       const int row_end = (t_hi * BN < p.L_valid) ? t_hi * BN : p.L_valid;
       const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
-      int issued = 0;
+      int issued = 0;  // the K pieces do not depend on q: start them before fetching q
       for (; issued < kStreamStages && issued < npieces; ++issued)
         ring.issue(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
+      QRegs Q;
+      load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
 
 #pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t, ++handoff) {
@@ -194,10 +195,11 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 
         if (MODE == kModeFlash) {
           // systematic counts, compaction, sparse V sum, running merge
+          // the four heads' offsets are computed on lanes 0..3 in parallel and broadcast
+          const float a0_lane = u01_from_seed(p.seed, (p.batch_offset + b) * p.H + h0 + (lane & 3), p.tile_offset + t);
           float a0[kGH];
 #pragma unroll
-          for (int g = 0; g < kGH; ++g)
-            a0[g] = u01_from_seed(p.seed, (p.batch_offset + b) * p.H + h0 + g, p.tile_offset + t);
+          for (int g = 0; g < kGH; ++g) a0[g] = __shfl_sync(0xffffffffu, a0_lane, g);
           RowTrace tr;
           tr.head_stride = size_t(p.L_valid);
           tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.L_valid + n0 : nullptr;
