@@ -21,7 +21,7 @@ struct WorkSplit {
 
 // Streaming kernels: Flash decode and Prop's first pass.
 struct StreamParams {
-  CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,16,1}
+  CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,32,1}
   const void* q;    // [B,H,128]
   const void* V;    // [B,L_storage,KVH,128]
   int H, KVH;

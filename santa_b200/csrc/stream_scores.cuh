@@ -1,5 +1,5 @@
 // stream_scores.cuh -- the K-streaming front end shared by the Flash kernel and
-// Prop's first pass: a warp stages 16-row pieces of one kv-head's K rows in
+// Prop's first pass: a warp stages 32-row pieces of one kv-head's K rows in
 // shared memory with tiled TMA loads (cp.async.bulk.tensor) and forms the four query heads'
 // scores for every row in the reference's exact floating-point order.
 //
@@ -112,8 +112,8 @@ __device__ __forceinline__ void partial_rows4(const KRaw& k, const QRegs& Q, flo
   *reinterpret_cast<float4*>(red + (4 * step + rr) * kRedStride + 4 * j) = make_float4(b[0], b[1], b[2], b[3]);
 }
 
-// Scores of the 16 rows of one staged piece.  `rows` points at the piece in the
-// staging buffer, `red` at this slot's exchange buffer (kRedFloats floats) and
+// Scores of 16 consecutive rows (half of a staged 32-row piece).  `rows` points at the first
+// of them in the staging buffer, `red` at this slot's exchange buffer (kRedFloats floats) and
 // `score_out` at 64 floats laid out [row][head].  The K words of the next
 // four-row step are fetched while the current step is multiplied, and a single
 // exchange finishes all 16 rows.  Rows that were not staged produce garbage
