@@ -198,6 +198,33 @@ SANTA_API int santa_prop_decode(const void* q, const void* K, const void* V, int
                       int64_t S, uint64_t seed, int block_n, void* out, float* m_star, int32_t* vrows,
                       void* workspace, size_t workspace_bytes, const santa_prop_ext* ext, void* stream);
 
+/* Bytes of workspace santa_prop_decode_ragged needs on the current device (0 on bad arguments). */
+SANTA_API size_t santa_prop_ragged_workspace_bytes(int B, int H, int KVH, int D, int max_len);
+
+/*
+ * S2ANTA-Prop decode attention for a RAGGED BATCH in one launch sequence.  Replaces the per-sequence
+ * loop the reference's adapter runs over decode_systematic_scalar
+ * (tutorial_code/attention_backends.py:491-500): sequence b gets exactly the result of
+ * santa_prop_decode(q[b], K[b,:len_b], V[b,:len_b], ..., block_n = 256) -- the same tile statistics,
+ * budgets, random offsets (keyed by the head index h, not b*H+h, as in the loop) and sampled row counts;
+ * outputs agree up to the fp32 order in which per-warp partial sums are added.
+ *
+ *   q        [B,H,D]             storage dtype, contiguous
+ *   K, V     [B,L_storage,KVH,D] storage dtype, contiguous; rows [0, len_b) of sequence b are used
+ *   seq_lens [B] int32 in DEVICE memory, read by the kernels when they run (so a captured CUDA graph
+ *            follows lengths that change between replays); each entry is clamped to [0, max_len]
+ *   max_len  host-side bound on the lengths, 0 < max_len <= L_storage; sizes the workspace
+ *   out      [B,H,D] storage dtype;  m_star [B,H] fp32;  vrows [B,KVH] int32 or NULL
+ * Tiles are 256 rows (what the reference's rule picks for every length above 3072; a shorter sequence
+ * gets the result of the per-sequence call with block_n = 256, not of its 32/64-row rule).  A
+ * sequence of length 0 yields a zero output row.  B <= 1024.  Trace arrays of `ext` are laid out
+ * [B,H,ceil(max_len/256)] and [B,H,max_len] (rowmask [B,KVH,max_len]); pass1_mode must be 0 or 2.
+ */
+SANTA_API int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH,
+                                       int D, int L_storage, const int32_t* seq_lens, int max_len, int64_t S,
+                                       uint64_t seed, void* out, float* m_star, int32_t* vrows, void* workspace,
+                                       size_t workspace_bytes, const santa_prop_ext* ext, void* stream);
+
 /* ---- split-KV combine ------------------------------------------------------- */
 
 /*

@@ -76,6 +76,8 @@ EXPORTS = (
     "santa_prop_decode",
     "santa_lse_combine",
     "santa_flash_decode_noalloc",
+    "santa_prop_ragged_workspace_bytes",
+    "santa_prop_decode_ragged",
 )
 
 
@@ -117,6 +119,17 @@ def lib() -> C.CDLL:
             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,  # q K V dtype
             C.c_int, C.c_int, C.c_int, C.c_int,  # H KVH D L
             C.c_int64, C.c_uint64, C.c_int,  # S seed block_n
+            C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
+            C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
+        ]
+    if hasattr(L, "santa_prop_decode_ragged"):
+        L.santa_prop_ragged_workspace_bytes.restype = C.c_size_t
+        L.santa_prop_ragged_workspace_bytes.argtypes = [C.c_int] * 5
+        L.santa_prop_decode_ragged.restype = C.c_int
+        L.santa_prop_decode_ragged.argtypes = [
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,  # q K V dtype
+            C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,  # B H KVH D L_storage
+            C.c_void_p, C.c_int, C.c_int64, C.c_uint64,  # seq_lens max_len S seed
             C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
             C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
         ]

@@ -77,10 +77,13 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Narrower column groups give more, smaller items.  The width that minimises
 // the busiest SM's load (in column-tiles) wins; on a tie the widest does, since
 // wide groups fetch whole token rows together.
-santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid) {
+// `within` > 0 restricts the width to divisors of it (ragged batches: a column group must not
+// span two sequences, so the width has to divide KVH).
+santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid, int within = 0) {
   santa::WorkSplit best{};
   long long best_load = -1;
   for (int gw = santa::kGroupWarps; gw >= 1; gw >>= 1) {
+    if (within > 0 && within % gw != 0) continue;
     const long long ncg = (ncol + gw - 1) / gw;
     const long long items = ncg * T_c;
     const long long slots = (long long)sms * (santa::kGroupWarps / gw);
@@ -156,6 +159,39 @@ int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPla
   pl->off_stash = pl->off_a0 + ht;
   pl->off_pvrows = pl->off_stash + align_up(size_t(H) * L * 2, 256);
   const size_t slots = size_t(santa::prop_pass2_max_groups(sms)) + KVH;
+  pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
+  pl->total = pl->off_partials + slots * santa::kGH * santa::kD * sizeof(float);
+  return SANTA_OK;
+}
+
+// Ragged Prop batch: tables and the stash are laid out for the length bound, [B,H,T_max] and
+// [B,H,max_len]; the work split assumes every sequence as long as the bound (the kernels count
+// the real items).
+struct PropRaggedPlan {
+  int T_max, grid;
+  santa::WorkSplit ws;
+  size_t off_m, off_ell, off_S, off_inv, off_a0, off_stash, off_pvrows, off_partials, total;
+};
+
+int plan_prop_ragged(int B, int H, int KVH, int D, int max_len, PropRaggedPlan* pl) {
+  if (KVH <= 0 || D != santa::kD || H != santa::kGH * KVH) return SANTA_E_SHAPE;
+  if (B <= 0 || B > santa::kMaxRaggedSeqs) return SANTA_E_TOO_LARGE;
+  if (max_len <= 0) return SANTA_E_LENGTH;
+  int sms = 0;
+  if (int rc = sm_count_of_current_device(&sms)) return rc;
+  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
+  pl->T_max = (max_len + 255) / 256;
+  if ((long long)B * KVH * pl->T_max >= (1LL << 31)) return SANTA_E_TOO_LARGE;
+  pl->ws = make_split(B * KVH, pl->T_max, sms, &pl->grid, KVH);
+  const size_t ht = align_up(size_t(B) * H * pl->T_max * 4, 256);
+  pl->off_m = 256;
+  pl->off_ell = pl->off_m + ht;
+  pl->off_S = pl->off_ell + ht;
+  pl->off_inv = pl->off_S + ht;
+  pl->off_a0 = pl->off_inv + ht;
+  pl->off_stash = pl->off_a0 + ht;
+  pl->off_pvrows = pl->off_stash + align_up(size_t(B) * H * max_len * 2, 256);
+  const size_t slots = size_t(santa::prop_pass2_max_groups(sms)) + size_t(B) * KVH;
   pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
   pl->total = pl->off_partials + slots * santa::kGH * santa::kD * sizeof(float);
   return SANTA_OK;
@@ -253,6 +289,10 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   p.KVH = KVH;
   p.L_valid = L_valid;
   p.L_storage = L_storage;
+  p.seq_lens = nullptr;
+  p.nseq = B;
+  p.tile_stride = pl.T_c;
+  p.len_stride = L_valid;
   p.ws = pl.ws;
   p.S_per_tile = spt;
   p.q_scale = 1.0f / std::sqrt((float)D);  // F.cpp:210
@@ -311,6 +351,10 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
   sp.KVH = KVH;
   sp.L_valid = L;
   sp.L_storage = L;
+  sp.seq_lens = nullptr;
+  sp.nseq = 1;
+  sp.tile_stride = pl.T_c;
+  sp.len_stride = L;
   sp.ws = pl.ws;
   sp.S_per_tile = 0;
   sp.q_scale = 1.0f / std::sqrt((float)D);  // P.cpp:208
@@ -323,6 +367,69 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
   p.block_n = pl.block_n;
   p.T_c = pl.T_c;
   p.use_vec = pl.use_vec;
+  p.S = S > 2147483647LL ? 2147483647 : (S < -2147483647LL ? -2147483647 : int(S));
+  p.flags = ext ? ext->flags : 3;
+  p.S_tiles = (ext && ext->S_tiles) ? ext->S_tiles : reinterpret_cast<int*>(ws + pl.off_S);
+  p.invdelta = (ext && ext->invdelta) ? ext->invdelta : reinterpret_cast<float*>(ws + pl.off_inv);
+  p.a0 = (ext && ext->a0) ? ext->a0 : reinterpret_cast<float*>(ws + pl.off_a0);
+  p.m_star = m_star;
+  p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
+  p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.out = out;
+  p.vrows = vrows;
+  p.dbg_c = ext ? ext->counts : nullptr;
+  p.rowmask = ext ? ext->rowmask : nullptr;
+  cudaError_t e = santa::launch_prop(p, dtype, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+size_t santa_prop_ragged_workspace_bytes(int B, int H, int KVH, int D, int max_len) {
+  PropRaggedPlan pl;
+  if (plan_prop_ragged(B, H, KVH, D, max_len, &pl) != SANTA_OK) return 0;
+  return pl.total;
+}
+
+int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
+                             int L_storage, const int32_t* seq_lens, int max_len, int64_t S, uint64_t seed,
+                             void* out, float* m_star, int32_t* vrows, void* workspace, size_t workspace_bytes,
+                             const santa_prop_ext* ext, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!q || !K || !V || !out || !m_star || !seq_lens) return SANTA_E_ARG;
+  if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
+  if (max_len <= 0 || max_len > L_storage) return SANTA_E_LENGTH;
+  if (ext && ext->pass1_mode != 0 && ext->pass1_mode != 2) return SANTA_E_ARG;
+  PropRaggedPlan pl;
+  if (int rc = plan_prop_ragged(B, H, KVH, D, max_len, &pl)) return rc;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
+    return SANTA_E_WORKSPACE;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+
+  santa::PropParams p{};
+  santa::StreamParams& sp = p.sp;
+  if (int rc = encode_k_map(&sp.tmK, K, B, L_storage, KVH)) return rc;
+  sp.q = q;
+  sp.V = V;
+  sp.H = H;
+  sp.KVH = KVH;
+  sp.L_valid = max_len;
+  sp.L_storage = L_storage;
+  sp.seq_lens = seq_lens;
+  sp.nseq = B;
+  sp.tile_stride = pl.T_max;
+  sp.len_stride = max_len;
+  sp.ws = pl.ws;
+  sp.S_per_tile = 0;
+  sp.q_scale = 1.0f / std::sqrt((float)D);  // P.cpp:208
+  sp.seed = seed;
+  sp.status = reinterpret_cast<int*>(ws);
+  sp.m_tiles = (ext && ext->m_tiles) ? ext->m_tiles : reinterpret_cast<float*>(ws + pl.off_m);
+  sp.ell_tiles = (ext && ext->ell_tiles) ? ext->ell_tiles : reinterpret_cast<float*>(ws + pl.off_ell);
+  sp.stash = (ext && ext->u16) ? ext->u16 : reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  p.K = K;
+  p.block_n = 256;
+  p.T_c = pl.T_max;
+  p.use_vec = 1;
   p.S = S > 2147483647LL ? 2147483647 : (S < -2147483647LL ? -2147483647 : int(S));
   p.flags = ext ? ext->flags : 3;
   p.S_tiles = (ext && ext->S_tiles) ? ext->S_tiles : reinterpret_cast<int*>(ws + pl.off_S);

@@ -149,8 +149,53 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int 
 __host__ __device__ __forceinline__ long long range_lo(long long i, long long items, long long ctas) {
   return (i * items) / ctas;
 }
-// the CTA whose range contains item x (requires items >= ctas)
+// the CTA whose range contains item x: the largest i with lo(i) <= x
 __host__ __device__ __forceinline__ int cta_of_item(long long x, long long items, long long ctas) {
   return int(((x + 1) * ctas - 1) / items);
+}
+
+// ---------------------------------------------------------------- ragged batches
+// A ragged batch gives every sequence its own length through a device array.  Work items are
+// ordered (sequence, column group, tile); `start[b]` is the first item of sequence b and
+// start[nseq] the item total.  Lengths are clamped to [0, max_len], so that a bad entry can
+// neither index outside the cache nor change the item arithmetic between kernels.
+constexpr int kMaxRaggedSeqs = 1024;
+
+__device__ __forceinline__ int ragged_len(const int* __restrict__ seq_lens, int b, int max_len) {
+  const int n = __ldg(seq_lens + b);
+  return n < 0 ? 0 : (n > max_len ? max_len : n);
+}
+
+// Built by one full warp; `start` has nseq + 1 entries in shared memory.
+__device__ __forceinline__ void build_item_starts(const int* __restrict__ seq_lens, int nseq, int max_len, int bn,
+                                                  int groups_per_seq, int* start, int lane) {
+  int carry = 0;
+  for (int base = 0; base < nseq; base += 32) {
+    const int b = base + lane;
+    int n = 0;
+    if (b < nseq) n = ((ragged_len(seq_lens, b, max_len) + bn - 1) / bn) * groups_per_seq;
+    int incl = n;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (b < nseq) start[b] = carry + incl - n;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) start[nseq] = carry;
+}
+
+// The sequence owning item `it` (0 <= it < start[nseq]): the largest b with start[b] <= it.
+__device__ __forceinline__ int seq_of_item(const int* start, int nseq, int it) {
+  int lo = 0, hi = nseq;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (start[mid] <= it)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  return lo;
 }
 }  // namespace santa

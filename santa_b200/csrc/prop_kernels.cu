@@ -151,21 +151,33 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
 // that is never stored), +1 for the first S - sum(floor) entries,
 // invdelta_t = S_t / ell_t, a0_t = u01(seed, h, t).
 // flags bit0: jitter added with one fma; bit1: thread partials of Z with fma.
-__global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restrict__ m_tiles,
-                                                           const float* __restrict__ ell_tiles, int T_c, int S,
-                                                           uint64_t seed, int flags, float* __restrict__ m_star,
-                                                           int* __restrict__ S_tiles, float* __restrict__ invdelta,
-                                                           float* __restrict__ a0_tile) {
+// Ragged batches: blockIdx.y is the sequence, its tile count comes from seq_lens and its rows of
+// the tables are tile_stride apart; every sequence uses the head index h in the random stream,
+// exactly like one call per sequence.
+__global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restrict__ m_tiles_all,
+                                                           const float* __restrict__ ell_tiles_all, int T_uniform,
+                                                           const int* __restrict__ seq_lens, int max_len, int bn,
+                                                           int tile_stride, int S, uint64_t seed, int flags,
+                                                           float* __restrict__ m_star_all,
+                                                           int* __restrict__ S_tiles_all,
+                                                           float* __restrict__ invdelta_all,
+                                                           float* __restrict__ a0_tile_all) {
   cudaGridDependencySynchronize();
   extern __shared__ unsigned char smraw[];
+  const int T_c = seq_lens ? (ragged_len(seq_lens, blockIdx.y, max_len) + bn - 1) / bn : T_uniform;
   float* frac = reinterpret_cast<float*>(smraw);
-  int* idx = reinterpret_cast<int*>(frac + T_c);
+  int* idx = reinterpret_cast<int*>(frac + tile_stride);
   __shared__ float s_part[128];
   __shared__ float s_bcast;
   __shared__ int s_ipart[128];
   const int h = blockIdx.x, tid = threadIdx.x;
-  const float* mt = m_tiles + size_t(h) * T_c;
-  const float* el = ell_tiles + size_t(h) * T_c;
+  const size_t row = (size_t(blockIdx.y) * gridDim.x + h) * tile_stride;
+  const float* mt = m_tiles_all + row;
+  const float* el = ell_tiles_all + row;
+  int* S_tiles = S_tiles_all + row;
+  float* invdelta = invdelta_all + row;
+  float* a0_tile = a0_tile_all + row;
+  float* m_star = m_star_all ? m_star_all + size_t(blockIdx.y) * gridDim.x : nullptr;
 
   float lm = -3.402823466e+38f;
   for (int t = tid; t < T_c; t += 128) {
@@ -204,9 +216,9 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
 
   if (S <= 0 || !(Z > 0.0f)) {
     for (int t = tid; t < T_c; t += 128) {
-      S_tiles[size_t(h) * T_c + t] = 0;
-      invdelta[size_t(h) * T_c + t] = 0.0f;
-      a0_tile[size_t(h) * T_c + t] = u01_from_seed(seed, h, t);
+      S_tiles[t] = 0;
+      invdelta[t] = 0.0f;
+      a0_tile[t] = u01_from_seed(seed, h, t);
     }
     return;
   }
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   for (int t = tid; t < T_c; t += 128) {
     const float q = __fmul_rn((float)S, __fdiv_rn(frac[t], Z));
     const int b = (int)floorf(q);
-    S_tiles[size_t(h) * T_c + t] = b;
+    S_tiles[t] = b;
     bl += b;
     const float ft = __fsub_rn(q, (float)b);
     const float u = u01_from_seed(seed, h, t);
@@ -255,29 +267,32 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   }
   for (int r = tid; r < rem; r += 128) {
     const int best = idx[r];
-    if (best >= 0) S_tiles[size_t(h) * T_c + best] += 1;
+    if (best >= 0) S_tiles[best] += 1;
   }
   __syncthreads();
   for (int t = tid; t < T_c; t += 128) {
     const float ell = el[t];
-    const int St = S_tiles[size_t(h) * T_c + t];
-    invdelta[size_t(h) * T_c + t] = (St > 0 && ell > 1e-20f) ? __fdiv_rn((float)St, ell) : 0.0f;
-    a0_tile[size_t(h) * T_c + t] = u01_from_seed(seed, h, t);
+    const int St = S_tiles[t];
+    invdelta[t] = (St > 0 && ell > 1e-20f) ? __fdiv_rn((float)St, ell) : 0.0f;
+    a0_tile[t] = u01_from_seed(seed, h, t);
   }
 }
 
 // ------------------------------------------------------------------ pass 2
 struct Pass2Params {
-  const void* V;            // [L,KVH,128]
-  const uint16_t* stash;    // [H][L]
-  const float* invdelta;    // [H,T_c]
-  const float* a0;          // [H,T_c]
-  int H, KVH, L, bn, T_c;
-  WorkSplit ws;             // gw == 1: one column (kv-head) per warp
-  float* partials;          // [nvg + KVH][4][128]
-  int* partial_vrows;       // [nvg + KVH]
-  int16_t* dbg_c;           // [H,L] or null
-  int* rowmask;             // [KVH,L] or null
+  const void* V;            // [nseq,L_storage,KVH,128]
+  const uint16_t* stash;    // [nseq,H,len_stride]
+  const float* invdelta;    // [nseq,H,tile_stride]
+  const float* a0;          // [nseq,H,tile_stride]
+  int H, KVH, L, bn, T_c;   // L, T_c: the uniform length / tile count, or the length bound when ragged
+  int L_storage, len_stride, tile_stride;
+  const int* seq_lens;      // [nseq] device lengths, or null
+  int nseq;
+  WorkSplit ws;             // gw == 1: one column (sequence, kv-head) per warp
+  float* partials;          // [nvg + columns][4][128]
+  int* partial_vrows;       // [nvg + columns]
+  int16_t* dbg_c;           // [nseq,H,len_stride] or null
+  int* rowmask;             // [nseq,KVH,len_stride] or null
 };
 
 constexpr int kPass2Warps = 8;
@@ -286,22 +301,46 @@ constexpr int kPass2Warps = 8;
 // sparse V sum (santa_cuda_kernel.cu:771-863), tiles in ascending order.
 template <typename TK>
 __global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass2Params p) {
-  cudaGridDependencySynchronize();
   __shared__ __align__(16) float4 s_buf[kPass2Warps][kMaxTileRows];
+  __shared__ int s_start[kMaxRaggedSeqs + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool ragged = p.seq_lens != nullptr;
+  if (ragged) {  // lengths are inputs of the call, not results of the preceding kernels
+    if (warp == 0) build_item_starts(p.seq_lens, p.nseq, p.L, p.bn, p.KVH, s_start, lane);
+    __syncthreads();
+  }
+  cudaGridDependencySynchronize();
+  long long items = p.ws.items;
+  int nvg = p.ws.nvg;
+  if (ragged) {
+    items = s_start[p.nseq];
+    nvg = (items < (long long)nvg) ? int(items) : nvg;
+  }
   const int vg = blockIdx.x * kPass2Warps + warp;
-  if (vg >= p.ws.nvg) return;
-  const long long lo = range_lo(vg, p.ws.items, p.ws.nvg), hi = range_lo(vg + 1, p.ws.items, p.ws.nvg);
+  if (vg >= nvg) return;
+  const long long lo = range_lo(vg, items, nvg), hi = range_lo(vg + 1, items, nvg);
   float4* sb = s_buf[warp];
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
 
   long long it = lo;
   while (it < hi) {
-    const int kv = int(it / p.T_c);
-    const int t_lo = int(it - (long long)kv * p.T_c);
-    const int t_hi = (hi - it < (long long)(p.T_c - t_lo)) ? t_lo + int(hi - it) : p.T_c;
+    int b = 0, kv, t_lo, L_b = p.L, T_b = p.T_c;
+    if (!ragged) {
+      kv = int(it / T_b);
+      t_lo = int(it - (long long)kv * T_b);
+    } else {
+      b = seq_of_item(s_start, p.nseq, int(it));
+      L_b = ragged_len(p.seq_lens, b, p.L);
+      T_b = (L_b + p.bn - 1) / p.bn;
+      const int rel = int(it) - s_start[b];
+      kv = rel / T_b;
+      t_lo = rel - kv * T_b;
+    }
+    const int t_hi = (hi - it < (long long)(T_b - t_lo)) ? t_lo + int(hi - it) : T_b;
     const int h0 = kv * kGH;
-    const unsigned char* vcol = static_cast<const unsigned char*>(p.V) + size_t(kv) * kRowBytes;
+    const size_t bh0 = size_t(b) * p.H + h0;
+    const unsigned char* vcol =
+        static_cast<const unsigned char*>(p.V) + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
     float acc[kGH][4];
 #pragma unroll
     for (int g = 0; g < kGH; ++g)
@@ -312,16 +351,17 @@ __global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass
 #pragma unroll 1
     for (int t = t_lo; t < t_hi; ++t) {
       const int n0 = t * p.bn;
-      const int tile_len = (p.L - n0 < p.bn) ? (p.L - n0) : p.bn;
+      const int tile_len = (L_b - n0 < p.bn) ? (L_b - n0) : p.bn;
       const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+      const size_t ls = size_t(p.len_stride);
 #pragma unroll 1
       for (int ch = 0; ch < nch; ++ch) {
         const int r = ch * kChunkRows + lane;
         float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < tile_len) {
-          const uint16_t* sp = p.stash + size_t(h0) * p.L + n0 + r;
-          const uint32_t w01 = uint32_t(__ldcg(sp)) | (uint32_t(__ldcg(sp + p.L)) << 16);
-          const uint32_t w23 = uint32_t(__ldcg(sp + 2 * size_t(p.L))) | (uint32_t(__ldcg(sp + 3 * size_t(p.L))) << 16);
+          const uint16_t* sp = p.stash + bh0 * ls + n0 + r;
+          const uint32_t w01 = uint32_t(__ldcg(sp)) | (uint32_t(__ldcg(sp + ls)) << 16);
+          const uint32_t w23 = uint32_t(__ldcg(sp + 2 * ls)) | (uint32_t(__ldcg(sp + 3 * ls)) << 16);
           const float2 f01 = Store16<TK>::unpack(w01), f23 = Store16<TK>::unpack(w23);
           u = make_float4(f01.x, f01.y, f23.x, f23.y);
         }
@@ -331,14 +371,14 @@ __global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass
       float invdel[kGH], a0[kGH];
 #pragma unroll
       for (int g = 0; g < kGH; ++g) {
-        invdel[g] = __ldcg(p.invdelta + size_t(h0 + g) * p.T_c + t);
-        a0[g] = __ldcg(p.a0 + size_t(h0 + g) * p.T_c + t);
+        invdel[g] = __ldcg(p.invdelta + (bh0 + g) * p.tile_stride + t);
+        a0[g] = __ldcg(p.a0 + (bh0 + g) * p.tile_stride + t);
       }
       RowTrace tr;
-      tr.head_stride = size_t(p.L);
+      tr.head_stride = ls;
       tr.u16 = nullptr;
-      tr.counts = p.dbg_c ? p.dbg_c + size_t(h0) * p.L + n0 : nullptr;
-      tr.rowmask = p.rowmask ? p.rowmask + size_t(kv) * p.L + n0 : nullptr;
+      tr.counts = p.dbg_c ? p.dbg_c + bh0 * ls + n0 : nullptr;
+      tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * ls + n0 : nullptr;
       const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
       vrow_count += n_emit;
       float o[kGH][4];
@@ -354,7 +394,7 @@ __global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass
           for (int i = 0; i < 4; ++i) acc[g][i] = __fadd_rn(acc[g][i], o[g][i]);
       }
     }
-    const size_t pslot = size_t(vg) + kv;
+    const size_t pslot = size_t(vg) + size_t(b) * p.KVH + kv;
     float* ps = p.partials + pslot * (kGH * kD);
 #pragma unroll
     for (int g = 0; g < kGH; ++g)
@@ -369,10 +409,12 @@ struct PropMergeParams {
   const float* partials;
   const int* partial_vrows;
   int KVH, T_c;
+  const int* seq_lens;  // ragged: [nseq] device lengths, else null
+  int nseq, max_len, bn;
   WorkSplit ws;
   float scale;   // 1/S, or 0 when S <= 0 (santa_cuda.cpp:333)
-  void* out;     // [H,128]
-  int* vrows;    // [KVH] or null
+  void* out;     // [nseq,H,128]
+  int* vrows;    // [nseq,KVH] or null
 };
 
 // One CTA of 8 warps per (kv-head, head): warp w adds the partials v = first+w, first+w+8, ... in
@@ -381,12 +423,48 @@ struct PropMergeParams {
 constexpr int kMergeWarps = 8;
 template <typename TK>
 __global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const PropMergeParams p) {
-  cudaGridDependencySynchronize();
   __shared__ float4 s_acc[kMergeWarps][32];
   __shared__ int s_vr[kMergeWarps];
-  const int kv = blockIdx.x >> 2, g = blockIdx.x & 3, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int v_first = cta_of_item((long long)kv * p.T_c, p.ws.items, p.ws.nvg);
-  const int v_last = cta_of_item((long long)(kv + 1) * p.T_c - 1, p.ws.items, p.ws.nvg);
+  __shared__ int s_before[kMergeWarps], s_total[kMergeWarps];
+  const int col = blockIdx.x >> 2;  // (sequence, kv-head)
+  const int kv = col, g = blockIdx.x & 3, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  long long items = p.ws.items, item0 = (long long)col * p.T_c;
+  int nvg = p.ws.nvg, T_b = p.T_c;
+  if (p.seq_lens != nullptr) {
+    // item range of this column: tiles of the sequences before it, times KVH, plus its own offset
+    const int b = col / p.KVH, kvb = col - b * p.KVH;
+    int before = 0, total = 0;
+    for (int i = threadIdx.x; i < p.nseq; i += kMergeWarps * 32) {
+      const int t = (ragged_len(p.seq_lens, i, p.max_len) + p.bn - 1) / p.bn;
+      total += t;
+      before += (i < b) ? t : 0;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      before += __shfl_xor_sync(0xffffffffu, before, off);
+      total += __shfl_xor_sync(0xffffffffu, total, off);
+    }
+    if (lane == 0) {
+      s_before[w] = before;
+      s_total[w] = total;
+    }
+    __syncthreads();
+    before = total = 0;
+    for (int k = 0; k < kMergeWarps; ++k) {
+      before += s_before[k];
+      total += s_total[k];
+    }
+    T_b = (ragged_len(p.seq_lens, b, p.max_len) + p.bn - 1) / p.bn;
+    items = (long long)total * p.KVH;
+    nvg = (items < (long long)nvg) ? int(items) : nvg;
+    item0 = (long long)before * p.KVH + (long long)kvb * T_b;
+  }
+  cudaGridDependencySynchronize();
+  int v_first = 0, v_last = -1;  // an empty sequence contributes nothing
+  if (T_b > 0) {
+    v_first = cta_of_item(item0, items, nvg);
+    v_last = cta_of_item(item0 + T_b - 1, items, nvg);
+  }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int v0 = v_first + w; v0 <= v_last; v0 += 4 * kMergeWarps) {
     float4 a[4];
@@ -460,12 +538,18 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   const int H = p.sp.H, KVH = p.sp.KVH, L = p.sp.L_valid;
   if (p.use_vec) {
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)kStreamSmemBytes);
+      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1, false>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
+      if (e != cudaSuccess) return e;
+      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1, true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
       if (e != cudaSuccess) return e;
       configured[dev] = true;
     }
-    stream_kernel<TK, 256, kModePropPass1><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
+    if (p.sp.seq_lens != nullptr)
+      stream_kernel<TK, 256, kModePropPass1, true><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
+    else
+      stream_kernel<TK, 256, kModePropPass1, false><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
   } else {
     const int nwarp = p.block_n / 16;
     const size_t smem = size_t(nwarp * 256 + 2 * 16 * nwarp + 16) * sizeof(float);
@@ -476,9 +560,10 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
-  e = launch_dependent(prop_budgets_kernel, dim3(H), dim3(128), size_t(p.T_c) * 8, stream,
-                       (const float*)p.sp.m_tiles, (const float*)p.sp.ell_tiles, p.T_c, p.S, p.sp.seed, p.flags,
-                       p.m_star, p.S_tiles, p.invdelta, p.a0);
+  const int nseq = p.sp.seq_lens ? p.sp.nseq : 1;
+  e = launch_dependent(prop_budgets_kernel, dim3(H, nseq), dim3(128), size_t(p.sp.tile_stride) * 8, stream,
+                       (const float*)p.sp.m_tiles, (const float*)p.sp.ell_tiles, p.T_c, p.sp.seq_lens, L,
+                       p.block_n, p.sp.tile_stride, p.S, p.sp.seed, p.flags, p.m_star, p.S_tiles, p.invdelta, p.a0);
   if (e != cudaSuccess) return e;
 
   Pass2Params p2{};
@@ -491,10 +576,15 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   p2.L = L;
   p2.bn = p.block_n;
   p2.T_c = p.T_c;
+  p2.L_storage = p.sp.L_storage;
+  p2.len_stride = p.sp.len_stride;
+  p2.tile_stride = p.sp.tile_stride;
+  p2.seq_lens = p.sp.seq_lens;
+  p2.nseq = nseq;
   p2.ws.gw = 1;
   p2.ws.T_c = p.T_c;
-  p2.ws.ncol = KVH;
-  p2.ws.items = (long long)KVH * p.T_c;
+  p2.ws.ncol = nseq * KVH;
+  p2.ws.items = (long long)nseq * KVH * p.T_c;  // ragged: an upper bound, the kernels count the real items
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long max_warps = (long long)sms * 4 * kPass2Warps;
@@ -512,11 +602,15 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   pm.partial_vrows = p.partial_vrows;
   pm.KVH = KVH;
   pm.T_c = p.T_c;
+  pm.seq_lens = p.sp.seq_lens;
+  pm.nseq = nseq;
+  pm.max_len = L;
+  pm.bn = p.block_n;
   pm.ws = p2.ws;
   pm.scale = (p.S > 0) ? (1.0f / (float)p.S) : 0.0f;
   pm.out = p.out;
   pm.vrows = p.vrows;
-  return launch_dependent(prop_merge_kernel<TK>, dim3(KVH * kGH), dim3(kMergeWarps * 32), 0, stream, pm);
+  return launch_dependent(prop_merge_kernel<TK>, dim3(nseq * KVH * kGH), dim3(kMergeWarps * 32), 0, stream, pm);
 }
 
 cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t stream) {

@@ -32,6 +32,13 @@ struct StreamParams {
   uint64_t seed;
   int batch_offset, tile_offset;
   int* status;  // one word
+  // Ragged batch (Prop pass 1): per-sequence lengths on the device, clamped to [0, L_valid];
+  // null for a uniform batch.  Column groups then never span sequences (gw divides KVH) and the
+  // item total is computed by the kernel.
+  const int* seq_lens;  // [nseq] or null
+  int nseq;
+  int tile_stride;  // tiles per (sequence, head) row of m_tiles / ell_tiles
+  int len_stride;   // rows per (sequence, head) row of stash / trace arrays
   // Flash: per (virtual group, column group) partials, read by the merge kernel
   float* partials;     // [nvg + column groups][gw][4][kPartialStride]
   int* partial_vrows;  // [nvg + column groups][gw]

@@ -38,7 +38,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <typename TK, int BN, int MODE>
+// RAGGED: per-sequence lengths from p.seq_lens (a compile-time switch, so that the uniform kernel
+// carries none of the look-up state).
+template <typename TK, int BN, int MODE, bool RAGGED = false>
 __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_constant__ StreamParams p) {
   constexpr int NW = (BN == 256) ? 8 : 4;  // warps of the reference block (fixes the ell order)
 
@@ -56,6 +58,10 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
   const uint32_t bar_empty = smem_u32(bars + kStreamStages + 2);  // [2]
 
   if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tmK) : "memory");
+  __shared__ int s_start[kMaxRaggedSeqs + 1];
+  constexpr bool ragged = RAGGED;
+  if (ragged && cta_warp == kCtaWarps - 1)
+    build_item_starts(p.seq_lens, p.nseq, p.L_valid, BN, p.KVH / p.ws.gw, s_start, lane);
   WarpRing<kStreamStages> ring;
   if (!is_sampler) {
     ring.init(sbase, bars, lane);
@@ -72,26 +78,48 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
   const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
   const unsigned char* __restrict__ Vg = static_cast<const unsigned char*>(p.V);
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
-  const WarpWork ww = warp_work(p.ws, blockIdx.x, gridDim.x, slot);
+  WorkSplit split = p.ws;
+  if (ragged) {  // the item total is only known here; never more groups than items
+    split.items = s_start[p.nseq];
+    split.nvg = (split.items < (long long)split.nvg) ? int(split.items) : split.nvg;
+  }
+  const WarpWork ww = warp_work(split, blockIdx.x, gridDim.x, slot);
 
   bool dead = false;     // set when a wait ran out; the status word then says why
   uint32_t handoff = 0;  // tiles handed over so far on this slot (selects buffer and parity)
 
   long long it = ww.lo;
   while (it < ww.hi) {
-    const int cg = int(it / p.ws.T_c);
-    const int t_lo = int(it - (long long)cg * p.ws.T_c);
-    const int t_hi = (ww.hi - it < (long long)(p.ws.T_c - t_lo)) ? t_lo + int(ww.hi - it) : p.ws.T_c;
-    const int col = cg * p.ws.gw + ww.col_in_group;
-    const bool active = col < p.ws.ncol;
-    const int b = active ? col / p.KVH : 0;
-    const int kv = col - b * p.KVH;
+    // item -> (column group, first tile); L_b / T_b are the column's length and tile count
+    int cg, t_lo, b, kv, L_b, T_b;
+    bool active;
+    if (!ragged) {
+      L_b = p.L_valid;
+      T_b = p.ws.T_c;
+      cg = int(it / T_b);
+      t_lo = int(it - (long long)cg * T_b);
+      const int col = cg * p.ws.gw + ww.col_in_group;
+      active = col < p.ws.ncol;
+      b = active ? col / p.KVH : 0;
+      kv = col - b * p.KVH;
+    } else {
+      b = seq_of_item(s_start, p.nseq, int(it));
+      L_b = ragged_len(p.seq_lens, b, p.L_valid);
+      T_b = (L_b + BN - 1) / BN;
+      const int rel = int(it) - s_start[b];
+      const int cgs = rel / T_b;
+      t_lo = rel - cgs * T_b;
+      cg = b * (p.KVH / p.ws.gw) + cgs;
+      kv = cgs * p.ws.gw + ww.col_in_group;
+      active = true;
+    }
+    const int t_hi = (ww.hi - it < (long long)(T_b - t_lo)) ? t_lo + int(ww.hi - it) : T_b;
     const int h0 = kv * kGH;
 
     if (active && !is_sampler) {
       // =========================== SCORE warp ===============================
       const int row_base = t_lo * BN;
-      const int row_end = (t_hi * BN < p.L_valid) ? t_hi * BN : p.L_valid;
+      const int row_end = (t_hi * BN < L_b) ? t_hi * BN : L_b;
       const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
       int issued = 0;  // the K pieces do not depend on q: start them before fetching q
       for (; issued < kStreamStages && issued < npieces; ++issued)
@@ -102,7 +130,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 #pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t, ++handoff) {
         const int n0 = t * BN;
-        const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const int tile_len = (L_b - n0 < BN) ? (L_b - n0) : BN;
         const uint32_t buf = handoff & 1u;
         float* scorebuf = scorebufs + buf * (kScoreBytes / 4);
         // wait until the sampler has released this buffer (passes at once the first two times)
@@ -145,7 +173,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 #pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t, ++handoff) {
         const int n0 = t * BN;
-        const int tile_len = (p.L_valid - n0 < BN) ? (p.L_valid - n0) : BN;
+        const int tile_len = (L_b - n0 < BN) ? (L_b - n0) : BN;
         const uint32_t buf = handoff & 1u;
         float4* sb = reinterpret_cast<float4*>(scorebufs + buf * (kScoreBytes / 4));
         if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u, 256)) {
@@ -166,11 +194,11 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             const int r = ch * kChunkRows + lane;
             if (r < tile_len) {
               const float4 u = sb[r];
-              uint16_t* sp = p.stash + bh0 * p.L_valid + n0 + r;
+              uint16_t* sp = p.stash + bh0 * p.len_stride + n0 + r;
               sp[0] = Store16<TK>::bits(u.x);
-              sp[size_t(p.L_valid)] = Store16<TK>::bits(u.y);
-              sp[2 * size_t(p.L_valid)] = Store16<TK>::bits(u.z);
-              sp[3 * size_t(p.L_valid)] = Store16<TK>::bits(u.w);
+              sp[size_t(p.len_stride)] = Store16<TK>::bits(u.y);
+              sp[2 * size_t(p.len_stride)] = Store16<TK>::bits(u.z);
+              sp[3 * size_t(p.len_stride)] = Store16<TK>::bits(u.w);
             }
           }
           __syncwarp();
@@ -187,7 +215,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             ev = (lane == g) ? ell[g] : ev;
             iv = (lane == g) ? invdel[g] : iv;
           }
-          const size_t o = (bh0 + lane) * p.ws.T_c + t;
+          const size_t o = (bh0 + lane) * p.tile_stride + t;
           p.m_tiles[o] = mv;
           p.ell_tiles[o] = ev;
           if (p.dbg_invdel != nullptr) p.dbg_invdel[o] = iv;
@@ -201,10 +229,10 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 #pragma unroll
           for (int g = 0; g < kGH; ++g) a0[g] = __shfl_sync(0xffffffffu, a0_lane, g);
           RowTrace tr;
-          tr.head_stride = size_t(p.L_valid);
-          tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.L_valid + n0 : nullptr;
-          tr.counts = p.dbg_c ? p.dbg_c + bh0 * p.L_valid + n0 : nullptr;
-          tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * p.L_valid + n0 : nullptr;
+          tr.head_stride = size_t(p.len_stride);
+          tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.len_stride + n0 : nullptr;
+          tr.counts = p.dbg_c ? p.dbg_c + bh0 * p.len_stride + n0 : nullptr;
+          tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * p.len_stride + n0 : nullptr;
           const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
           vrow_count += n_emit;
 

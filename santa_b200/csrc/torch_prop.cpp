@@ -128,9 +128,66 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tens
   return std::make_tuple(out, m_star, vrows);
 }
 
+// Ragged batch in one launch sequence; not part of the reference module.  It is exported under
+// its own name: the reference adapter treats a module that has `decode_systematic_batched` as truly
+// batched with Flash semantics (tutorial_code/attention_backends.py:447), which this is not --
+// every sequence here uses the head index h in the random stream, as the adapter's per-sequence
+// loop does (attention_backends.py:491-500).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tensor q_bh, at::Tensor K_g,
+                                                                        at::Tensor V_g, at::Tensor seq_lens,
+                                                                        int64_t S, uint64_t seed, bool want_vrows,
+                                                                        int64_t max_len) {
+  SANTA_CHECK(q_bh.is_cuda() && K_g.is_cuda() && V_g.is_cuda(), "q_bh, K_g and V_g must be CUDA");
+  SANTA_CHECK(q_bh.scalar_type() == at::kBFloat16 || q_bh.scalar_type() == at::kHalf, "q_bh must be bf16 or f16");
+  SANTA_CHECK(K_g.scalar_type() == q_bh.scalar_type() && V_g.scalar_type() == q_bh.scalar_type(),
+              "q_bh dtype must match K_g/V_g");
+  SANTA_CHECK(q_bh.dim() == 3 && K_g.dim() == 4 && V_g.dim() == 4,
+              "Ragged path expects q_bh [B,H,D], K_g/V_g [B,L,KVH,D]");
+  SANTA_CHECK(q_bh.device() == K_g.device() && q_bh.device() == V_g.device(), "device mismatch");
+  SANTA_CHECK(K_g.sizes() == V_g.sizes(), "K_g and V_g must have the same shape");
+  SANTA_CHECK(q_bh.size(0) == K_g.size(0), "Batch mismatch between q_bh and K_g/V_g");
+  SANTA_CHECK(q_bh.size(2) == K_g.size(3), "D mismatch (q_bh.size(2) vs K_g.size(3))");
+  SANTA_CHECK(K_g.is_contiguous() && V_g.is_contiguous(), "K_g/V_g must be contiguous with layout [B, L, KVH, D]");
+  const int B = (int)q_bh.size(0), H = (int)q_bh.size(1), D = (int)q_bh.size(2);
+  const int L_storage = (int)K_g.size(1), KVH = (int)K_g.size(2);
+  SANTA_CHECK(D == 128 && H == 4 * KVH, "This build supports only D=128 and GH=4 (H/KVH). Got D=", D, " H=", H,
+              " KVH=", KVH);
+  SANTA_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.dim() == 1 && seq_lens.size(0) == B,
+              "seq_lens must be an int32 tensor with one length per sequence");
+  const int mlen = max_len > 0 ? (int)max_len : L_storage;
+  SANTA_CHECK(mlen <= L_storage, "max_len exceeds storage length: max_len=", mlen, " storage=", L_storage);
+  SANTA_CHECK(B <= 1024, "The ragged path takes at most 1024 sequences. Got B=", B);
+
+  const c10::cuda::CUDAGuard guard(q_bh.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_bh.contiguous();
+  // lengths are read on the device when the kernels run; a host tensor is copied over
+  at::Tensor lens = seq_lens.is_cuda() ? seq_lens.contiguous() : seq_lens.to(q.device(), /*non_blocking=*/false);
+  SANTA_CHECK(lens.device() == q.device(), "seq_lens must be on q_bh's device or on the CPU");
+
+  at::Tensor out = at::empty({B, H, D}, q.options());
+  at::Tensor m_star = at::empty({B, H}, q.options().dtype(at::kFloat));
+  at::Tensor vrows = want_vrows ? at::empty({B, KVH}, q.options().dtype(at::kInt))
+                                : at::empty({0}, q.options().dtype(at::kInt));
+  const size_t ws_bytes = santa_prop_ragged_workspace_bytes(B, H, KVH, D, mlen);
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  const int rc = santa_prop_decode_ragged(
+      q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16,
+      B, H, KVH, D, L_storage, lens.data_ptr<int>(), mlen, S, seed, out.data_ptr(), m_star.data_ptr<float>(),
+      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), nullptr,
+      (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+  return std::make_tuple(out, m_star, vrows);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_bh"), py::arg("K_g"), py::arg("V_g"),
+        py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("want_vrows") = false,
+        py::arg("max_len") = -1);
   m.def("decode_systematic_scalar", &decode_systematic_scalar, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false);
 }

@@ -242,6 +242,70 @@ def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace
     return res + (tr,) if trace else res
 
 
+def prop_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, want_vrows=False, *, max_len=None, trace=False,
+                       flags=None):
+    """S2ANTA-Prop decode of a ragged batch in one launch sequence: ``q_bh [B,H,D]``,
+    ``K_g/V_g [B,L_storage,KVH,D]``, ``seq_lens`` int32 ``[B]`` on the device (a CPU tensor or a
+    list is copied there).  Sequence ``b`` gets the result of
+    ``prop_decode(q_bh[b], K_g[b, :len_b], V_g[b, :len_b], S, seed, block_n=256)``.
+    ``max_len`` bounds the lengths (default: the storage length) and sizes the scratch.
+    Returns ``(out [B,H,D], m_star [B,H], vrows [B,KVH] or empty)`` (+ ``PropTrace`` with batched
+    arrays ``[B,H,T_max]`` / ``[B,H,max_len]``)."""
+    _check(q_bh.is_cuda and K_g.is_cuda and V_g.is_cuda, "q_bh, K_g and V_g must be CUDA")
+    _check(q_bh.dtype in (torch.bfloat16, torch.float16), "q_bh must be bf16 or f16")
+    _check(K_g.dtype == q_bh.dtype and V_g.dtype == q_bh.dtype, "q_bh dtype must match K_g/V_g")
+    _check(q_bh.dim() == 3 and K_g.dim() == 4 and V_g.dim() == 4,
+           "Ragged path expects q_bh [B,H,D], K_g/V_g [B,L,KVH,D]")
+    _check(q_bh.device == K_g.device and q_bh.device == V_g.device, "device mismatch")
+    _check(K_g.shape == V_g.shape, "K_g and V_g must have the same shape")
+    _check(q_bh.size(0) == K_g.size(0), "Batch mismatch between q_bh and K_g/V_g")
+    _check(q_bh.size(2) == K_g.size(3), "D mismatch (q_bh.size(2) vs K_g.size(3))")
+    _check(K_g.is_contiguous() and V_g.is_contiguous(), "K_g/V_g must be contiguous with layout [B, L, KVH, D]")
+    if seed < 0:
+        raise TypeError("seed must be a non-negative 64-bit integer")
+    q = q_bh.contiguous()
+    B, H, D = q.shape
+    L_storage, KVH = K_g.size(1), K_g.size(2)
+    _check(D == 128 and H == 4 * KVH, f"This build supports only D=128 and GH=4 (H/KVH). Got D={D} H={H} KVH={KVH}")
+    dev = q.device
+    if not isinstance(seq_lens, torch.Tensor):
+        seq_lens = torch.tensor(list(seq_lens), dtype=torch.int32)
+    _check(seq_lens.numel() == B, "seq_lens must hold one length per sequence")
+    lens = seq_lens.to(device=dev, dtype=torch.int32).contiguous()
+    mlen = L_storage if max_len is None else int(max_len)
+    _check(0 < mlen <= L_storage, f"max_len must be in (0, storage length]; got {mlen} (storage {L_storage})")
+    T_max = (mlen + 255) // 256
+    with torch.cuda.device(dev):
+        lib = capi.lib()
+        nbytes = lib.santa_prop_ragged_workspace_bytes(B, H, KVH, D, mlen)
+        _check(nbytes > 0, "santa_b200: unsupported ragged problem (B must be 1..1024)")
+        ws = _workspace("prop_ragged", dev, nbytes)
+        out = torch.empty((B, H, D), device=dev, dtype=q.dtype)
+        m_star = torch.empty((B, H), device=dev, dtype=torch.float32)
+        vrows = torch.empty((B, KVH) if want_vrows else (0,), device=dev, dtype=torch.int32)
+        ext = capi.PropExt(pass1_mode=0, flags=3 if flags is None else int(flags))
+        tr = None
+        if trace:
+            f32 = dict(device=dev, dtype=torch.float32)
+            tr = PropTrace(256, T_max, torch.zeros((B, H, T_max), **f32), torch.zeros((B, H, T_max), **f32),
+                           torch.zeros((B, H, mlen), device=dev, dtype=torch.int16),
+                           torch.zeros((B, H, mlen), device=dev, dtype=torch.int16),
+                           torch.zeros((B, KVH, mlen), device=dev, dtype=torch.int32),
+                           torch.zeros((B, H, T_max), device=dev, dtype=torch.int32),
+                           torch.zeros((B, H, T_max), **f32), torch.zeros((B, H, T_max), **f32))
+            ext.m_tiles, ext.ell_tiles, ext.u16 = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr(), tr.u16.data_ptr()
+            ext.counts, ext.rowmask = tr.counts.data_ptr(), tr.rowmask.data_ptr()
+            ext.S_tiles, ext.invdelta, ext.a0 = tr.S_tiles.data_ptr(), tr.invdelta.data_ptr(), tr.a0.data_ptr()
+        rc = lib.santa_prop_decode_ragged(
+            q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), _dtype_code(q), B, H, KVH, D, L_storage,
+            lens.data_ptr(), mlen, int(S), int(seed) & (2**64 - 1), out.data_ptr(), m_star.data_ptr(),
+            vrows.data_ptr() if want_vrows else None, ws.data_ptr(), ws.numel(), C.byref(ext),
+            torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    res = (out, m_star, vrows)
+    return res + (tr,) if trace else res
+
+
 def lse_combine(partials: torch.Tensor, S_per_tile: int, dtype: torch.dtype):
     """Combine ``partials [G,B,H,130]`` (or ``[G,BH,130]``) fp32 into ``(out [B,H,128], m_star [B,H])``."""
     _check(partials.is_cuda and partials.dtype == torch.float32 and partials.is_contiguous(),

@@ -334,3 +334,76 @@ def test_prop_ragged_batch_properties():
         for kv in range(8):
             ev[4 * kv:4 * kv + 4] = tr.counts[4 * kv:4 * kv + 4].float() @ V[:, kv].float()
         assert close(out, ev / 256)
+
+
+RAGGED_SETS = [
+    ([300, 5000, 1, 777, 4096], 5120, 256, "bf16", 8),
+    ([256, 0, 513], 600, 64, "f16", 2),
+    ([8769, 23132, 11428, 9000], 23132, 256, "bf16", 8),
+]
+
+
+@pytest.mark.parametrize("lengths,Ls,S,dtype,KVH", RAGGED_SETS)
+def test_prop_ragged_entry_equals_per_sequence_calls(lengths, Ls, S, dtype, KVH):
+    """One ragged launch sequence against one 256-row-tile call per sequence (what the reference adapter's
+    loop does, attention_backends.py:491-500): tile statistics, budgets, sampled counts, vrows and m_star
+    bit for bit; outputs in tolerance (the partial sums are added in a different order)."""
+    B, H = len(lengths), 4 * KVH
+    q, K, V = cases.make_qkv(B, Ls, KVH, dtype, 77 + B, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    lens = torch.tensor(lengths, dtype=torch.int32, device=dev())
+    out, m_star, vrows, tr = ops().prop_decode_ragged(q, K, V, lens, S, seed=1690, want_vrows=True, trace=True)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("prop_ragged", dev()) == 0
+    assert out.shape == (B, H, 128) and m_star.shape == (B, H) and vrows.shape == (B, KVH)
+    for b, L in enumerate(lengths):
+        if L == 0:
+            assert (out[b] == 0).all() and (vrows[b] == 0).all()
+            continue
+        o1, m1, v1, t1 = ops().prop_decode(q[b], K[b, :L].contiguous(), V[b, :L].contiguous(), S, seed=1690,
+                                           block_n=256, want_vrows=True, trace=True)
+        T = t1.T_c
+        assert bits_eq(tr.m_tiles[b, :, :T], t1.m_tiles) and bits_eq(tr.ell_tiles[b, :, :T], t1.ell_tiles)
+        assert torch.equal(tr.u16[b, :, :L], t1.u16)
+        assert torch.equal(tr.S_tiles[b, :, :T], t1.S_tiles)
+        assert bits_eq(tr.invdelta[b, :, :T], t1.invdelta) and bits_eq(tr.a0[b, :, :T], t1.a0)
+        assert torch.equal(tr.counts[b, :, :L], t1.counts)
+        assert (tr.counts[b, :, L:] == 0).all()
+        assert torch.equal(tr.rowmask[b, :, :L], t1.rowmask)
+        assert bits_eq(m_star[b], m1) and torch.equal(vrows[b], v1)
+        assert close(out[b], o1)
+    # lengths live on the device: changing them changes the next call without any host-side re-planning
+    if B > 1 and lengths[0] > 1:
+        lens2 = lens.clone()
+        lens2[0] = lengths[0] - 1
+        out2 = ops().prop_decode_ragged(q, K, V, lens2, S, seed=1690)[0]
+        o1 = ops().prop_decode(q[0], K[0, :lengths[0] - 1].contiguous(), V[0, :lengths[0] - 1].contiguous(), S,
+                               seed=1690, block_n=256)[0]
+        assert close(out2[0], o1)
+        assert torch.equal(out2[1:], out[1:])
+
+
+def test_prop_ragged_module_function():
+    import santa_b200
+    santa_b200.enable_dropin()
+    import santa_prop_batch_cuda as mod
+    assert not hasattr(mod, "decode_systematic_batched")
+    lengths = [4000, 3500, 6000]
+    q, K, V = cases.make_qkv(3, 6000, 8, "bf16", 41, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    lens = torch.tensor(lengths, dtype=torch.int32)
+    o = mod.decode_systematic_ragged(q, K, V, lens, 256, seed=7, want_vrows=True)   # host lengths are copied over
+    o_dev = mod.decode_systematic_ragged(q, K, V, lens.to(dev()), 256, seed=7, want_vrows=True, max_len=6000)
+    assert torch.equal(o[0], o_dev[0]) and torch.equal(o[1], o_dev[1]) and torch.equal(o[2], o_dev[2])
+    o2 = ops().prop_decode_ragged(q, K, V, lengths, 256, seed=7, want_vrows=True)
+    assert torch.equal(o[0], o2[0]) and torch.equal(o[2], o2[2])
+    for b, L in enumerate(lengths):
+        ob = mod.decode_systematic_scalar(q[b].contiguous(), K[b, :L].contiguous(), V[b, :L].contiguous(), 256,
+                                          seed=7, want_vrows=True)
+        assert close(o[0][b], ob[0]) and torch.equal(o[1][b], ob[1]) and torch.equal(o[2][b], ob[2])
+    with pytest.raises(RuntimeError, match="Ragged path expects"):
+        mod.decode_systematic_ragged(q[0], K, V, lens, 256)
+    with pytest.raises(RuntimeError, match="one length per sequence"):
+        mod.decode_systematic_ragged(q, K, V, lens[:2], 256)
+    with pytest.raises(RuntimeError, match="max_len exceeds"):
+        mod.decode_systematic_ragged(q, K, V, lens, 256, max_len=7000)
