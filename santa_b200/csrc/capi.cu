@@ -362,7 +362,8 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
   sp.status = reinterpret_cast<int*>(ws);
   sp.m_tiles = (ext && ext->m_tiles) ? ext->m_tiles : reinterpret_cast<float*>(ws + pl.off_m);
   sp.ell_tiles = (ext && ext->ell_tiles) ? ext->ell_tiles : reinterpret_cast<float*>(ws + pl.off_ell);
-  sp.stash = (ext && ext->u16) ? ext->u16 : reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  sp.stash = reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  sp.dbg_u = ext ? ext->u16 : nullptr;
   p.K = K;
   p.block_n = pl.block_n;
   p.T_c = pl.T_c;
@@ -425,7 +426,8 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
   sp.status = reinterpret_cast<int*>(ws);
   sp.m_tiles = (ext && ext->m_tiles) ? ext->m_tiles : reinterpret_cast<float*>(ws + pl.off_m);
   sp.ell_tiles = (ext && ext->ell_tiles) ? ext->ell_tiles : reinterpret_cast<float*>(ws + pl.off_ell);
-  sp.stash = (ext && ext->u16) ? ext->u16 : reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  sp.stash = reinterpret_cast<uint16_t*>(ws + pl.off_stash);
+  sp.dbg_u = ext ? ext->u16 : nullptr;
   p.K = K;
   p.block_n = 256;
   p.T_c = pl.T_max;

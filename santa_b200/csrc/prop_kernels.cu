@@ -61,7 +61,8 @@ struct MmaOp<__half> {
 template <typename TK>
 __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __restrict__ K, int H, int KVH, int L,
                                       int bn, int T_c, float q_scale, float* __restrict__ m_tiles,
-                                      float* __restrict__ ell_tiles, uint16_t* __restrict__ stash) {
+                                      float* __restrict__ ell_tiles, uint16_t* __restrict__ stash,
+                                      uint16_t* __restrict__ dbg_u) {
   extern __shared__ float smf[];
   const int t = blockIdx.x, kv = blockIdx.y;
   const int NWARP = blockDim.x >> 5;
@@ -127,7 +128,9 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
         if (n < L) {
           const float u = __expf(Ct[lane * 16 + j] - mr);
           ep = __fadd_rn(ep, u);
-          stash[size_t(h) * L + n] = Store16<TK>::bits(u);
+          const uint16_t ub = Store16<TK>::bits(u);
+          stash[(size_t(kv) * L + n) * kGH + lane] = ub;  // [kv][row][head of the group]
+          if (dbg_u != nullptr) dbg_u[size_t(h) * L + n] = ub;
         }
       }
     }
@@ -296,11 +299,12 @@ struct Pass2Params {
 };
 
 constexpr int kPass2Warps = 8;
+constexpr int kPass2CtasPerSm = 2;  // resident CTAs per SM (register-limited)
 
 // One warp per (kv-head, tile range): counts from the stash, compaction,
 // sparse V sum (santa_cuda_kernel.cu:771-863), tiles in ascending order.
 template <typename TK>
-__global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass2Params p) {
+__global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_kernel(const Pass2Params p) {
   __shared__ __align__(16) float4 s_buf[kPass2Warps][kMaxTileRows];
   __shared__ int s_start[kMaxRaggedSeqs + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -350,36 +354,36 @@ __global__ void __launch_bounds__(kPass2Warps * 32) prop_pass2_kernel(const Pass
 
 #pragma unroll 1
     for (int t = t_lo; t < t_hi; ++t) {
-      const int n0 = t * p.bn;
-      const int tile_len = (L_b - n0 < p.bn) ? (L_b - n0) : p.bn;
-      const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
-      const size_t ls = size_t(p.len_stride);
-#pragma unroll 1
-      for (int ch = 0; ch < nch; ++ch) {
-        const int r = ch * kChunkRows + lane;
-        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < tile_len) {
-          const uint16_t* sp = p.stash + bh0 * ls + n0 + r;
-          const uint32_t w01 = uint32_t(__ldcg(sp)) | (uint32_t(__ldcg(sp + ls)) << 16);
-          const uint32_t w23 = uint32_t(__ldcg(sp + 2 * ls)) | (uint32_t(__ldcg(sp + 3 * ls)) << 16);
-          const float2 f01 = Store16<TK>::unpack(w01), f23 = Store16<TK>::unpack(w23);
-          u = make_float4(f01.x, f01.y, f23.x, f23.y);
-        }
-        sb[r] = u;
-      }
-      __syncwarp();
       float invdel[kGH], a0[kGH];
 #pragma unroll
-      for (int g = 0; g < kGH; ++g) {
-        invdel[g] = __ldcg(p.invdelta + (bh0 + g) * p.tile_stride + t);
-        a0[g] = __ldcg(p.a0 + (bh0 + g) * p.tile_stride + t);
+      for (int g = 0; g < kGH; ++g) invdel[g] = __ldcg(p.invdelta + (bh0 + g) * p.tile_stride + t);
+      // a tile without budget on any of its four heads samples nothing: every count is zero
+      if (!(invdel[0] > 0.f || invdel[1] > 0.f || invdel[2] > 0.f || invdel[3] > 0.f)) continue;
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) a0[g] = __ldcg(p.a0 + (bh0 + g) * p.tile_stride + t);
+      const int n0 = t * p.bn;
+      const int tile_len = (L_b - n0 < p.bn) ? (L_b - n0) : p.bn;
+      const size_t ls = size_t(p.len_stride);
+      // the tile's rounded weights: one 8-byte word per row, all loads in flight together
+      const uint2* sp = reinterpret_cast<const uint2*>(p.stash) + (size_t(b) * p.KVH + kv) * ls + n0;
+      uint2 w[kMaxTileRows / kChunkRows];
+#pragma unroll
+      for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
+        const int r = ch * kChunkRows + lane;
+        w[ch] = (r < tile_len) ? __ldcg(sp + r) : make_uint2(0u, 0u);
       }
+#pragma unroll
+      for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
+        const float2 f01 = Store16<TK>::unpack(w[ch].x), f23 = Store16<TK>::unpack(w[ch].y);
+        sb[ch * kChunkRows + lane] = make_float4(f01.x, f01.y, f23.x, f23.y);
+      }
+      __syncwarp();
       RowTrace tr;
       tr.head_stride = ls;
       tr.u16 = nullptr;
       tr.counts = p.dbg_c ? p.dbg_c + bh0 * ls + n0 : nullptr;
       tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * ls + n0 : nullptr;
-      const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
+      const int n_emit = tile_counts<TK, true>(sb, tile_len, lane, invdel, a0, tr);
       vrow_count += n_emit;
       float o[kGH][4];
 #pragma unroll
@@ -555,7 +559,7 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
     const size_t smem = size_t(nwarp * 256 + 2 * 16 * nwarp + 16) * sizeof(float);
     prop_pass1_mma_kernel<TK><<<dim3(p.T_c, KVH), nwarp * 32, smem, stream>>>(
         static_cast<const TK*>(p.sp.q), static_cast<const TK*>(p.K), H, KVH, L, p.block_n, p.T_c, p.sp.q_scale,
-        p.sp.m_tiles, p.sp.ell_tiles, p.sp.stash);
+        p.sp.m_tiles, p.sp.ell_tiles, p.sp.stash, p.sp.dbg_u);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -587,7 +591,7 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   p2.ws.items = (long long)nseq * KVH * p.T_c;  // ragged: an upper bound, the kernels count the real items
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long max_warps = (long long)sms * 4 * kPass2Warps;
+  const long long max_warps = (long long)prop_pass2_max_groups(sms);
   p2.ws.nvg = int(p2.ws.items < max_warps ? p2.ws.items : max_warps);
   p2.partials = p.partials;
   p2.partial_vrows = p.partial_vrows;
@@ -618,6 +622,6 @@ cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t s
 }
 
 // Upper bound on pass-2 warps for workspace sizing (must match launch_prop_t).
-int prop_pass2_max_groups(int sms) { return sms * 4 * kPass2Warps; }
+int prop_pass2_max_groups(int sms) { return sms * kPass2CtasPerSm * kPass2Warps; }
 
 }  // namespace santa

@@ -120,7 +120,9 @@ struct RowTrace {
 // counts, row index within the tile) describes the i-th gathered row in
 // ascending row order and lands on row i, which has been consumed by then.
 // Returns the number of gathered rows.
-template <typename TK>
+// ROUNDED: sb already holds values of the storage type (Prop's second pass reads them from the
+// stash), so the rounding step is skipped.
+template <typename TK, bool ROUNDED = false>
 __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, const float (&invdel)[kGH],
                                            const float (&a0)[kGH], const RowTrace& tr) {
   const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
@@ -148,8 +150,10 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
     float xA[kGH], xB[kGH], rA[kGH], rB[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
-      xA[g] = (validA && invdel[g] > 0.f) ? __fmul_rn(Store16<TK>::round(uA[g]), invdel[g]) : 0.f;
-      xB[g] = (validB && invdel[g] > 0.f) ? __fmul_rn(Store16<TK>::round(uB[g]), invdel[g]) : 0.f;
+      const float ruA = ROUNDED ? uA[g] : Store16<TK>::round(uA[g]);
+      const float ruB = ROUNDED ? uB[g] : Store16<TK>::round(uB[g]);
+      xA[g] = (validA && invdel[g] > 0.f) ? __fmul_rn(ruA, invdel[g]) : 0.f;
+      xB[g] = (validB && invdel[g] > 0.f) ? __fmul_rn(ruB, invdel[g]) : 0.f;
       rA[g] = xA[g];
       rB[g] = xB[g];
     }

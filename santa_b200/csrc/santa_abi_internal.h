@@ -45,11 +45,11 @@ struct StreamParams {
   // Prop pass 1 outputs / Flash trace ([B,H,T_c]); Flash: may be null
   float* m_tiles;
   float* ell_tiles;
-  // Prop pass 1: rounded tile-local weights, [H][L_valid] 16-bit
+  // Prop pass 1: rounded tile-local weights, [sequence][kv-head][len_stride][4 heads] 16-bit
   uint16_t* stash;
-  // Flash trace (may be null)
-  float* dbg_invdel;  // [B,H,T_c]
-  uint16_t* dbg_u;    // [B,H,L_valid]
+  // trace (may be null)
+  float* dbg_invdel;  // [B,H,T_c]                    (Flash)
+  uint16_t* dbg_u;    // [B,H,len_stride]             (Flash; Prop pass 1: the stash per head)
   int16_t* dbg_c;     // [B,H,L_valid]
   int* rowmask;       // [B,KVH,L_valid]
 };

@@ -194,11 +194,18 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             const int r = ch * kChunkRows + lane;
             if (r < tile_len) {
               const float4 u = sb[r];
-              uint16_t* sp = p.stash + bh0 * p.len_stride + n0 + r;
-              sp[0] = Store16<TK>::bits(u.x);
-              sp[size_t(p.len_stride)] = Store16<TK>::bits(u.y);
-              sp[2 * size_t(p.len_stride)] = Store16<TK>::bits(u.z);
-              sp[3 * size_t(p.len_stride)] = Store16<TK>::bits(u.w);
+              const uint32_t w01 = uint32_t(Store16<TK>::bits(u.x)) | (uint32_t(Store16<TK>::bits(u.y)) << 16);
+              const uint32_t w23 = uint32_t(Store16<TK>::bits(u.z)) | (uint32_t(Store16<TK>::bits(u.w)) << 16);
+              // one 8-byte word per row: the four heads of the group side by side
+              reinterpret_cast<uint2*>(p.stash)[(size_t(b) * p.KVH + kv) * p.len_stride + n0 + r] =
+                  make_uint2(w01, w23);
+              if (p.dbg_u != nullptr) {
+                uint16_t* sp = p.dbg_u + bh0 * p.len_stride + n0 + r;
+                sp[0] = uint16_t(w01 & 0xffffu);
+                sp[size_t(p.len_stride)] = uint16_t(w01 >> 16);
+                sp[2 * size_t(p.len_stride)] = uint16_t(w23 & 0xffffu);
+                sp[3 * size_t(p.len_stride)] = uint16_t(w23 >> 16);
+              }
             }
           }
           __syncwarp();
