@@ -150,6 +150,35 @@ SANTA_API int santa_flash_decode_noalloc(const void* q, const void* K, const voi
                                int D, int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
                                float* m_star, int32_t* vrows, const santa_flash_ext* ext, void* stream);
 
+/* Bytes of workspace santa_flash_decode_ragged needs on the current device (0 on bad arguments). */
+SANTA_API size_t santa_flash_ragged_workspace_bytes(int B, int KVH, int max_len, int block_n);
+
+/*
+ * S2ANTA-Flash decode attention with PER-SEQUENCE LENGTHS READ FROM DEVICE MEMORY.  No counterpart
+ * in the reference, whose entry point takes one host-side valid_len for the whole batch
+ * (F.cpp:188-191): this is the variant for a decode step captured once in a CUDA graph and replayed
+ * while the cache grows -- the step before it (tutorial_code/runtime_common.py:551-557) bumps the
+ * lengths on the device -- and for batches whose sequences differ in length.
+ * Sequence b gets exactly the result of santa_flash_decode on that sequence alone with
+ * L_valid = seq_lens[b], the same block_n and ext.batch_offset = batch_offset + b (the random stream
+ * is keyed by b*H + h, F.cu:281); with all lengths equal to L it therefore equals the uniform call
+ * with valid_len = L.  The per-tile budget max(1, S / ceil(len_b / block_n)) follows each length.
+ *
+ *   seq_lens [B] int32 in DEVICE memory, read when the kernels run; clamped to [0, max_len]
+ *   max_len  host-side bound, 0 < max_len <= L_storage; sizes the workspace
+ *   block_n  32, 64 or 256; <= 0 applies the reference's rule to max_len.  The host cannot see
+ *            the lengths, so a caller that wants the rule's tile size re-plans (and re-captures)
+ *            when its lengths cross 1536 / 3072.
+ * Other arguments as santa_flash_decode (out is required).  A sequence of length 0 yields a zero
+ * output row.  B <= 1024.  Of `ext` only batch_offset and the trace arrays may be set; the trace
+ * arrays are laid out [B,H,ceil(max_len/block_n)] and [B,H,max_len] (rowmask [B,KVH,max_len]).
+ */
+SANTA_API int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH,
+                                        int D, int L_storage, const int32_t* seq_lens, int max_len, int64_t S,
+                                        uint64_t seed, int block_n, void* out, float* m_star, int32_t* vrows,
+                                        void* workspace, size_t workspace_bytes, const santa_flash_ext* ext,
+                                        void* stream);
+
 /* ---- Prop decode ----------------------------------------------------------- */
 
 typedef struct santa_prop_ext {

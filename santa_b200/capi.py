@@ -78,6 +78,8 @@ EXPORTS = (
     "santa_flash_decode_noalloc",
     "santa_prop_ragged_workspace_bytes",
     "santa_prop_decode_ragged",
+    "santa_flash_ragged_workspace_bytes",
+    "santa_flash_decode_ragged",
 )
 
 
@@ -121,6 +123,17 @@ def lib() -> C.CDLL:
             C.c_int64, C.c_uint64, C.c_int,  # S seed block_n
             C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
             C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
+        ]
+    if hasattr(L, "santa_flash_decode_ragged"):
+        L.santa_flash_ragged_workspace_bytes.restype = C.c_size_t
+        L.santa_flash_ragged_workspace_bytes.argtypes = [C.c_int] * 4
+        L.santa_flash_decode_ragged.restype = C.c_int
+        L.santa_flash_decode_ragged.argtypes = [
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,  # q K V dtype
+            C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,  # B H KVH D L_storage
+            C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_int,  # seq_lens max_len S seed block_n
+            C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
+            C.c_void_p, C.c_size_t, C.POINTER(FlashExt), C.c_void_p,
         ]
     if hasattr(L, "santa_prop_decode_ragged"):
         L.santa_prop_ragged_workspace_bytes.restype = C.c_size_t

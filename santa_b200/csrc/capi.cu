@@ -164,6 +164,28 @@ int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPla
   return SANTA_OK;
 }
 
+// Ragged Flash batch: planned for the length bound; column groups stay inside a sequence.
+int plan_flash_ragged(int B, int KVH, int max_len, int block_n, FlashPlan* pl) {
+  if (B <= 0 || KVH <= 0) return SANTA_E_SHAPE;
+  if (B > santa::kMaxRaggedSeqs) return SANTA_E_TOO_LARGE;
+  if (max_len <= 0) return SANTA_E_LENGTH;
+  const int bn = santa_block_n_rule(max_len, block_n);
+  if (bn != 32 && bn != 64 && bn != 256) return SANTA_E_BLOCK_N;
+  int sms = 0;
+  if (int rc = sm_count_of_current_device(&sms)) return rc;
+  if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
+  pl->block_n = bn;
+  pl->T_c = (max_len + bn - 1) / bn;
+  if ((long long)B * KVH * pl->T_c >= (1LL << 31)) return SANTA_E_TOO_LARGE;
+  pl->ws = make_split(B * KVH, pl->T_c, sms, &pl->grid, KVH);
+  const size_t ncg = size_t(B) * (KVH / pl->ws.gw);
+  const size_t slots = (size_t(pl->ws.nvg) + ncg) * pl->ws.gw;
+  pl->off_pvrows = 256;
+  pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
+  pl->total = pl->off_partials + slots * santa::kGH * santa::kPartialStride * sizeof(float);
+  return SANTA_OK;
+}
+
 // Ragged Prop batch: tables and the stash are laid out for the length bound, [B,H,T_max] and
 // [B,H,max_len]; the work split assumes every sequence as long as the bound (the kernels count
 // the real items).
@@ -295,6 +317,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   p.len_stride = L_valid;
   p.ws = pl.ws;
   p.S_per_tile = spt;
+  p.S_total = 0;
   p.q_scale = 1.0f / std::sqrt((float)D);  // F.cpp:210
   p.seed = seed;
   p.batch_offset = ext ? ext->batch_offset : 0;
@@ -321,6 +344,85 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   mp.m_star = m_star;
   mp.vrows = vrows;
   mp.partial_out = want_partial ? ext->partial_out : nullptr;
+
+  cudaError_t e = santa::launch_flash(p, mp, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+size_t santa_flash_ragged_workspace_bytes(int B, int KVH, int max_len, int block_n) {
+  FlashPlan pl;
+  if (plan_flash_ragged(B, KVH, max_len, block_n, &pl) != SANTA_OK) return 0;
+  return pl.total;
+}
+
+int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
+                              int L_storage, const int32_t* seq_lens, int max_len, int64_t S, uint64_t seed,
+                              int block_n, void* out, float* m_star, int32_t* vrows, void* workspace,
+                              size_t workspace_bytes, const santa_flash_ext* ext, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!q || !K || !V || !out || !seq_lens) return SANTA_E_ARG;
+  if (D != santa::kD || KVH <= 0 || H != santa::kGH * KVH || B <= 0) return SANTA_E_SHAPE;
+  if (max_len <= 0 || max_len > L_storage) return SANTA_E_LENGTH;
+  if (ext && (ext->tile_offset != 0 || ext->s_per_tile_override >= 0 || ext->partial_out != nullptr))
+    return SANTA_E_ARG;  // the sequence-sharding extensions belong to the uniform entry point
+  if (ext && ((ext->u16 == nullptr) != (ext->counts == nullptr))) return SANTA_E_ARG;
+  if (ext && ((ext->m_tiles == nullptr) != (ext->ell_tiles == nullptr))) return SANTA_E_ARG;
+  if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
+
+  FlashPlan pl;
+  if (int rc = plan_flash_ragged(B, KVH, max_len, block_n, &pl)) return rc;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
+    return SANTA_E_WORKSPACE;
+  const int S32 = S > 2147483647LL ? 2147483647 : (S < 0 ? 0 : int(S));
+
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  santa::StreamParams p{};
+  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH)) return rc;
+  p.q = q;
+  p.V = V;
+  p.H = H;
+  p.KVH = KVH;
+  p.L_valid = max_len;
+  p.L_storage = L_storage;
+  p.seq_lens = seq_lens;
+  p.nseq = B;
+  p.tile_stride = pl.T_c;
+  p.len_stride = max_len;
+  p.ws = pl.ws;
+  p.S_per_tile = 0;
+  p.S_total = S32;
+  p.q_scale = 1.0f / std::sqrt((float)D);  // F.cpp:210
+  p.seed = seed;
+  p.batch_offset = ext ? ext->batch_offset : 0;
+  p.tile_offset = 0;
+  p.status = reinterpret_cast<int*>(ws);
+  p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
+  p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.m_tiles = ext ? ext->m_tiles : nullptr;
+  p.ell_tiles = ext ? ext->ell_tiles : nullptr;
+  p.stash = nullptr;
+  p.dbg_invdel = (ext && ext->m_tiles) ? ext->invdel : nullptr;
+  p.dbg_u = ext ? ext->u16 : nullptr;
+  p.dbg_c = ext ? ext->counts : nullptr;
+  p.rowmask = ext ? ext->rowmask : nullptr;
+
+  santa::FlashMergeParams mp{};
+  mp.H = H;
+  mp.KVH = KVH;
+  mp.S_per_tile = 0;
+  mp.seq_lens = seq_lens;
+  mp.nseq = B;
+  mp.max_len = max_len;
+  mp.bn = pl.block_n;
+  mp.S_total = S32;
+  mp.ws = pl.ws;
+  mp.partials = p.partials;
+  mp.partial_vrows = p.partial_vrows;
+  mp.out = out;
+  mp.m_star = m_star;
+  mp.vrows = vrows;
+  mp.partial_out = nullptr;
 
   cudaError_t e = santa::launch_flash(p, mp, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);

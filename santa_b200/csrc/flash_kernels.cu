@@ -34,24 +34,58 @@ namespace santa {
 //   out = A / (Z * S_per_tile)            (reference :436-468 over all tiles)
 template <typename TK>
 __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams p) {
-  cudaGridDependencySynchronize();
   __shared__ float s_w[kMaxCtas * kGroupWarps];
   __shared__ float s_red[4];
   __shared__ int s_redi[4];
+  __shared__ int s_before[4], s_total[4];
   __shared__ float4 s_acc[4][32];
 
   const int col = blockIdx.x >> 2;
   const int g = blockIdx.x & 3;
   const int gw = p.ws.gw;
-  const int cg = col / gw;
-  const int w = col - cg * gw;
-  const int T_c = p.ws.T_c;
   const int b = col / p.KVH;
   const int kv = col - b * p.KVH;
   const int tid = threadIdx.x, lane = tid & 31, wq = tid >> 5;
+  int cg = col / gw;
+  const int w = col - cg * gw;
+  int T_c = p.ws.T_c, spt = p.S_per_tile, nvg = p.ws.nvg;
+  long long items = p.ws.items, item0 = (long long)cg * T_c;
+  if (p.seq_lens != nullptr) {
+    // ragged batch: column groups never span sequences; the items of the sequences before this one
+    // come first (the lengths are inputs of the call, so they may be read before the producer ends)
+    int before = 0, total = 0;
+    for (int i = tid; i < p.nseq; i += 128) {
+      const int t = (ragged_len(p.seq_lens, i, p.max_len) + p.bn - 1) / p.bn;
+      total += t;
+      before += (i < b) ? t : 0;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      before += __shfl_xor_sync(0xffffffffu, before, off);
+      total += __shfl_xor_sync(0xffffffffu, total, off);
+    }
+    if (lane == 0) {
+      s_before[wq] = before;
+      s_total[wq] = total;
+    }
+    __syncthreads();
+    before = (s_before[0] + s_before[1]) + (s_before[2] + s_before[3]);
+    total = (s_total[0] + s_total[1]) + (s_total[2] + s_total[3]);
+    const int gps = p.KVH / gw, cgs = kv / gw;
+    T_c = (ragged_len(p.seq_lens, b, p.max_len) + p.bn - 1) / p.bn;
+    spt = (p.S_total > 0 && T_c > 0) ? (p.S_total / T_c > 1 ? p.S_total / T_c : 1) : 0;
+    cg = b * gps + cgs;
+    items = (long long)total * gps;
+    nvg = (items < (long long)nvg) ? int(items) : nvg;
+    item0 = ((long long)before * gps) + (long long)cgs * T_c;
+  }
+  cudaGridDependencySynchronize();
 
-  const int v_first = cta_of_item((long long)cg * T_c, p.ws.items, p.ws.nvg);
-  const int v_last = cta_of_item((long long)(cg + 1) * T_c - 1, p.ws.items, p.ws.nvg);
+  int v_first = 0, v_last = -1;  // an empty sequence has no partials
+  if (T_c > 0) {
+    v_first = cta_of_item(item0, items, nvg);
+    v_last = cta_of_item(item0 + T_c - 1, items, nvg);
+  }
   const int nv = v_last - v_first + 1;
   auto partial = [&](int v) {
     return p.partials + ((size_t(v + cg) * gw + w) * kGH + g) * kPartialStride;
@@ -134,7 +168,7 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
       }
     }
     if (p.out != nullptr) {
-      const float inv = (p.S_per_tile > 0 && zs > 0.f) ? 1.0f / (zs * (float)p.S_per_tile) : 0.f;
+      const float inv = (spt > 0 && zs > 0.f) ? 1.0f / (zs * (float)spt) : 0.f;
       TK* op = static_cast<TK*>(p.out) + bh * kD + 4 * lane;
       uint2 wv;
       wv.x = uint32_t(Store16<TK>::bits(acc.x * inv)) | (uint32_t(Store16<TK>::bits(acc.y * inv)) << 16);
@@ -154,12 +188,18 @@ static cudaError_t launch_one(const StreamParams& p, const FlashMergeParams& mp,
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(stream_kernel<TK, BN, kModeFlash>,
+    cudaError_t e = cudaFuncSetAttribute(stream_kernel<TK, BN, kModeFlash, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(stream_kernel<TK, BN, kModeFlash, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kStreamSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  stream_kernel<TK, BN, kModeFlash><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p);
+  if (p.seq_lens != nullptr)
+    stream_kernel<TK, BN, kModeFlash, true><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p);
+  else
+    stream_kernel<TK, BN, kModeFlash, false><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 

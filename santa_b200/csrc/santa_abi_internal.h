@@ -27,7 +27,8 @@ struct StreamParams {
   int H, KVH;
   int L_valid, L_storage;
   WorkSplit ws;
-  int S_per_tile;  // Flash: fixed per-tile budget
+  int S_per_tile;  // Flash: fixed per-tile budget (uniform batch)
+  int S_total;     // Flash, ragged batch: S; the per-tile budget max(1, S / T_b) follows each length
   float q_scale;
   uint64_t seed;
   int batch_offset, tile_offset;
@@ -56,6 +57,9 @@ struct StreamParams {
 
 struct FlashMergeParams {
   int H, KVH, S_per_tile;
+  // ragged batch: device lengths (else null), their bound, the tile size and S
+  const int* seq_lens;
+  int nseq, max_len, bn, S_total;
   WorkSplit ws;
   const float* partials;
   const int* partial_vrows;

@@ -210,10 +210,13 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           }
           __syncwarp();
         }
+        // Flash budget rule (santa_cuda.cpp:202-208); a ragged batch applies it to each length
+        const int spt = (RAGGED && MODE == kModeFlash) ? (p.S_total > 0 ? (p.S_total / T_b > 1 ? p.S_total / T_b : 1) : 0)
+                                                       : p.S_per_tile;
         float invdel[kGH];
 #pragma unroll
         for (int g = 0; g < kGH; ++g)
-          invdel[g] = (p.S_per_tile > 0 && ell[g] > 1e-20f) ? ((float)p.S_per_tile / ell[g]) : 0.0f;
+          invdel[g] = (spt > 0 && ell[g] > 1e-20f) ? ((float)spt / ell[g]) : 0.0f;
         if (p.m_tiles != nullptr && lane < kGH) {
           float mv = m[0], ev = ell[0], iv = invdel[0];
 #pragma unroll

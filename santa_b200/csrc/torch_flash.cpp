@@ -133,9 +133,55 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
   return std::make_tuple(out, m_star, vrows);
 }
 
+// Per-sequence lengths from a device tensor; not part of the reference module (its entry point
+// takes one host-side valid_len, santa_cuda.cpp:188-191).  Nothing on the host depends on the
+// lengths' values, so a captured CUDA graph of this call follows lengths that change between replays.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tensor q_h, at::Tensor K_g,
+                                                                        at::Tensor V_g, at::Tensor seq_lens,
+                                                                        int64_t S, uint64_t seed, int64_t block_n,
+                                                                        bool want_vrows, int64_t max_len) {
+  const ShapeInfo info = check_inputs(q_h, K_g, V_g);
+  SANTA_CHECK(info.batched, "Ragged path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
+  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
+  SANTA_CHECK(D == 128, "This build supports only D=128. Got D=", D);
+  SANTA_CHECK(H % KVH == 0 && H / KVH == 4, "This build supports only GH=4 (H/KVH). Got H=", H, " KVH=", KVH);
+  SANTA_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.dim() == 1 && seq_lens.size(0) == B,
+              "seq_lens must be an int32 tensor with one length per sequence");
+  const int mlen = max_len > 0 ? (int)max_len : L_storage;
+  SANTA_CHECK(mlen <= L_storage, "max_len exceeds storage length: max_len=", mlen, " storage=", L_storage);
+  SANTA_CHECK(B <= 1024, "The ragged path takes at most 1024 sequences. Got B=", B);
+  const int bn = santa_block_n_rule(mlen, (int)block_n);
+  SANTA_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
+
+  const c10::cuda::CUDAGuard guard(q_h.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_h.contiguous();
+  at::Tensor lens = seq_lens.is_cuda() ? seq_lens.contiguous() : seq_lens.to(q.device(), /*non_blocking=*/false);
+  SANTA_CHECK(lens.device() == q.device(), "seq_lens must be on q_h's device or on the CPU");
+
+  at::Tensor out = at::empty({B, H, D}, q.options());
+  at::Tensor m_star = at::empty({B, H}, q.options().dtype(at::kFloat));
+  at::Tensor vrows = want_vrows ? at::empty({B, KVH}, q.options().dtype(at::kInt))
+                                : at::empty({0}, q.options().dtype(at::kInt));
+  const size_t ws_bytes = santa_flash_ragged_workspace_bytes(B, KVH, mlen, bn);
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  const int rc = santa_flash_decode_ragged(
+      q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16,
+      B, H, KVH, D, L_storage, lens.data_ptr<int>(), mlen, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
+      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), nullptr,
+      (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+  return std::make_tuple(out, m_star, vrows);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
+        py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0,
+        py::arg("want_vrows") = false, py::arg("max_len") = -1);
   m.def("decode_systematic_scalar", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),
         py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1);
   m.def("decode_systematic_batched", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),

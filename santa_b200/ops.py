@@ -145,6 +145,62 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
     return res + (tr,) if trace else res
 
 
+def flash_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, block_n=0, want_vrows=False, *, max_len=None,
+                        batch_offset=0, trace=False):
+    """S2ANTA-Flash decode with per-sequence lengths read from device memory: ``q_bh [B,H,D]``,
+    ``K_g/V_g [B,L_storage,KVH,D]``, ``seq_lens`` int32 ``[B]`` (a CPU tensor or list is copied over).
+    Sequence ``b`` gets the result of ``flash_decode`` on it alone with ``valid_len=len_b``, the same
+    ``block_n`` and ``batch_offset + b``.  ``block_n <= 0`` applies the tile-size rule to ``max_len``
+    (default: the storage length).  Returns ``(out, m_star, vrows)`` (+ ``FlashTrace`` with arrays laid
+    out for ``max_len``)."""
+    batched, B, H, D, L_storage, KVH = _check_flash_inputs(q_bh, K_g, V_g)
+    _check(batched, "Ragged path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]")
+    if seed < 0:
+        raise TypeError("seed must be a non-negative 64-bit integer")
+    q = q_bh.contiguous()
+    _check(D == 128, f"This build supports only D=128. Got D={D}")
+    _check(H % KVH == 0 and H // KVH == 4, f"This build supports only GH=4 (H/KVH). Got H={H} KVH={KVH}")
+    dev = q.device
+    if not isinstance(seq_lens, torch.Tensor):
+        seq_lens = torch.tensor(list(seq_lens), dtype=torch.int32)
+    _check(seq_lens.numel() == B, "seq_lens must hold one length per sequence")
+    lens = seq_lens.to(device=dev, dtype=torch.int32).contiguous()
+    mlen = L_storage if max_len is None else int(max_len)
+    _check(0 < mlen <= L_storage, f"max_len must be in (0, storage length]; got {mlen} (storage {L_storage})")
+    bn = capi.block_n_rule(mlen, int(block_n))
+    _check(bn in (32, 64, 256), f"block_n must be 0 (auto) or one of {{32,64,256}}. Got block_n={bn}")
+    T_max = (mlen + bn - 1) // bn
+    with torch.cuda.device(dev):
+        lib = capi.lib()
+        nbytes = lib.santa_flash_ragged_workspace_bytes(B, KVH, mlen, bn)
+        _check(nbytes > 0, "santa_b200: unsupported ragged problem (B must be 1..1024)")
+        ws = _workspace("flash_ragged", dev, nbytes)
+        fopt = dict(device=dev, dtype=torch.float32)
+        out = torch.empty((B, H, D), device=dev, dtype=q.dtype)
+        m_star = torch.empty((B, H), **fopt)
+        vrows = torch.empty((B, KVH) if want_vrows else (0,), device=dev, dtype=torch.int32)
+        ext = capi.FlashExt(batch_offset=int(batch_offset), tile_offset=0, s_per_tile_override=-1)
+        tr = None
+        if trace:
+            tr = FlashTrace(bn, T_max, -1,
+                            torch.zeros((B, H, T_max), **fopt), torch.zeros((B, H, T_max), **fopt),
+                            torch.zeros((B, H, mlen), device=dev, dtype=torch.int16),
+                            torch.zeros((B, H, mlen), device=dev, dtype=torch.int16),
+                            torch.zeros((B, KVH, mlen), device=dev, dtype=torch.int32),
+                            torch.zeros((B, H, T_max), **fopt))
+            ext.invdel = tr.invdel.data_ptr()
+            ext.m_tiles, ext.ell_tiles = tr.m_tiles.data_ptr(), tr.ell_tiles.data_ptr()
+            ext.u16, ext.counts, ext.rowmask = tr.u16.data_ptr(), tr.counts.data_ptr(), tr.rowmask.data_ptr()
+        rc = lib.santa_flash_decode_ragged(
+            q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), _dtype_code(q), B, H, KVH, D, L_storage,
+            lens.data_ptr(), mlen, int(S), int(seed) & (2**64 - 1), bn, out.data_ptr(), m_star.data_ptr(),
+            vrows.data_ptr() if want_vrows else None, ws.data_ptr(), ws.numel(), C.byref(ext),
+            torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    res = (out, m_star, vrows)
+    return res + (tr,) if trace else res
+
+
 def workspace_status(kind: str, device: torch.device) -> int:
     """Synchronise and read the status word of the scratch used on the current stream."""
     stream = torch.cuda.current_stream(device).cuda_stream

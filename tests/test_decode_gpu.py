@@ -407,3 +407,75 @@ def test_prop_ragged_module_function():
         mod.decode_systematic_ragged(q, K, V, lens[:2], 256)
     with pytest.raises(RuntimeError, match="max_len exceeds"):
         mod.decode_systematic_ragged(q, K, V, lens, 256, max_len=7000)
+
+
+FLASH_RAGGED_SETS = [
+    ([300, 5000, 1, 777, 4096], 5120, 256, "bf16", 8, 256),
+    ([256, 0, 513, 100], 600, 64, "f16", 2, 32),
+    ([2000, 1537, 3072], 3072, 100, "bf16", 4, 64),
+    ([8769, 23132, 11428, 9000], 23132, 256, "bf16", 8, 0),
+]
+
+
+@pytest.mark.parametrize("lengths,Ls,S,dtype,KVH,block_n", FLASH_RAGGED_SETS)
+def test_flash_ragged_entry_equals_per_sequence_calls(lengths, Ls, S, dtype, KVH, block_n):
+    """Lengths from device memory against one uniform call per sequence (valid_len = its length,
+    batch_offset = its index, same tile size): everything bit for bit, the output included -- the
+    partial sums of a sequence are folded in the same order whenever its tiles are split the same way,
+    and in tolerance otherwise."""
+    B, H = len(lengths), 4 * KVH
+    q, K, V = cases.make_qkv(B, Ls, KVH, dtype, 91 + B, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    lens = torch.tensor(lengths, dtype=torch.int32, device=dev())
+    out, m_star, vrows, tr = ops().flash_decode_ragged(q, K, V, lens, S, seed=1690, block_n=block_n,
+                                                       want_vrows=True, trace=True)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("flash_ragged", dev()) == 0
+    bn = tr.block_n
+    for b, L in enumerate(lengths):
+        if L == 0:
+            assert (out[b] == 0).all() and (vrows[b] == 0).all()
+            continue
+        o1, m1, v1, t1 = ops().flash_decode(q[b:b + 1], K[b:b + 1], V[b:b + 1], S, seed=1690, block_n=bn,
+                                            want_vrows=True, valid_len=L, batch_offset=b, trace=True)
+        T = t1.T_c
+        assert bits_eq(tr.m_tiles[b, :, :T], t1.m_tiles[0]) and bits_eq(tr.ell_tiles[b, :, :T], t1.ell_tiles[0])
+        assert bits_eq(tr.invdel[b, :, :T], t1.invdel[0])
+        assert torch.equal(tr.u16[b, :, :L], t1.u16[0]) and torch.equal(tr.counts[b, :, :L], t1.counts[0])
+        assert (tr.counts[b, :, L:] == 0).all()
+        assert torch.equal(tr.rowmask[b, :, :L], t1.rowmask[0])
+        assert bits_eq(m_star[b], m1[0]) and torch.equal(vrows[b], v1[0])
+        assert close(out[b], o1[0])
+
+
+def test_flash_ragged_equal_lengths_is_the_uniform_call_and_graph_replay_follows_lengths():
+    import santa_b200
+    santa_b200.enable_dropin()
+    import santa_flash_batch_cuda as mod
+    B, Ls, L = 4, 9000, 8000
+    q, K, V = cases.make_qkv(B, Ls, 8, "bf16", 55, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    lens = torch.full((B,), L, dtype=torch.int32, device=dev())
+    o_u = mod.decode_systematic_batched(q, K, V, 256, seed=3, want_vrows=True, valid_len=L)
+    o_r = mod.decode_systematic_ragged(q, K, V, lens, 256, seed=3, want_vrows=True)
+    assert bits_eq(o_u[1], o_r[1]) and torch.equal(o_u[2], o_r[2]) and close(o_u[0], o_r[0])
+    # capture once, replay after the lengths changed on the device
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        mod.decode_systematic_ragged(q, K, V, lens, 256, seed=3)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_g = mod.decode_systematic_ragged(q, K, V, lens, 256, seed=3)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(o_g[0], o_r[0])
+    lens += 500            # the cache "grew": same graph, new lengths
+    graph.replay()
+    torch.cuda.synchronize()
+    o_u2 = mod.decode_systematic_batched(q, K, V, 256, seed=3, valid_len=L + 500)
+    assert bits_eq(o_g[1], o_u2[1]) and close(o_g[0], o_u2[0])
+    with pytest.raises(RuntimeError, match="one length per sequence"):
+        mod.decode_systematic_ragged(q, K, V, lens[:2], 256)
