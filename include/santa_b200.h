@@ -254,6 +254,32 @@ SANTA_API int santa_prop_decode_ragged(const void* q, const void* K, const void*
                                        uint64_t seed, void* out, float* m_star, int32_t* vrows, void* workspace,
                                        size_t workspace_bytes, const santa_prop_ext* ext, void* stream);
 
+/* ---- the step in front of the attention call -------------------------------- */
+
+/*
+ * Rotary embedding of the new token's q and k, append of k and v to the cache, packed q -- one
+ * launch.  Replaces the tensor code between the projections and the attention call in the
+ * reference runtime, tutorial_code/runtime_common.py:540-556 (view/transpose/contiguous,
+ * apply_rotary_pos_emb :165-185, kc[:, pos].copy_, vc[:, pos].copy_, q[:, :, 0, :].contiguous()),
+ * with the same three roundings per element: rn(rn(x*cos) + rn(rotate_half(x)*sin)).
+ *
+ *   q_proj [B,H,D], k_proj/v_proj [B,KVH,D]   the projections of ONE new token per sequence
+ *   cos, sin [B,D]                            rotary tables of each sequence's position
+ *   k_cache, v_cache [B,L_storage,KVH,D]      row `position` of every sequence is overwritten
+ *   pos       host position of all sequences, used when pos_dev is NULL (0 <= pos < L_storage)
+ *   pos_dev   [B] int32 positions in DEVICE memory or NULL; read when the kernel runs; a position
+ *             outside [0, L_storage) is skipped (nothing is written for that sequence's k/v) and
+ *             *status, if given, is set to 3
+ *   q_out [B,H,D]                             rotated q, the layout santa_flash_decode reads
+ *   seq_lens_out [B] int32 or NULL            position + 1: the lengths for the *_ragged decode calls
+ *   status  one int32 in device memory or NULL
+ * All tensors in the storage dtype, contiguous, 8-byte aligned; D == 128.
+ */
+SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, const void* cos,
+                                const void* sin, int dtype, int B, int H, int KVH, int D, void* k_cache,
+                                void* v_cache, int L_storage, int pos, const int32_t* pos_dev, void* q_out,
+                                int32_t* seq_lens_out, int32_t* status, void* stream);
+
 /* ---- split-KV combine ------------------------------------------------------- */
 
 /*

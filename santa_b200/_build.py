@@ -32,6 +32,7 @@ UNITS = {
     "flash_kernels.cu": ["--use_fast_math"],
     "prop_kernels.cu": [],
     "combine_kernels.cu": [],
+    "rope_kernels.cu": [],
     "capi.cu": [],
 }
 

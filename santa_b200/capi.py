@@ -80,6 +80,7 @@ EXPORTS = (
     "santa_prop_decode_ragged",
     "santa_flash_ragged_workspace_bytes",
     "santa_flash_decode_ragged",
+    "santa_rope_append",
 )
 
 
@@ -123,6 +124,14 @@ def lib() -> C.CDLL:
             C.c_int64, C.c_uint64, C.c_int,  # S seed block_n
             C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
             C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
+        ]
+    if hasattr(L, "santa_rope_append"):
+        L.santa_rope_append.restype = C.c_int
+        L.santa_rope_append.argtypes = [
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,  # q k v cos sin dtype
+            C.c_int, C.c_int, C.c_int, C.c_int,  # B H KVH D
+            C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,  # k_cache v_cache L_storage pos pos_dev
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,  # q_out seq_lens_out status stream
         ]
     if hasattr(L, "santa_flash_decode_ragged"):
         L.santa_flash_ragged_workspace_bytes.restype = C.c_size_t

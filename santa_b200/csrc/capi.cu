@@ -562,6 +562,38 @@ int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_til
   return SANTA_OK;
 }
 
+int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, const void* cos, const void* sin,
+                      int dtype, int B, int H, int KVH, int D, void* k_cache, void* v_cache, int L_storage, int pos,
+                      const int32_t* pos_dev, void* q_out, int32_t* seq_lens_out, int32_t* status, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!q_proj || !k_proj || !v_proj || !cos || !sin || !k_cache || !v_cache || !q_out) return SANTA_E_ARG;
+  if (D != santa::kD || B <= 0 || H <= 0 || KVH <= 0 || L_storage <= 0) return SANTA_E_SHAPE;
+  if (!pos_dev && (pos < 0 || pos >= L_storage)) return SANTA_E_LENGTH;
+  const void* ptrs[] = {q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, q_out};
+  for (const void* ptr : ptrs)
+    if (reinterpret_cast<uintptr_t>(ptr) & 7u) return SANTA_E_ALIGN;  // 8-byte vector accesses
+  santa::RopeAppendParams p{};
+  p.q_proj = q_proj;
+  p.k_proj = k_proj;
+  p.v_proj = v_proj;
+  p.cos = cos;
+  p.sin = sin;
+  p.B = B;
+  p.H = H;
+  p.KVH = KVH;
+  p.L_storage = L_storage;
+  p.pos = pos;
+  p.pos_dev = pos_dev;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.q_out = q_out;
+  p.seq_lens_out = seq_lens_out;
+  p.status = status;
+  cudaError_t e = santa::launch_rope_append(p, dtype, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
 // ---- no-allocation variant of the Flash decode ---------------------------------------------
 // Scratch for callers that cannot provide a workspace.  In host code this name is only a
 // stand-in for the device array: its device address comes from cudaGetSymbolAddress, once per

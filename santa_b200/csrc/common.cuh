@@ -34,6 +34,7 @@ enum : int {
   kStatusOk = 0,
   kStatusStageTimeout = 1,    // a staged K piece never arrived
   kStatusHandoffTimeout = 2,  // a score buffer was never handed over between the warps of a column
+  kStatusBadPosition = 3,     // an append position outside the cache was skipped
 };
 
 // ---------------------------------------------------------------- RNG

@@ -99,6 +99,24 @@ struct PropParams {
 cudaError_t launch_prop(const PropParams& p, int dtype, int grid, cudaStream_t stream);
 int prop_pass2_max_groups(int sms);
 
+// RoPE of the new token's q/k + append of k/v to the cache + packed q.
+struct RopeAppendParams {
+  const void* q_proj;   // [B,H,128]
+  const void* k_proj;   // [B,KVH,128]
+  const void* v_proj;   // [B,KVH,128]
+  const void* cos;      // [B,128]
+  const void* sin;      // [B,128]
+  int B, H, KVH, L_storage;
+  int pos;              // host position, used when pos_dev is null
+  const int* pos_dev;   // [B] device positions or null
+  void* k_cache;        // [B,L_storage,KVH,128]
+  void* v_cache;
+  void* q_out;          // [B,H,128]
+  int* seq_lens_out;    // [B] or null: position + 1
+  int* status;          // one word or null
+};
+cudaError_t launch_rope_append(const RopeAppendParams& p, int dtype, cudaStream_t stream);
+
 // Cross-device combine of G unnormalised partials [G][BH][130].
 cudaError_t launch_lse_combine(const float* partials, int G, int BH, int S_per_tile, int dtype, void* out,
                                float* m_star, cudaStream_t stream);

@@ -201,6 +201,47 @@ def flash_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, block_n=0, want_vr
     return res + (tr,) if trace else res
 
 
+def rope_append(q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, pos, *, seq_lens_out=None, status=None,
+                q_out=None):
+    """Rotary embedding of one new token's q/k, append of k/v to the NHD caches at ``pos`` and the packed
+    ``q [B,H,D]`` -- one launch for runtime_common.py:540-556 of the reference.  ``q_proj`` is
+    ``[B,H*D]``/``[B,1,H*D]``/``[B,H,D]``, ``k_proj``/``v_proj`` likewise with KVH heads, ``cos``/``sin``
+    ``[B,D]`` or ``[B,1,D]``; ``pos`` is an int or an int32 device tensor ``[B]``.  Returns the rotated q."""
+    B, L_storage, KVH, D = k_cache.shape
+    _check(D == 128, f"This build supports only D=128. Got D={D}")
+    _check(k_cache.shape == v_cache.shape and k_cache.is_contiguous() and v_cache.is_contiguous(),
+           "k_cache/v_cache must be contiguous [B,L,KVH,D] tensors of one shape")
+    _check(q_proj.is_cuda and q_proj.dtype in (torch.bfloat16, torch.float16), "q_proj must be a CUDA bf16/f16 tensor")
+    for t in (k_proj, v_proj, cos, sin, k_cache, v_cache):
+        _check(t.dtype == q_proj.dtype and t.device == q_proj.device, "all tensors must share q_proj's dtype and device")
+    _check(q_proj.size(0) == B and q_proj.numel() % (B * D) == 0, "q_proj must hold [B, H*D] elements")
+    H = q_proj.numel() // (B * D)
+    _check(k_proj.numel() == B * KVH * D and v_proj.numel() == B * KVH * D, "k_proj/v_proj must hold [B, KVH*D] elements")
+    _check(cos.numel() == B * D and sin.numel() == B * D, "cos/sin must hold [B, D] elements")
+    q_proj, k_proj, v_proj = q_proj.contiguous(), k_proj.contiguous(), v_proj.contiguous()
+    cos, sin = cos.contiguous(), sin.contiguous()
+    dev = q_proj.device
+    pos_dev = None
+    if isinstance(pos, torch.Tensor):
+        _check(pos.dtype == torch.int32 and pos.device == dev and pos.numel() == B and pos.is_contiguous(),
+               "pos must be an int or a contiguous int32 tensor [B] on the same device")
+        pos_dev, pos_host = pos, 0
+    else:
+        pos_host = int(pos)
+        _check(0 <= pos_host < L_storage, f"pos out of range: {pos_host} (storage {L_storage})")
+    with torch.cuda.device(dev):
+        if q_out is None:
+            q_out = torch.empty((B, H, D), device=dev, dtype=q_proj.dtype)
+        rc = capi.lib().santa_rope_append(
+            q_proj.data_ptr(), k_proj.data_ptr(), v_proj.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+            _dtype_code(q_proj), B, H, KVH, D, k_cache.data_ptr(), v_cache.data_ptr(), L_storage, pos_host,
+            None if pos_dev is None else pos_dev.data_ptr(), q_out.data_ptr(),
+            None if seq_lens_out is None else seq_lens_out.data_ptr(),
+            None if status is None else status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        capi.check(rc)
+    return q_out
+
+
 def workspace_status(kind: str, device: torch.device) -> int:
     """Synchronise and read the status word of the scratch used on the current stream."""
     stream = torch.cuda.current_stream(device).cuda_stream

@@ -62,3 +62,24 @@ def make_qkv(B, Ls, KVH, dtype, gen_seed, kscale=1.0, heavy=False, GH=4, D=128):
 def bits(t: torch.Tensor) -> np.ndarray:
     """uint16 bit patterns of a bf16/f16 tensor (CPU or CUDA)."""
     return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+# ---- the step in front of the attention call (RoPE of q/k, cache append, packed q) ------------
+ROPE_CASES = {
+    "bf16_B3_pos517": dict(B=3, H=32, KVH=8, L=640, pos=517, dtype="bf16", gen_seed=21),
+    "f16_B2_pos0": dict(B=2, H=8, KVH=2, L=64, pos=0, dtype="f16", gen_seed=22),
+    "bf16_B1_pos40000": dict(B=1, H=32, KVH=8, L=40001, pos=40000, dtype="bf16", gen_seed=23),
+}
+
+
+def make_rope_inputs(c):
+    """Seeded projections of one new token per sequence and caches filled with a marker value."""
+    dt = torch_dtype(c["dtype"])
+    g = torch.Generator().manual_seed(c["gen_seed"])
+    B, H, KVH, D, L = c["B"], c["H"], c["KVH"], 128, c["L"]
+    q_proj = (2.0 * torch.randn(B, H * D, generator=g)).to(dt)
+    k_proj = (2.0 * torch.randn(B, KVH * D, generator=g)).to(dt)
+    v_proj = torch.randn(B, KVH * D, generator=g).to(dt)
+    kc = torch.full((B, L, KVH, D), 0.5, dtype=dt)
+    vc = torch.full((B, L, KVH, D), -0.25, dtype=dt)
+    return q_proj, k_proj, v_proj, kc, vc

@@ -479,3 +479,45 @@ def test_flash_ragged_equal_lengths_is_the_uniform_call_and_graph_replay_follows
     assert bits_eq(o_g[1], o_u2[1]) and close(o_g[0], o_u2[0])
     with pytest.raises(RuntimeError, match="one length per sequence"):
         mod.decode_systematic_ragged(q, K, V, lens[:2], 256)
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_CASES))
+def test_rope_append_matches_reference_golden(name):
+    """The fused RoPE + cache append + q pack launch against what the reference's tensor code produced
+    (runtime_common.py:540-556, golden made by tests/golden/make_golden_rope.py): bit for bit."""
+    from oracle import rope_append as ro
+    c = cases.ROPE_CASES[name]
+    g = np.load(os.path.join(GOLDEN, f"rope_{name}.npz"))
+    dt = cases.torch_dtype(c["dtype"])
+    B, pos = c["B"], c["pos"]
+    q_proj, k_proj, v_proj, kc, vc = cases.make_rope_inputs(c)
+    cos, sin = ro.rope_tables(torch.full((B,), pos), 128, dt)
+    d = dev()
+    kc_d, vc_d = kc.to(d), vc.to(d)
+    q = ops().rope_append(q_proj.to(d), k_proj.to(d), v_proj.to(d), cos.to(d), sin.to(d), kc_d, vc_d, pos)
+    torch.cuda.synchronize()
+    assert (cases.bits(q) == g["ref_q"]).all()
+    assert (cases.bits(kc_d[:, pos]) == g["ref_k_row"]).all()
+    assert (cases.bits(vc_d[:, pos]) == g["ref_v_row"]).all()
+    assert kc_d.float().abs().sum().item() == float(g["ref_k_cache_sum"])
+    # device positions, one per sequence, with the new lengths written for the attention call
+    q_proj, k_proj, v_proj, kc2, vc2 = cases.make_rope_inputs(c)
+    plist = [(pos + 3 * b) % c["L"] for b in range(B)]
+    cos2, sin2 = ro.rope_tables(torch.tensor(plist), 128, dt)
+    q_ref = ro.rope_append_step(q_proj, k_proj, v_proj, cos2, sin2, kc2, vc2, plist)
+    kc_d, vc_d = torch.full_like(kc_d, 0.5), torch.full_like(vc_d, -0.25)
+    lens = torch.zeros(B, dtype=torch.int32, device=d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    q2 = ops().rope_append(q_proj.to(d), k_proj.to(d), v_proj.to(d), cos2.to(d), sin2.to(d), kc_d, vc_d,
+                           torch.tensor(plist, dtype=torch.int32, device=d), seq_lens_out=lens, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(q2.cpu(), q_ref) and torch.equal(kc_d.cpu(), kc2) and torch.equal(vc_d.cpu(), vc2)
+    assert lens.tolist() == [p + 1 for p in plist] and status.item() == 0
+    # a position outside the cache is skipped and reported, nothing is written
+    bad = torch.tensor([c["L"]] * B, dtype=torch.int32, device=d)
+    before = kc_d.clone()
+    ops().rope_append(q_proj.to(d), k_proj.to(d), v_proj.to(d), cos2.to(d), sin2.to(d), kc_d, vc_d, bad, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 3 and torch.equal(kc_d, before)
+    with pytest.raises(RuntimeError, match="pos out of range"):
+        ops().rope_append(q_proj.to(d), k_proj.to(d), v_proj.to(d), cos2.to(d), sin2.to(d), kc_d, vc_d, c["L"])

@@ -224,3 +224,29 @@ def test_merge_of_sharded_partials_equals_unsharded():
     out, m_star = so.merge_partials(parts, full.S_per_tile)
     assert np.abs(out - full.out[0]).max() < 1e-5
     assert (m_star == full.m_star[0]).all()
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_CASES))
+def test_rope_oracle_matches_reference_golden(name):
+    """The written-out roundings of oracle/rope_append.py against the outputs of the reference's own
+    apply_rotary_pos_emb + cache copies (tests/golden/make_golden_rope.py), bit for bit."""
+    from oracle import rope_append as ro
+    c = cases.ROPE_CASES[name]
+    g = np.load(os.path.join(GOLDEN, f"rope_{name}.npz"))
+    dt = cases.torch_dtype(c["dtype"])
+    q_proj, k_proj, v_proj, kc, vc = cases.make_rope_inputs(c)
+    cos, sin = ro.rope_tables(torch.full((c["B"],), c["pos"]), 128, dt)
+    assert (cases.bits(cos) == g["cos"]).all() and (cases.bits(sin) == g["sin"]).all()
+    q = ro.rope_append_step(q_proj, k_proj, v_proj, cos, sin, kc, vc, c["pos"])
+    assert (cases.bits(q) == g["ref_q"]).all()
+    assert (cases.bits(kc[:, c["pos"]]) == g["ref_k_row"]).all()
+    assert (cases.bits(vc[:, c["pos"]]) == g["ref_v_row"]).all()
+    assert kc.float().abs().sum().item() == float(g["ref_k_cache_sum"])   # no other row was touched
+    # per-sequence positions: each sequence equals the single-position step on it alone
+    if c["B"] > 1:
+        q_proj, k_proj, v_proj, kc2, vc2 = cases.make_rope_inputs(c)
+        pos = [(c["pos"] + 3 * b) % c["L"] for b in range(c["B"])]
+        cos2, sin2 = ro.rope_tables(torch.tensor(pos), 128, dt)
+        q2 = ro.rope_append_step(q_proj, k_proj, v_proj, cos2, sin2, kc2, vc2, pos)
+        assert (cases.bits(q2[0]) == g["ref_q"][0]).all()
+        assert (cases.bits(kc2[0, pos[0]]) == g["ref_k_row"][0]).all()
