@@ -264,6 +264,9 @@ SANTA_API int santa_prop_decode_ragged(const void* q, const void* K, const void*
  * with the same three roundings per element: rn(rn(x*cos) + rn(rotate_half(x)*sin)).
  *
  *   q_proj [B,H,D], k_proj/v_proj [B,KVH,D]   the projections of ONE new token per sequence
+ *   q_stride, k_stride, v_stride              elements between consecutive sequences of each projection
+ *                                             (multiples of 4); <= 0 means dense.  Slices of one fused
+ *                                             [B,(H+2*KVH)*D] projection are passed without a copy
  *   cos, sin [B,D]                            rotary tables of each sequence's position
  *   k_cache, v_cache [B,L_storage,KVH,D]      row `position` of every sequence is overwritten
  *   pos       host position of all sequences, used when pos_dev is NULL (0 <= pos < L_storage)
@@ -275,10 +278,11 @@ SANTA_API int santa_prop_decode_ragged(const void* q, const void* K, const void*
  *   status  one int32 in device memory or NULL
  * All tensors in the storage dtype, contiguous, 8-byte aligned; D == 128.
  */
-SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, const void* cos,
-                                const void* sin, int dtype, int B, int H, int KVH, int D, void* k_cache,
-                                void* v_cache, int L_storage, int pos, const int32_t* pos_dev, void* q_out,
-                                int32_t* seq_lens_out, int32_t* status, void* stream);
+SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, int64_t q_stride,
+                                int64_t k_stride, int64_t v_stride, const void* cos, const void* sin, int dtype,
+                                int B, int H, int KVH, int D, void* k_cache, void* v_cache, int L_storage, int pos,
+                                const int32_t* pos_dev, void* q_out, int32_t* seq_lens_out, int32_t* status,
+                                void* stream);
 
 /* ---- split-KV combine ------------------------------------------------------- */
 

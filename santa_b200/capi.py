@@ -128,7 +128,8 @@ def lib() -> C.CDLL:
     if hasattr(L, "santa_rope_append"):
         L.santa_rope_append.restype = C.c_int
         L.santa_rope_append.argtypes = [
-            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,  # q k v cos sin dtype
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,  # q k v and their strides
+            C.c_void_p, C.c_void_p, C.c_int,  # cos sin dtype
             C.c_int, C.c_int, C.c_int, C.c_int,  # B H KVH D
             C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,  # k_cache v_cache L_storage pos pos_dev
             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,  # q_out seq_lens_out status stream

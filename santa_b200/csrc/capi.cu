@@ -562,13 +562,18 @@ int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_til
   return SANTA_OK;
 }
 
-int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, const void* cos, const void* sin,
-                      int dtype, int B, int H, int KVH, int D, void* k_cache, void* v_cache, int L_storage, int pos,
-                      const int32_t* pos_dev, void* q_out, int32_t* seq_lens_out, int32_t* status, void* stream) {
+int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, int64_t q_stride, int64_t k_stride,
+                      int64_t v_stride, const void* cos, const void* sin, int dtype, int B, int H, int KVH, int D,
+                      void* k_cache, void* v_cache, int L_storage, int pos, const int32_t* pos_dev, void* q_out,
+                      int32_t* seq_lens_out, int32_t* status, void* stream) {
   if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
   if (!q_proj || !k_proj || !v_proj || !cos || !sin || !k_cache || !v_cache || !q_out) return SANTA_E_ARG;
   if (D != santa::kD || B <= 0 || H <= 0 || KVH <= 0 || L_storage <= 0) return SANTA_E_SHAPE;
   if (!pos_dev && (pos < 0 || pos >= L_storage)) return SANTA_E_LENGTH;
+  if (q_stride <= 0) q_stride = int64_t(H) * D;
+  if (k_stride <= 0) k_stride = int64_t(KVH) * D;
+  if (v_stride <= 0) v_stride = int64_t(KVH) * D;
+  if ((q_stride | k_stride | v_stride) & 3) return SANTA_E_ALIGN;  // rows stay 8-byte aligned
   const void* ptrs[] = {q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, q_out};
   for (const void* ptr : ptrs)
     if (reinterpret_cast<uintptr_t>(ptr) & 7u) return SANTA_E_ALIGN;  // 8-byte vector accesses
@@ -576,6 +581,9 @@ int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj
   p.q_proj = q_proj;
   p.k_proj = k_proj;
   p.v_proj = v_proj;
+  p.q_stride = q_stride;
+  p.k_stride = k_stride;
+  p.v_stride = v_stride;
   p.cos = cos;
   p.sin = sin;
   p.B = B;

@@ -56,12 +56,13 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendParams
   }
 
   const unsigned char* src;
+  // projections may be slices of one fused [B, (H+2*KVH)*D] tensor: per-sequence strides in elements
   if (kind == 0)
-    src = static_cast<const unsigned char*>(p.q_proj) + (size_t(b) * p.H + head) * kRowBytes;
+    src = static_cast<const unsigned char*>(p.q_proj) + size_t(b) * p.q_stride * 2 + size_t(head) * kRowBytes;
   else if (kind == 1)
-    src = static_cast<const unsigned char*>(p.k_proj) + (size_t(b) * p.KVH + head) * kRowBytes;
+    src = static_cast<const unsigned char*>(p.k_proj) + size_t(b) * p.k_stride * 2 + size_t(head) * kRowBytes;
   else
-    src = static_cast<const unsigned char*>(p.v_proj) + (size_t(b) * p.KVH + head) * kRowBytes;
+    src = static_cast<const unsigned char*>(p.v_proj) + size_t(b) * p.v_stride * 2 + size_t(head) * kRowBytes;
   uint2 xw = *(reinterpret_cast<const uint2*>(src) + lane);
 
   if (kind != 2) {

@@ -101,9 +101,10 @@ int prop_pass2_max_groups(int sms);
 
 // RoPE of the new token's q/k + append of k/v to the cache + packed q.
 struct RopeAppendParams {
-  const void* q_proj;   // [B,H,128]
+  const void* q_proj;   // [B,H,128], sequences q_stride elements apart
   const void* k_proj;   // [B,KVH,128]
   const void* v_proj;   // [B,KVH,128]
+  long long q_stride, k_stride, v_stride;
   const void* cos;      // [B,128]
   const void* sin;      // [B,128]
   int B, H, KVH, L_storage;

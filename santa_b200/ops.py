@@ -218,7 +218,13 @@ def rope_append(q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, pos, *, seq_
     H = q_proj.numel() // (B * D)
     _check(k_proj.numel() == B * KVH * D and v_proj.numel() == B * KVH * D, "k_proj/v_proj must hold [B, KVH*D] elements")
     _check(cos.numel() == B * D and sin.numel() == B * D, "cos/sin must hold [B, D] elements")
-    q_proj, k_proj, v_proj = q_proj.contiguous(), k_proj.contiguous(), v_proj.contiguous()
+    def rows(t):
+        # [B, n] with unit inner stride is taken as is (a slice of a fused projection), else packed
+        if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 4 == 0 and t.data_ptr() % 8 == 0:
+            return t, t.stride(0)
+        t = t.contiguous()
+        return t, t.numel() // B
+    (q_proj, qs), (k_proj, ks), (v_proj, vs) = rows(q_proj), rows(k_proj), rows(v_proj)
     cos, sin = cos.contiguous(), sin.contiguous()
     dev = q_proj.device
     pos_dev = None
@@ -233,7 +239,7 @@ def rope_append(q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, pos, *, seq_
         if q_out is None:
             q_out = torch.empty((B, H, D), device=dev, dtype=q_proj.dtype)
         rc = capi.lib().santa_rope_append(
-            q_proj.data_ptr(), k_proj.data_ptr(), v_proj.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+            q_proj.data_ptr(), k_proj.data_ptr(), v_proj.data_ptr(), qs, ks, vs, cos.data_ptr(), sin.data_ptr(),
             _dtype_code(q_proj), B, H, KVH, D, k_cache.data_ptr(), v_cache.data_ptr(), L_storage, pos_host,
             None if pos_dev is None else pos_dev.data_ptr(), q_out.data_ptr(),
             None if seq_lens_out is None else seq_lens_out.data_ptr(),

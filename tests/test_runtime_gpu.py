@@ -1,0 +1,54 @@
+"""The decode runtime on a GPU: one decode step equals a prefill of the extended prompt (dense
+backend), and the CUDA-graph replay of the sampled-attention step equals its eager run."""
+import pytest
+import torch
+
+from santa_b200.runtime import DecodeRuntime, LlamaShape
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = LlamaShape(hidden=512, layers=2, heads=4, kv_heads=1, head_dim=128, intermediate=1024, vocab=1000)
+
+
+def test_decode_steps_equal_prefill_of_the_extended_prompt():
+    dev = torch.device("cuda:0")
+    B, L, new = 2, 45, 5
+    ids = torch.randint(0, 1000, (B, L), generator=torch.Generator().manual_seed(2)).to(dev)
+    rt = DecodeRuntime(SHAPE, B, 64, dev, attention="sdpa", init_std=0.05)
+    last = rt.prefill(ids, chunk=16)
+    res = rt.generate(last, L, new, use_graph=False)
+    toks = res["generated_token_ids_all"].to(dev)
+    assert toks.shape == (B, new) and res["steps_sampled"] == new and res["timed_generated_tokens"] == B * new
+    assert res["device_status_word"] == 0 and rt.pos.tolist() == [L + new - 1] * B
+    logits_step = rt.logits.clone()                       # logits after feeding token new-2 at position L+new-2
+    k_rows = rt.k_cache[1][:, L:L + new - 1].clone()
+    rt2 = DecodeRuntime(SHAPE, B, 64, dev, attention="sdpa", init_std=0.05)
+    last2 = rt2.prefill(torch.cat([ids, toks[:, :new - 1]], dim=1), chunk=16)
+    assert (logits_step - last2).abs().max().item() < 0.06 * max(1.0, last2.abs().max().item())
+    assert (k_rows.float() - rt2.k_cache[1][:, L:L + new - 1].float()).abs().max().item() < 0.06
+    assert torch.equal(last.argmax(-1), toks[:, 0])
+
+
+def test_graph_replay_of_the_sampled_step_equals_eager_and_stops_in_lockstep():
+    dev = torch.device("cuda:0")
+    B, L, new = 3, 700, 6
+    outs = []
+    for use_graph in (False, True):
+        rt = DecodeRuntime(SHAPE, B, 1024, dev, attention="santa_flash", S=64, init_std=0.05)
+        rt.fill_cache_synthetic(L, seed=4)
+        first = torch.zeros(B, 1000, device=dev)
+        first[:, 7] = 1.0
+        res = rt.generate(first, L, new, use_graph=use_graph)
+        outs.append((res["generated_token_ids_all"], rt.logits.clone(), rt.k_cache[1][:, L:L + new].clone()))
+        assert res["device_status_word"] == 0 and (res["generated_token_ids_all"][:, 0] == 7).all()
+        assert rt.pos.tolist() == [L + new - 1] * B
+        assert torch.isfinite(rt.logits).all()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert torch.equal(outs[0][2], outs[1][2])
+    # stop tokens: a finished sequence keeps emitting the stop token; "all_finished" ends the loop early
+    rt = DecodeRuntime(SHAPE, B, 1024, dev, attention="santa_flash", S=64, init_std=0.05)
+    rt.fill_cache_synthetic(L, seed=4)
+    first = torch.zeros(B, 1000, device=dev)
+    first[:, 7] = 1.0
+    res = rt.generate(first, L, new, stop_token_ids=[7], lockstep_stop_mode="all_finished")
+    assert res["steps_sampled"] == 1 and (res["generated_token_ids_all"] == 7).all()
