@@ -220,6 +220,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-seq-sharded", action="store_true", help="skip the 512k-context sequence-sharded extra")
     ap.add_argument("--no-prop", action="store_true", help="skip the santa_prop ragged-batch extra")
+    ap.add_argument("--no-e2e-model", action="store_true",
+                    help="skip the end-to-end Llama-3.1-8B-shaped decode extra (needs ~160 GB of HBM)")
+    ap.add_argument("--e2e-model-batch", type=int, default=32)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -408,6 +411,12 @@ def main():
         del qp2, Kr, Vr, qr
         torch.cuda.empty_cache()
 
+    # ---- extra: end-to-end decode of a Llama-3.1-8B-shaped model (BASELINE configs[4]) -----------------
+    if not args.no_e2e_model:
+        res4 = e2e_model_decode(dev, args.e2e_model_batch, world)
+        if rank == 0:
+            line["e2e_llama8b_decode"] = res4
+
     if rank == 0:
         line["cpu_baseline"] = cpu_dense_baseline() if world == 1 else None
         print(json.dumps(line))
@@ -416,6 +425,66 @@ def main():
 
         dist.barrier()
         dist.destroy_process_group()
+
+
+def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128):
+    """Random-init (seed 0) Llama-3.1-8B-shaped decoder, `batch` sequences with `prompt_len` cached tokens
+    each, `new_tokens` greedy tokens with santa_flash S=256; one replica per GPU.  The caches are filled
+    with seeded N(0,1) values instead of running the prefill (random weights: the prefill would produce
+    values of no more meaning, and only the decode phase is the metric).  Returns per-replica numbers;
+    the whole-job token rate is world x the replica's."""
+    import torch.distributed as dist
+    from santa_b200.runtime import DecodeRuntime, LlamaShape
+
+    torch.cuda.empty_cache()
+    out = {"workload": f"Llama-3.1-8B shape, random init seed 0, B={batch} x {prompt_len} cached tokens, "
+                       f"{new_tokens} greedy tokens, santa_flash S={S}, CUDA-graph step, 1 replica per GPU",
+           "cache": "synthetic N(0,1) fill (no prefill run)"}
+    try:
+        rt = DecodeRuntime(LlamaShape(), batch, prompt_len + new_tokens, dev, attention="santa_flash", S=S,
+                           attn_seed=SEED, weight_seed=0)
+        rt.fill_cache_synthetic(prompt_len, seed=SEED + 4)
+        first = torch.zeros(batch, rt.shape.vocab, device=dev)
+        first[:, 1] = 1.0
+        rt.capture(prompt_len + new_tokens)
+        rt.generate(first, prompt_len, 4)                           # warm-up replays
+        if world > 1:
+            dist.barrier()
+        res = rt.generate(first, prompt_len, new_tokens)
+        t = torch.tensor([res["decode_time_s"]], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        steps_fwd = res["steps_sampled"] - 1                         # forward passes inside the timed loop
+        # attention share: eager steps with events around every layer's attention call
+        rt.attn_events = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        rt.pos.fill_(prompt_len)
+        rt._bn = rt._plan_tile(prompt_len + new_tokens)
+        for _ in range(2):
+            rt._step(prompt_len + new_tokens)
+        rt.attn_events = []
+        e0.record()
+        for _ in range(3):
+            rt._step(prompt_len + new_tokens)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        attn_ms = sum(a.elapsed_time(b) for a, b in rt.attn_events) / 3
+        eager_ms = e0.elapsed_time(e1) / 3
+        kv_bytes = 32 * (batch * prompt_len * KVH * D * 2)           # K rows read per step, all layers
+        out.update({
+            "tokens_per_s": world * res["timed_generated_tokens"] / dt,
+            "ms_per_step_graph": dt / max(1, steps_fwd) * 1e3,
+            "ms_per_step_eager": eager_ms, "attention_ms_per_step": attn_ms,
+            "attention_share_of_eager_step": attn_ms / eager_ms,
+            "attention_k_gbs": kv_bytes / (attn_ms * 1e-3) / 1e9,
+            "hbm_gb_allocated": torch.cuda.max_memory_allocated(dev) / 1e9,
+            "device_status_word": res["device_status_word"]})
+        del rt
+    except torch.OutOfMemoryError as exc:
+        out["error"] = f"out of device memory: {str(exc)[:120]}"
+    torch.cuda.empty_cache()
+    return out
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from

@@ -93,6 +93,7 @@ class DecodeRuntime:
         self.tok = torch.zeros(self.B, dtype=torch.long, device=self.dev)
         self.logits = torch.zeros(self.B, s.vocab, device=self.dev, dtype=torch.float32)
         self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._graph_max_len = 0
         self._graph_stream: Optional[torch.cuda.Stream] = None
         self.attn_events: Optional[list] = None   # filled by eager steps when profiling is on
         if attention == "santa_flash":
@@ -276,7 +277,7 @@ class DecodeRuntime:
         cur_logits = prefill_logits_last.to(dev).float().contiguous()
         self.pos.fill_(prompt_len)
         max_len = prompt_len + max_new_tokens
-        if use_graph and self.attention == "santa_flash" and self._graph is None:
+        if use_graph and self.attention == "santa_flash" and (self._graph is None or max_len > self._graph_max_len):
             self.capture(max_len)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
