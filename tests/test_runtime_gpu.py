@@ -52,3 +52,26 @@ def test_graph_replay_of_the_sampled_step_equals_eager_and_stops_in_lockstep():
     first[:, 7] = 1.0
     res = rt.generate(first, L, new, stop_token_ids=[7], lockstep_stop_mode="all_finished")
     assert res["steps_sampled"] == 1 and (res["generated_token_ids_all"] == 7).all()
+
+
+def test_longctx_harness_writes_the_reference_files(tmp_path):
+    import csv
+    import json
+    from santa_b200 import bench_longctx
+    out = tmp_path / "res"
+    bench_longctx.main(["--out-dir", str(out), "--batch-size", "2", "--prompt-len", "300", "--max-new-tokens", "5",
+                        "--backends", "santa_flash", "sdpa", "--timed-runs", "2", "--warmup-runs", "1",
+                        "--layers", "2", "--hidden", "512", "--heads", "4", "--kv-heads", "1",
+                        "--intermediate", "1024", "--vocab", "1000", "--prefill-chunk-size", "128"])
+    names = {"config.json", "batch_metrics.jsonl", "run_metrics.jsonl", "generations.jsonl", "aggregates.json",
+             "aggregates.csv", "backend_agreement.json"}
+    assert names <= {p.name for p in out.iterdir()}
+    runs = [json.loads(x) for x in open(out / "run_metrics.jsonl")]
+    assert len(runs) == 6 and {r["backend"] for r in runs} == {"santa_flash", "sdpa"}
+    assert all(r["timed_generated_tokens"] == 10 and r["output_tokens_per_s"] > 0 for r in runs)
+    batches = [json.loads(x) for x in open(out / "batch_metrics.jsonl")]
+    assert all(b["steps_sampled"] == 5 and b["prompt_len"] == 300 and b["prefill_time_s"] > 0 for b in batches)
+    rows = list(csv.DictReader(open(out / "aggregates.csv")))
+    assert [r["backend"] for r in rows] == ["santa_flash", "sdpa"] and rows[0]["runs"] == "2"
+    agree = json.load(open(out / "backend_agreement.json"))
+    assert agree[0]["backend_a"] == "santa_flash" and agree[0]["comparable_examples"] == 4
