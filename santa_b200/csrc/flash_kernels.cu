@@ -196,23 +196,23 @@ static cudaError_t launch_one(const StreamParams& p, const FlashMergeParams& mp,
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  if (p.seq_lens != nullptr)
-    stream_kernel<TK, BN, kModeFlash, true><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p);
-  else
-    stream_kernel<TK, BN, kModeFlash, false><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(unsigned(p.ws.ncol) * kGH);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(kCtaWarps * 32);
+  cfg.dynamicSmemBytes = kStreamSmemBytes;
+  cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  cudaError_t e = (p.seq_lens != nullptr) ? cudaLaunchKernelEx(&cfg, stream_kernel<TK, BN, kModeFlash, true>, p)
+                                          : cudaLaunchKernelEx(&cfg, stream_kernel<TK, BN, kModeFlash, false>, p);
+  if (e != cudaSuccess) return e;
+
+  cfg.gridDim = dim3(unsigned(p.ws.ncol) * kGH);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
   return cudaLaunchKernelEx(&cfg, flash_merge_kernel<TK>, mp);
 }
 

@@ -551,9 +551,12 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
       configured[dev] = true;
     }
     if (p.sp.seq_lens != nullptr)
-      stream_kernel<TK, 256, kModePropPass1, true><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
+      e = launch_dependent(stream_kernel<TK, 256, kModePropPass1, true>, dim3(grid), dim3(kCtaWarps * 32),
+                           kStreamSmemBytes, stream, p.sp);
     else
-      stream_kernel<TK, 256, kModePropPass1, false><<<grid, kCtaWarps * 32, kStreamSmemBytes, stream>>>(p.sp);
+      e = launch_dependent(stream_kernel<TK, 256, kModePropPass1, false>, dim3(grid), dim3(kCtaWarps * 32),
+                           kStreamSmemBytes, stream, p.sp);
+    if (e != cudaSuccess) return e;
   } else {
     const int nwarp = p.block_n / 16;
     const size_t smem = size_t(nwarp * 256 + 2 * 16 * nwarp + 16) * sizeof(float);

@@ -60,8 +60,6 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
   if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tmK) : "memory");
   __shared__ int s_start[kMaxRaggedSeqs + 1];
   constexpr bool ragged = RAGGED;
-  if (ragged && cta_warp == kCtaWarps - 1)
-    build_item_starts(p.seq_lens, p.nseq, p.L_valid, BN, p.KVH / p.ws.gw, s_start, lane);
   WarpRing<kStreamStages> ring;
   if (!is_sampler) {
     ring.init(sbase, bars, lane);
@@ -73,6 +71,13 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
       mbar_fence_init();
     }
   }
+  // The kernel is launched as a programmatic dependent of whatever precedes it on the stream (the
+  // previous decode call's merge, the RoPE/append launch): the set-up above overlaps that kernel's
+  // tail; nothing below may run before it has completed -- it produced q, the new K/V rows and the
+  // lengths, and it still reads the workspace this kernel is about to overwrite.
+  cudaGridDependencySynchronize();
+  if (ragged && cta_warp == kCtaWarps - 1)
+    build_item_starts(p.seq_lens, p.nseq, p.L_valid, BN, p.KVH / p.ws.gw, s_start, lane);
   __syncthreads();
 
   const TK* __restrict__ Qg = static_cast<const TK*>(p.q);
