@@ -35,6 +35,7 @@ namespace santa {
 template <typename TK>
 __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams p) {
   __shared__ float s_w[kMaxCtas * kGroupWarps];
+  __shared__ float s_z[kMaxCtas * kGroupWarps];
   __shared__ float s_red[4];
   __shared__ int s_redi[4];
   __shared__ int s_before[4], s_total[4];
@@ -91,12 +92,23 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
     return p.partials + ((size_t(v + cg) * gw + w) * kGH + g) * kPartialStride;
   };
 
-  // phase 1: m*
+  // All loads of a small merge are issued before anything depends on them: the first four partial
+  // vectors of every warp (phase 3 below) together with every partial's (m, Z) pair.
+  float4 a_pre[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = wq + 4 * k;
+    a_pre[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < nv) a_pre[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
+  }
+
+  // phase 1: m* (Z rides along in the same 8-byte load)
   float mloc = -CUDART_INF_F;
   for (int i = tid; i < nv; i += 128) {
-    const float mv = __ldcg(partial(v_first + i) + kD);
-    s_w[i] = mv;
-    mloc = fmaxf(mloc, mv);
+    const float2 mz = __ldcg(reinterpret_cast<const float2*>(partial(v_first + i) + kD));
+    s_w[i] = mz.x;
+    s_z[i] = mz.y;
+    mloc = fmaxf(mloc, mz.x);
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
@@ -110,7 +122,7 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
   int vloc = 0;
   for (int i = tid; i < nv; i += 128) {
     const float e = __expf(s_w[i] - ms);
-    zloc += e * __ldcg(partial(v_first + i) + kD + 1);
+    zloc += e * s_z[i];
     if (g == 0 && p.vrows != nullptr) vloc += __ldcg(p.partial_vrows + size_t(v_first + i + cg) * gw + w);
     s_w[i] = e;
   }
@@ -126,7 +138,7 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
   __syncthreads();
   const float zs = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
 
-  // phase 3: A, four partials in flight per warp
+  // phase 3: A, four partials in flight per warp (the first four were fetched above)
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i0 = wq; i0 < nv; i0 += 16) {
     float e[4];
@@ -136,7 +148,10 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
       const int i = i0 + 4 * k;
       e[k] = (i < nv) ? s_w[i] : 0.f;
       a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (i < nv) a[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
+      if (i0 == wq)
+        a[k] = a_pre[k];
+      else if (i < nv)
+        a[k] = __ldcg(reinterpret_cast<const float4*>(partial(v_first + i)) + lane);
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
