@@ -488,8 +488,8 @@ def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from
-# the ncu capture summarised in profiles/stream_kernel_flash_config1.md (556.65 MB + 8.99 MB).
-TRAFFIC_BYTES_PER_LAUNCH = 565_636_864
+# the ncu capture summarised in profiles/stream_kernel_flash_config1.md (557.92 MB + 7.83 MB).
+TRAFFIC_BYTES_PER_LAUNCH = 565_754_112
 
 if __name__ == "__main__":
     main()
