@@ -68,3 +68,36 @@ def test_host_mirror_rejects_like_the_reference():
         ops.flash_decode(q, K, K, 4)
     with pytest.raises(RuntimeError, match="q_h must be CUDA"):
         ops.prop_decode(q[0], K[0], K[0], 4)
+
+
+def test_argument_validation_of_the_entries_around_the_path():
+    """The ragged decode entries and the RoPE/append entry reject bad arguments before any CUDA call."""
+    lib = capi.lib()
+    P = 256  # a non-null, aligned stand-in pointer; never dereferenced on these paths
+    # santa_flash_decode_ragged: null lengths, bad dtype, bad shape, bound above the storage, sharding ext
+    fr = lib.santa_flash_decode_ragged
+    assert fr(P, P, P, 0, 2, 32, 8, 128, 64, None, 64, 4, 1, 0, P, P, None, None, 0, None, None) == -8
+    assert fr(P, P, P, 5, 2, 32, 8, 128, 64, P, 64, 4, 1, 0, P, P, None, None, 0, None, None) == -1
+    assert fr(P, P, P, 0, 2, 32, 9, 128, 64, P, 64, 4, 1, 0, P, P, None, None, 0, None, None) == -2
+    assert fr(P, P, P, 0, 2, 32, 8, 128, 64, P, 65, 4, 1, 0, P, P, None, None, 0, None, None) == -3
+    ext = capi.FlashExt(batch_offset=0, tile_offset=3, s_per_tile_override=-1)
+    assert fr(P, P, P, 0, 2, 32, 8, 128, 64, P, 64, 4, 1, 0, P, P, None, None, 0, ctypes.byref(ext), None) == -8
+    # santa_prop_decode_ragged
+    pr = lib.santa_prop_decode_ragged
+    assert pr(P, P, P, 0, 2, 32, 8, 128, 64, None, 64, 4, 1, P, P, None, None, 0, None, None) == -8
+    assert pr(P, P, P, 0, 2, 32, 8, 128, 64, P, 0, 4, 1, P, P, None, None, 0, None, None) == -3
+    assert pr(P + 4, P, P, 0, 2, 32, 8, 128, 64, P, 64, 4, 1, P, P, None, None, 0, None, None) == -6
+    # santa_rope_append: null tensor, D != 128, host position outside the cache, stride not a multiple of 4
+    ra = lib.santa_rope_append
+    assert ra(None, P, P, 0, 0, 0, P, P, 0, 2, 32, 8, 128, P, P, 64, 0, None, P, None, None, None) == -8
+    assert ra(P, P, P, 0, 0, 0, P, P, 0, 2, 32, 8, 64, P, P, 64, 0, None, P, None, None, None) == -2
+    assert ra(P, P, P, 0, 0, 0, P, P, 0, 2, 32, 8, 128, P, P, 64, 64, None, P, None, None, None) == -3
+    assert ra(P, P, P, 6146, 0, 0, P, P, 0, 2, 32, 8, 128, P, P, 64, 0, None, P, None, None, None) == -6
+    assert ra(P, P, P, 0, 0, 0, P, P, 3, 2, 32, 8, 128, P, P, 64, 0, None, P, None, None, None) == -1
+    # host mirrors
+    q = torch.zeros(2, 32, 128, dtype=torch.bfloat16)
+    K = torch.zeros(2, 16, 8, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="must be CUDA"):
+        ops.prop_decode_ragged(q, K, K, [16, 16], 4)
+    with pytest.raises(RuntimeError, match="q_h must be CUDA"):
+        ops.flash_decode_ragged(q, K, K, [16, 16], 4)
