@@ -256,21 +256,27 @@ def main():
     q_host = [q.cpu().pin_memory() for q in qpool]
     kv_new_host = torch.randn(2, B, KVH, D, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
     out_host = torch.empty(B, H, D, dtype=torch.bfloat16).pin_memory()
-    q_dev = torch.empty_like(qpool[0])
-    kv_new_dev = torch.empty(2, B, KVH, D, device=dev, dtype=torch.bfloat16)
+    # one pinned staging buffer per step, [all q | all new k rows | all new v rows]: one copy in
+    nq, nkv = B * H * D, B * KVH * D
+    stage_host = torch.empty(nq + 2 * nkv, dtype=torch.bfloat16).pin_memory()
+    stage_host[nq:nq + nkv].copy_(kv_new_host[0].reshape(-1))
+    stage_host[nq + nkv:].copy_(kv_new_host[1].reshape(-1))
+    q_stage = stage_host[:nq].view(B, H, D)
+    stage_dev = torch.empty(nq + 2 * nkv, device=dev, dtype=torch.bfloat16)
+    q_dev = stage_dev[:nq].view(B, H, D)
+    k_new_dev = stage_dev[nq:nq + nkv].view(B, KVH, D)
+    v_new_dev = stage_dev[nq + nkv:].view(B, KVH, D)
 
     def e2e_body():
-        q_dev.copy_(q_stage, non_blocking=True)
-        kv_new_dev.copy_(kv_new_host, non_blocking=True)
-        K[:, L - 1].copy_(kv_new_dev[0])  # append this step's key/value row in place (fixed valid_len)
-        V[:, L - 1].copy_(kv_new_dev[1])
+        stage_dev.copy_(stage_host, non_blocking=True)
+        K[:, L - 1].copy_(k_new_dev)  # append this step's key/value row in place (fixed valid_len)
+        V[:, L - 1].copy_(v_new_dev)
         out = flash_mod.decode_systematic_batched(q_dev, K, V, S, seed=SEED, want_vrows=False, valid_len=L)[0]
         out_host.copy_(out, non_blocking=True)
 
     # The whole step (copies in, KV append, decode, copy out) is captured once into a CUDA graph, as a
     # serving loop would do, and replayed per step; the step's q is first written into the pinned staging
     # buffer by the host.  If capture is not possible the step runs eagerly.
-    q_stage = torch.empty_like(q_host[0]).pin_memory()
     q_stage.copy_(q_host[0])
     graph = None
     try:
@@ -306,7 +312,7 @@ def main():
 
     e2e_steps = max(20, steps // 4)
     t_e2e = timed_loop(e2e_step, e2e_steps, 3, world, dev)
-    h2d = q_host[0].numel() * 2 + kv_new_host.numel() * 2
+    h2d = stage_host.numel() * 2
     d2h = out_host.numel() * 2
 
     line = None
@@ -347,8 +353,33 @@ def main():
         K3, V3 = K3[:, row0:row1].contiguous(), V3[:, row0:row1].contiguous()
         gbuf = torch.empty(world, 1, H, 130, device=dev, dtype=torch.float32)
         n3 = max(20, steps // 5)
-        t3 = timed_loop(lambda i: sharded.seq_sharded_flash_decode(qp3[i % QPOOL], K3, V3, S3, SEED, L3,
-                                                                    gather_buf=gbuf), n3, 5, world, dev)
+        # decode + all-gather + combine captured once in a CUDA graph (the per-rank work is tens of
+        # microseconds at 8 GPUs, less than the host needs to issue it); q is copied in before each replay
+        q3 = qp3[0].clone()
+
+        def seq_body():
+            return sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, gather_buf=gbuf)
+
+        side3 = torch.cuda.Stream()
+        side3.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side3):
+            for _ in range(3):
+                seq_body()
+        torch.cuda.current_stream().wait_stream(side3)
+        torch.cuda.synchronize()
+        graph3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph3, stream=side3):
+            out3 = seq_body()
+        eager3 = seq_body()[0]
+        graph3.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(eager3, out3[0]), "seq-sharded graph replay differs from the eager call"
+
+        def seq_step(i):
+            q3.copy_(qp3[i % QPOOL])
+            graph3.replay()
+
+        t3 = timed_loop(seq_step, n3, 5, world, dev)
         if rank == 0:
             kb = L3 * KVH * D * 2
             line["seq_sharded_512k"] = {

@@ -219,7 +219,8 @@ SANTA_API size_t santa_prop_workspace_bytes(int H, int KVH, int D, int L, int bl
  *   out    [H,D]       storage dtype
  *   m_star [H]         fp32
  *   vrows  [KVH] int32 or NULL
- * Requires D == 128, H == 4*KVH, block_n <= 0 (auto) or a multiple of 16 up to 256.
+ * Requires D == 128, H == 4*KVH, block_n <= 0 (auto) or a multiple of 16 up to 256, and at most
+ * 11 622 tiles per sequence (2.9 M tokens at 256-row tiles; SANTA_E_TOO_LARGE beyond).
  * The output is summed in a fixed order, so repeated calls give identical bits (the reference
  * accumulates with atomics and does not).  Workspace rules as for santa_flash_decode.
  */

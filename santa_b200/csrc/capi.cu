@@ -148,6 +148,7 @@ int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPla
   if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
   pl->block_n = bn;
   pl->T_c = (L + bn - 1) / bn;
+  if (size_t(pl->T_c) * 20 > size_t(227) * 1024) return SANTA_E_TOO_LARGE;  // budget tables live in shared memory
   pl->use_vec = (bn == 256 && pass1_mode != 1) ? 1 : 0;  // P.cpp:215-229
   pl->ws = make_split(KVH, pl->T_c, sms, &pl->grid);
   const size_t ht = align_up(size_t(H) * pl->T_c * 4, 256);
@@ -204,6 +205,7 @@ int plan_prop_ragged(int B, int H, int KVH, int D, int max_len, PropRaggedPlan* 
   if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
   pl->T_max = (max_len + 255) / 256;
   if ((long long)B * KVH * pl->T_max >= (1LL << 31)) return SANTA_E_TOO_LARGE;
+  if (size_t(pl->T_max) * 20 > size_t(227) * 1024) return SANTA_E_TOO_LARGE;  // budget tables live in shared memory
   pl->ws = make_split(B * KVH, pl->T_max, sms, &pl->grid, KVH);
   const size_t ht = align_up(size_t(B) * H * pl->T_max * 4, 256);
   pl->off_m = 256;

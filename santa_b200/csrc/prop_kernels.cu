@@ -168,12 +168,17 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   cudaGridDependencySynchronize();
   extern __shared__ unsigned char smraw[];
   const int T_c = seq_lens ? (ragged_len(seq_lens, blockIdx.y, max_len) + bn - 1) / bn : T_uniform;
+  // per-tile tables of this head, all in shared memory: sort keys, sort payload, ell, budgets, offsets
   float* frac = reinterpret_cast<float*>(smraw);
   int* idx = reinterpret_cast<int*>(frac + tile_stride);
+  float* ells = reinterpret_cast<float*>(idx + tile_stride);
+  int* bud = reinterpret_cast<int*>(ells + tile_stride);
+  float* offs = reinterpret_cast<float*>(bud + tile_stride);
   __shared__ float s_part[128];
   __shared__ float s_bcast;
-  __shared__ int s_ipart[128];
-  const int h = blockIdx.x, tid = threadIdx.x;
+  __shared__ float s_wmax[4];
+  __shared__ int s_wsum[4];
+  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wq = tid >> 5;
   const size_t row = (size_t(blockIdx.y) * gridDim.x + h) * tile_stride;
   const float* mt = m_tiles_all + row;
   const float* el = ell_tiles_all + row;
@@ -182,31 +187,30 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   float* a0_tile = a0_tile_all + row;
   float* m_star = m_star_all ? m_star_all + size_t(blockIdx.y) * gridDim.x : nullptr;
 
+  // m* (a maximum is the same in any order); ell and the random offsets ride along
   float lm = -3.402823466e+38f;
   for (int t = tid; t < T_c; t += 128) {
-    const float v = mt[t];
+    const float v = __ldcg(mt + t);
+    ells[t] = __ldcg(el + t);
     frac[t] = v;
     lm = fmaxf(lm, v);
+    offs[t] = u01_from_seed(seed, h, t);
   }
-  s_part[tid] = lm;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) lm = fmaxf(lm, __shfl_xor_sync(0xffffffffu, lm, off));
+  if (lane == 0) s_wmax[wq] = lm;
   __syncthreads();
-  if (tid == 0) {
-    float v = s_part[0];
-    for (int i = 1; i < 128; ++i) v = fmaxf(v, s_part[i]);
-    s_bcast = v;
-  }
-  __syncthreads();
-  const float mstar = s_bcast;
+  const float mstar = fmaxf(fmaxf(s_wmax[0], s_wmax[1]), fmaxf(s_wmax[2], s_wmax[3]));
   if (tid == 0 && m_star != nullptr) m_star[h] = mstar;
 
+  // W_t and Z: per-thread partials in tile order, then thread 0 adds the 128 partials in order
   float zl = 0.f;
   for (int t = tid; t < T_c; t += 128) {
     const float e = __expf(frac[t] - mstar);
-    const float W = __fmul_rn(e, el[t]);
+    const float W = __fmul_rn(e, ells[t]);
     frac[t] = W;
-    zl = (flags & 2) ? __fmaf_rn(e, el[t], zl) : __fadd_rn(zl, W);
+    zl = (flags & 2) ? __fmaf_rn(e, ells[t], zl) : __fadd_rn(zl, W);
   }
-  __syncthreads();
   s_part[tid] = zl;
   __syncthreads();
   if (tid == 0) {
@@ -221,7 +225,7 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
     for (int t = tid; t < T_c; t += 128) {
       S_tiles[t] = 0;
       invdelta[t] = 0.0f;
-      a0_tile[t] = u01_from_seed(seed, h, t);
+      a0_tile[t] = offs[t];
     }
     return;
   }
@@ -230,18 +234,18 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   for (int t = tid; t < T_c; t += 128) {
     const float q = __fmul_rn((float)S, __fdiv_rn(frac[t], Z));
     const int b = (int)floorf(q);
-    S_tiles[t] = b;
+    bud[t] = b;
     bl += b;
     const float ft = __fsub_rn(q, (float)b);
-    const float u = u01_from_seed(seed, h, t);
+    const float u = offs[t];
     frac[t] = (flags & 1) ? __fmaf_rn(1.0e-7f, u, ft) : __fadd_rn(ft, __fmul_rn(1.0e-7f, u));
     idx[t] = t;
   }
-  s_ipart[tid] = bl;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) bl += __shfl_xor_sync(0xffffffffu, bl, off);
+  if (lane == 0) s_wsum[wq] = bl;
   __syncthreads();
-  int sum_base = 0;
-  for (int i = 0; i < 128; ++i) sum_base += s_ipart[i];
-  int rem = S - sum_base;
+  int rem = S - ((s_wsum[0] + s_wsum[1]) + (s_wsum[2] + s_wsum[3]));
   rem = rem < 0 ? 0 : rem;
   rem = rem > T_c ? T_c : rem;
 
@@ -270,14 +274,15 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
   }
   for (int r = tid; r < rem; r += 128) {
     const int best = idx[r];
-    if (best >= 0) S_tiles[best] += 1;
+    if (best >= 0) bud[best] += 1;  // the entries of idx are distinct tiles
   }
   __syncthreads();
   for (int t = tid; t < T_c; t += 128) {
-    const float ell = el[t];
-    const int St = S_tiles[t];
+    const float ell = ells[t];
+    const int St = bud[t];
+    S_tiles[t] = St;
     invdelta[t] = (St > 0 && ell > 1e-20f) ? __fdiv_rn((float)St, ell) : 0.0f;
-    a0_tile[t] = u01_from_seed(seed, h, t);
+    a0_tile[t] = offs[t];
   }
 }
 
@@ -568,7 +573,12 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   if (e != cudaSuccess) return e;
 
   const int nseq = p.sp.seq_lens ? p.sp.nseq : 1;
-  e = launch_dependent(prop_budgets_kernel, dim3(H, nseq), dim3(128), size_t(p.sp.tile_stride) * 8, stream,
+  const size_t budget_smem = size_t(p.sp.tile_stride) * 20;  // five per-tile tables
+  if (budget_smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(prop_budgets_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget_smem);
+    if (e != cudaSuccess) return e;
+  }
+  e = launch_dependent(prop_budgets_kernel, dim3(H, nseq), dim3(128), budget_smem, stream,
                        (const float*)p.sp.m_tiles, (const float*)p.sp.ell_tiles, p.T_c, p.sp.seq_lens, L,
                        p.block_n, p.sp.tile_stride, p.S, p.sp.seed, p.flags, p.m_star, p.S_tiles, p.invdelta, p.a0);
   if (e != cudaSuccess) return e;
