@@ -176,9 +176,65 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tens
   return std::make_tuple(out, m_star, vrows);
 }
 
+// Sequence-sharded decode (no counterpart in the reference, which is single-device): this rank's
+// shard of the cache sampled with the GLOBAL tile index and the GLOBAL per-tile budget; returns the
+// unnormalised partial [B,H,130] fp32 (A[128], m, Z per head) that `lse_combine` folds across ranks.
+at::Tensor decode_systematic_partial(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g, int64_t S, uint64_t seed,
+                                     int64_t block_n, int64_t valid_len, int64_t batch_offset, int64_t tile_offset,
+                                     int64_t s_per_tile) {
+  const ShapeInfo info = check_inputs(q_h, K_g, V_g);
+  SANTA_CHECK(info.batched, "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
+  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
+  const int L = (valid_len > 0) ? (int)valid_len : L_storage;
+  SANTA_CHECK(L <= L_storage, "valid_len exceeds storage length: valid_len=", L, " storage=", L_storage);
+  SANTA_CHECK(D == 128 && H % KVH == 0 && H / KVH == 4, "This build supports only D=128 and GH=4 (H/KVH)");
+  const int bn = santa_block_n_rule(L, (int)block_n);
+  SANTA_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
+  const c10::cuda::CUDAGuard guard(q_h.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_h.contiguous();
+  at::Tensor part = at::empty({B, H, D + 2}, q.options().dtype(at::kFloat));
+  const size_t ws_bytes = santa_flash_workspace_bytes(B, KVH, L, bn);
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  santa_flash_ext ext{};
+  ext.batch_offset = (int)batch_offset;
+  ext.tile_offset = (int)tile_offset;
+  ext.s_per_tile_override = (int)s_per_tile;
+  ext.partial_out = part.data_ptr<float>();
+  const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
+                                    q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, B, H, KVH,
+                                    D, L, L_storage, S, seed, bn, nullptr, nullptr, nullptr, ws.data_ptr(),
+                                    (size_t)ws.numel(), &ext, (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+  return part;
+}
+
+// Fold partials [G,B,H,130] fp32 of G disjoint tile sets into (out [B,H,128], m_star [B,H]).
+std::tuple<at::Tensor, at::Tensor> lse_combine(at::Tensor partials, int64_t s_per_tile, bool bf16) {
+  SANTA_CHECK(partials.is_cuda() && partials.scalar_type() == at::kFloat && partials.is_contiguous() &&
+                  partials.dim() == 4 && partials.size(3) == 130,
+              "partials must be a contiguous CUDA fp32 tensor [G,B,H,130]");
+  const c10::cuda::CUDAGuard guard(partials.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int G = (int)partials.size(0), B = (int)partials.size(1), H = (int)partials.size(2);
+  at::Tensor out = at::empty({B, H, 128}, partials.options().dtype(bf16 ? at::kBFloat16 : at::kHalf));
+  at::Tensor m_star = at::empty({B, H}, partials.options());
+  const int rc = santa_lse_combine(partials.data_ptr<float>(), G, B * H, 128, (int)s_per_tile,
+                                   bf16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, out.data_ptr(),
+                                   m_star.data_ptr<float>(), (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ")");
+  return std::make_tuple(out, m_star);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("decode_systematic_partial", &decode_systematic_partial, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
+        py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("valid_len") = -1,
+        py::arg("batch_offset") = 0, py::arg("tile_offset") = 0, py::arg("s_per_tile") = -1);
+  m.def("lse_combine", &lse_combine, py::arg("partials"), py::arg("s_per_tile"), py::arg("bf16") = true);
   m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0,
         py::arg("want_vrows") = false, py::arg("max_len") = -1);

@@ -47,19 +47,34 @@ def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0
     if K_shard.size(1) < row1 - row0:
         raise RuntimeError(f"rank {rank}: shard holds {K_shard.size(1)} rows, plan needs {row1 - row0}")
     B, H = q.size(0), q.size(1)
+    mod = _flash_module()   # the compiled module: a few microseconds of host time per call
     if row1 > row0:
-        part, _, _ = ops.flash_decode(q, K_shard, V_shard, S, seed=seed, block_n=bn, valid_len=row1 - row0,
-                                      tile_offset=tile0, s_per_tile=spt, partial=True)
+        part = mod.decode_systematic_partial(q, K_shard, V_shard, S, seed=seed, block_n=bn, valid_len=row1 - row0,
+                                             tile_offset=tile0, s_per_tile=spt)
     else:  # more ranks than tiles: an empty shard contributes weight zero
         part = torch.zeros(B, H, 130, device=q.device, dtype=torch.float32)
         part[..., 128] = float("-inf")
+    bf16 = q.dtype == torch.bfloat16
     if world == 1:
-        return ops.lse_combine(part.unsqueeze(0), spt, q.dtype)
+        return mod.lse_combine(part.unsqueeze(0), spt, bf16)
     if gather_buf is None:
         gather_buf = torch.empty((world,) + tuple(part.shape), device=q.device, dtype=torch.float32)
     # concatenated layout ([world*B,H,130]) is accepted by every backend
     dist.all_gather_into_tensor(gather_buf.view(world * part.size(0), *part.shape[1:]), part, group=group)
-    return ops.lse_combine(gather_buf, spt, q.dtype)
+    return mod.lse_combine(gather_buf, spt, bf16)
+
+
+_flash_mod = None
+
+
+def _flash_module():
+    global _flash_mod
+    if _flash_mod is None:
+        import santa_b200
+        santa_b200.enable_dropin()
+        import santa_flash_batch_cuda
+        _flash_mod = santa_flash_batch_cuda
+    return _flash_mod
 
 
 def batch_sharded_flash_decode(q_local, K_local, V_local, S, seed, batch_offset, **kw):

@@ -521,3 +521,33 @@ def test_rope_append_matches_reference_golden(name):
     assert status.item() == 3 and torch.equal(kc_d, before)
     with pytest.raises(RuntimeError, match="pos out of range"):
         ops().rope_append(q_proj.to(d), k_proj.to(d), v_proj.to(d), cos2.to(d), sin2.to(d), kc_d, vc_d, c["L"])
+
+
+def test_sharded_module_path_equals_the_c_abi_mirror():
+    """The compiled module's partial / combine functions (used by santa_b200.sharded) against the ctypes
+    mirror, and the one-rank sequence-sharded call against the plain call."""
+    import santa_b200
+    from santa_b200 import sharded
+    santa_b200.enable_dropin()
+    import santa_flash_batch_cuda as mod
+    q, K, V = cases.make_qkv(2, 9000, 8, "bf16", 61, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    L, S = 8700, 300
+    bn, T_c, spt, plan = sharded.shard_plan(L, 3, S)
+    parts = []
+    for row0, row1, tile0 in plan:
+        Ks, Vs = K[:, row0:row1].contiguous(), V[:, row0:row1].contiguous()
+        p_mod = mod.decode_systematic_partial(q, Ks, Vs, S, seed=9, block_n=bn, valid_len=row1 - row0,
+                                              tile_offset=tile0, s_per_tile=spt)
+        p_ops = ops().flash_decode(q, Ks, Vs, S, seed=9, block_n=bn, valid_len=row1 - row0, tile_offset=tile0,
+                                   s_per_tile=spt, partial=True)[0]
+        assert torch.equal(p_mod, p_ops)
+        parts.append(p_mod)
+    buf = torch.stack(parts)
+    o_mod, m_mod = mod.lse_combine(buf, spt, True)
+    o_ops, m_ops = ops().lse_combine(buf, spt, torch.bfloat16)
+    assert torch.equal(o_mod, o_ops) and torch.equal(m_mod, m_ops)
+    full = ops().flash_decode(q, K, V, S, seed=9, valid_len=L)
+    assert close(o_mod, full[0]) and bits_eq(m_mod, full[1])
+    one = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L)
+    assert close(one[0], full[0]) and bits_eq(one[1], full[1])
