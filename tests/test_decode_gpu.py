@@ -551,3 +551,64 @@ def test_sharded_module_path_equals_the_c_abi_mirror():
     assert close(o_mod, full[0]) and bits_eq(m_mod, full[1])
     one = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L)
     assert close(one[0], full[0]) and bits_eq(one[1], full[1])
+
+
+def test_flash_config3_full_size_properties():
+    """Config 3 at full size (B=1, L=524288, S=1024 => 2048 tiles, one sample per head and tile), whole
+    and as four sequence shards through the module path: size-independent properties."""
+    import santa_b200
+    from santa_b200 import sharded
+    santa_b200.enable_dropin()
+    import santa_flash_batch_cuda as mod
+    L, S = 524288, 1024
+    g = torch.Generator(device=dev()).manual_seed(33)
+    q = torch.randn(1, 32, 128, device=dev(), generator=g).to(torch.bfloat16)
+    K = torch.randn(1, L, 8, 128, device=dev(), generator=g).to(torch.bfloat16)
+    V = torch.randn(1, L, 8, 128, device=dev(), generator=g).to(torch.bfloat16)
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, S, seed=1690, want_vrows=True, trace=True)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("flash", dev()) == 0
+    assert (tr.block_n, tr.T_c, tr.S_per_tile) == (256, 2048, 1)
+    per_tile = tr.counts.view(1, 32, 2048, 256).sum(-1)
+    assert per_tile.min() >= 0 and per_tile.max() <= 2 and abs(per_tile.float().mean().item() - 1.0) < 0.02
+    flagged = (tr.counts.view(1, 8, 4, L) > 0).any(2)
+    assert (flagged.sum(-1).int() == vrows).all() and ((tr.rowmask != 0) == flagged).all()
+    assert bits_eq(m_star, tr.m_tiles.max(-1).values)
+    assert close(out, flash_eval_torch(tr.counts, V, tr.m_tiles, tr.ell_tiles, 256, 1))
+    bn, T_c, spt, plan = sharded.shard_plan(L, 4, S)
+    assert (bn, T_c, spt) == (256, 2048, 1) and [p[2] for p in plan] == [0, 512, 1024, 1536]
+    parts = [mod.decode_systematic_partial(q, K[:, r0:r1], V[:, r0:r1], S, seed=1690, block_n=bn,
+                                           valid_len=r1 - r0, tile_offset=t0, s_per_tile=spt)
+             for r0, r1, t0 in plan]
+    o4, m4 = mod.lse_combine(torch.stack(parts), spt, True)
+    assert bits_eq(m4, m_star) and close(o4, out)
+
+
+def test_prop_config2_full_size_properties():
+    """Config 2 at full size through the ragged entry: 16 sequences with the seed-7 lengths, S=256."""
+    lengths = torch.randint(8192, 65537, (16,), generator=torch.Generator().manual_seed(7)).tolist()
+    B, Ls, S = 16, 65536, 256
+    g = torch.Generator(device=dev()).manual_seed(34)
+    q = torch.randn(B, 32, 128, device=dev(), generator=g).to(torch.bfloat16)
+    K = torch.randn(B, Ls, 8, 128, device=dev(), generator=g).to(torch.bfloat16)
+    V = torch.randn(B, Ls, 8, 128, device=dev(), generator=g).to(torch.bfloat16)
+    lens = torch.tensor(lengths, dtype=torch.int32, device=dev())
+    out, m_star, vrows, tr = ops().prop_decode_ragged(q, K, V, lens, S, seed=1690, want_vrows=True, trace=True)
+    out2 = ops().prop_decode_ragged(q, K, V, lens, S, seed=1690)[0]
+    torch.cuda.synchronize()
+    assert ops().workspace_status("prop_ragged", dev()) == 0
+    assert torch.equal(out, out2)                                           # fixed summation order
+    for b, Lb in enumerate(lengths):
+        T = (Lb + 255) // 256
+        St = tr.S_tiles[b, :, :T]
+        assert (St.sum(1) <= S).all() and (St.sum(1) >= S - T).all() and (tr.S_tiles[b, :, T:] == 0).all()
+        cnt = tr.counts[b].view(32, 256, 256).sum(-1)[:, :T]                # [H, tiles] (max_len = 256 tiles)
+        assert ((cnt - St).abs() <= 1).all()
+        assert (tr.counts[b, :, Lb:] == 0).all()
+        flagged = (tr.counts[b].view(8, 4, Ls) > 0).any(1)
+        assert (flagged.sum(-1).int() == vrows[b]).all()
+        assert bits_eq(m_star[b], tr.m_tiles[b, :, :T].max(-1).values)
+        ev = torch.zeros(32, 128, device=dev())
+        for kv in range(8):
+            ev[4 * kv:4 * kv + 4] = tr.counts[b, 4 * kv:4 * kv + 4, :Lb].float() @ V[b, :Lb, kv].float()
+        assert close(out[b], ev / S)
