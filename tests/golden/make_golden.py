@@ -4,7 +4,7 @@ CUDA kernels (oracle/_ref, built unmodified from the reference tree by
 library's kernel that the reference keeps in shared memory.
 
 Run on a GPU box from the repository root:
-    python tests/golden/make_golden.py --out gpurun_out/golden
+    python tests/golden/make_golden.py --out out/golden
 then copy the .npz files into tests/golden/.
 
 Each Flash fixture holds, for the seeded inputs of tests/cases.py:
@@ -41,7 +41,7 @@ def sparse(c):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/golden")
+    ap.add_argument("--out", default="out/golden")
     args = ap.parse_args()
     os.makedirs(args.out, exist_ok=True)
     dev = torch.device("cuda:0")
