@@ -66,6 +66,24 @@ SANTA_API float santa_u01(uint64_t seed, int head_index, int tile_index);
 
 /* ---- optional extensions of the Flash decode ------------------------------ */
 
+/* Exchange of Flash partials between the ranks of a sequence-sharded decode through peer-mapped device
+ * memory (NVLink), without a collective library.  Every rank owns one exchange buffer of
+ * santa_peer_exchange_bytes() bytes, zero-filled once, and maps all of them (CUDA IPC, symmetric memory):
+ * peer_buffer[r] is the address of rank r's buffer in THIS process.  A decode call whose ext names a
+ * santa_peer_exchange stores its [B,H,130] partial into every rank's buffer (plain peer stores, then a
+ * system-scope release of a per-sender arrival counter); santa_lse_combine_wait() on every rank waits,
+ * with a bound, until all `world` partials of the same epoch have arrived in its own buffer and folds
+ * them.  `epoch` counts the steps (1, 2, 3, ...; the same value on every rank for the same step);
+ * buffers alternate with its parity, so the ranks only have to stay within one step of each other --
+ * which the wait itself guarantees.  No counterpart in the reference (single device). */
+typedef struct santa_peer_exchange {
+  int world;             /* ranks taking part, 1..16 */
+  int rank;              /* this rank */
+  uint32_t epoch;        /* >= 1 */
+  uint32_t reserved;
+  void* peer_buffer[16]; /* [world] used */
+} santa_peer_exchange;
+
 typedef struct santa_flash_ext {
   /* Added to the batch index in the RNG key (head index b*H+h, F.cu:281) so that a batch-sharded
    * call reproduces the unsharded call's samples.  0 = reference behaviour. */
@@ -93,6 +111,8 @@ typedef struct santa_flash_ext {
   /* [B,H,T_c] fp32 or NULL: the per-tile sampling step S_per_tile/ell_t as the device computed it
    * (an approximate division, F.cu:279-280). */
   float* invdel;
+  /* If not NULL: the partial (as partial_out) is also stored into every rank's exchange buffer. */
+  const santa_peer_exchange* peer;
 } santa_flash_ext;
 
 /* Bytes of workspace santa_flash_decode needs on the current device for this problem. */
@@ -294,6 +314,19 @@ SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const vo
  * m_star [BH] (may be NULL).  This is the reference's finalize (F.cu:386-470) over the union of the
  * tiles; the reference itself has no multi-device path.
  */
+/* Bytes of one rank's exchange buffer for `world` ranks and BH = B*H (batch x heads) partial rows. */
+SANTA_API size_t santa_peer_exchange_bytes(int world, int BH);
+
+/*
+ * The receiving half of the peer exchange: wait until the partials of px->epoch from all px->world
+ * ranks have arrived in this rank's buffer (px->peer_buffer[px->rank]), then combine them exactly as
+ * santa_lse_combine does.  The wait is bounded (about a second); when it runs out the kernel writes 4
+ * to *status (device int32, may be NULL), stores zeros and returns, so the context stays usable.
+ * Asynchronous on `stream`; call it after the decode call of the same epoch.
+ */
+SANTA_API int santa_lse_combine_wait(const santa_peer_exchange* px, int BH, int D, int S_per_tile, int dtype,
+                                     void* out, float* m_star, int32_t* status, void* stream);
+
 SANTA_API int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_tile, int dtype, void* out,
                       float* m_star, void* stream);
 

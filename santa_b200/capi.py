@@ -24,6 +24,18 @@ class SantaError(RuntimeError):
         self.code = code
 
 
+class PeerExchange(C.Structure):
+    """``santa_peer_exchange`` of include/santa_b200.h."""
+
+    _fields_ = [
+        ("world", C.c_int),
+        ("rank", C.c_int),
+        ("epoch", C.c_uint32),
+        ("reserved", C.c_uint32),
+        ("peer_buffer", C.c_void_p * 16),
+    ]
+
+
 class FlashExt(C.Structure):
     """``santa_flash_ext`` of include/santa_b200.h."""
 
@@ -39,6 +51,7 @@ class FlashExt(C.Structure):
         ("counts", C.c_void_p),
         ("rowmask", C.c_void_p),
         ("invdel", C.c_void_p),
+        ("peer", C.POINTER(PeerExchange)),
     ]
 
 
@@ -81,6 +94,8 @@ EXPORTS = (
     "santa_flash_ragged_workspace_bytes",
     "santa_flash_decode_ragged",
     "santa_rope_append",
+    "santa_peer_exchange_bytes",
+    "santa_lse_combine_wait",
 )
 
 
@@ -124,6 +139,14 @@ def lib() -> C.CDLL:
             C.c_int64, C.c_uint64, C.c_int,  # S seed block_n
             C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star vrows
             C.c_void_p, C.c_size_t, C.POINTER(PropExt), C.c_void_p,
+        ]
+    if hasattr(L, "santa_lse_combine_wait"):
+        L.santa_peer_exchange_bytes.restype = C.c_size_t
+        L.santa_peer_exchange_bytes.argtypes = [C.c_int, C.c_int]
+        L.santa_lse_combine_wait.restype = C.c_int
+        L.santa_lse_combine_wait.argtypes = [
+            C.POINTER(PeerExchange), C.c_int, C.c_int, C.c_int, C.c_int,  # px BH D S_per_tile dtype
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,  # out m_star status stream
         ]
     if hasattr(L, "santa_rope_append"):
         L.santa_rope_append.restype = C.c_int

@@ -290,7 +290,15 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   if (D != santa::kD || KVH <= 0 || H != santa::kGH * KVH || B <= 0) return SANTA_E_SHAPE;
   if (L_valid <= 0 || L_valid > L_storage) return SANTA_E_LENGTH;
   const bool want_partial = ext && ext->partial_out;
-  if (!out && !want_partial) return SANTA_E_ARG;
+  const bool want_peer = ext && ext->peer;
+  if (!out && !want_partial && !want_peer) return SANTA_E_ARG;
+  if (want_peer) {
+    const santa_peer_exchange* px = ext->peer;
+    if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world || px->epoch == 0)
+      return SANTA_E_ARG;
+    for (int r = 0; r < px->world; ++r)
+      if (!px->peer_buffer[r] || (reinterpret_cast<uintptr_t>(px->peer_buffer[r]) & 255u)) return SANTA_E_ARG;
+  }
   if (ext && ((ext->u16 == nullptr) != (ext->counts == nullptr))) return SANTA_E_ARG;
   if (ext && ((ext->m_tiles == nullptr) != (ext->ell_tiles == nullptr))) return SANTA_E_ARG;
   if (!aligned16(q) || !aligned16(K) || !aligned16(V) || (out && !aligned16(out))) return SANTA_E_ALIGN;
@@ -346,6 +354,13 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   mp.m_star = m_star;
   mp.vrows = vrows;
   mp.partial_out = want_partial ? ext->partial_out : nullptr;
+  if (ext && ext->peer) {
+    const santa_peer_exchange* px = ext->peer;
+    mp.px.world = px->world;
+    mp.px.rank = px->rank;
+    mp.px.parity = int(px->epoch & 1u);
+    for (int r = 0; r < px->world; ++r) mp.px.base[r] = static_cast<unsigned char*>(px->peer_buffer[r]);
+  }
 
   cudaError_t e = santa::launch_flash(p, mp, dtype, pl.block_n, pl.grid, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
@@ -549,6 +564,29 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
   p.dbg_c = ext ? ext->counts : nullptr;
   p.rowmask = ext ? ext->rowmask : nullptr;
   cudaError_t e = santa::launch_prop(p, dtype, pl.grid, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e);
+  return SANTA_OK;
+}
+
+size_t santa_peer_exchange_bytes(int world, int BH) {
+  if (world < 1 || world > santa::kMaxPeers || BH <= 0) return 0;
+  return align_up(santa::peer_data_offset(2, world, 0, BH), 256);
+}
+
+int santa_lse_combine_wait(const santa_peer_exchange* px, int BH, int D, int S_per_tile, int dtype, void* out,
+                           float* m_star, int32_t* status, void* stream) {
+  if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
+  if (!px || !out || BH <= 0) return SANTA_E_ARG;
+  if (D != santa::kD) return SANTA_E_SHAPE;
+  if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world || px->epoch == 0)
+    return SANTA_E_ARG;
+  if (!px->peer_buffer[px->rank]) return SANTA_E_ARG;
+  const int parity = int(px->epoch & 1u);
+  // every sender has added BH to its counter of this parity once per epoch of that parity so far
+  const unsigned uses = (px->epoch + unsigned(parity)) >> 1;
+  cudaError_t e = santa::launch_lse_combine_wait(static_cast<unsigned char*>(px->peer_buffer[px->rank]), px->world,
+                                                 parity, uses * unsigned(BH), BH, S_per_tile, dtype, out, m_star,
+                                                 status, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   return SANTA_OK;
 }

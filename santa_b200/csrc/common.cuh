@@ -35,6 +35,7 @@ enum : int {
   kStatusStageTimeout = 1,    // a staged K piece never arrived
   kStatusHandoffTimeout = 2,  // a score buffer was never handed over between the warps of a column
   kStatusBadPosition = 3,     // an append position outside the cache was skipped
+  kStatusPeerTimeout = 4,     // a rank's partial never arrived in the exchange buffer
 };
 
 // ---------------------------------------------------------------- RNG

@@ -182,6 +182,27 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
         po[kD + 1] = zs;
       }
     }
+    if (p.px.world > 0) {
+      // the same partial into every rank's exchange buffer: plain peer stores, made visible system-wide,
+      // then one arrival count per receiver (released after the whole row is out)
+      const int BH = int(gridDim.x);
+      for (int r = 0; r < p.px.world; ++r) {
+        float* po = reinterpret_cast<float*>(p.px.base[r] + peer_data_offset(p.px.parity, p.px.world, p.px.rank, BH)) +
+                    bh * (kD + 2);
+        po[4 * lane + 0] = acc.x;
+        po[4 * lane + 1] = acc.y;
+        po[4 * lane + 2] = acc.z;
+        po[4 * lane + 3] = acc.w;
+        if (lane == 0) {
+          po[kD] = ms;
+          po[kD + 1] = zs;
+        }
+      }
+      __threadfence_system();
+      __syncwarp();
+      if (lane < p.px.world)
+        atomicAdd_system(reinterpret_cast<int*>(p.px.base[lane]) + p.px.parity * kMaxPeers + p.px.rank, 1);
+    }
     if (p.out != nullptr) {
       const float inv = (spt > 0 && zs > 0.f) ? 1.0f / (zs * (float)spt) : 0.f;
       TK* op = static_cast<TK*>(p.out) + bh * kD + 4 * lane;

@@ -55,6 +55,17 @@ struct StreamParams {
   int* rowmask;       // [B,KVH,L_valid]
 };
 
+// Peer exchange: layout of one rank's buffer and what the kernels need of it.
+constexpr int kMaxPeers = 16;
+constexpr size_t kPeerFlagBytes = 256;  // int32 counters [2 parities][kMaxPeers senders], then the data
+__host__ __device__ inline size_t peer_data_offset(int parity, int world, int sender, int BH) {
+  return kPeerFlagBytes + ((size_t(parity) * world + sender) * BH) * 130 * sizeof(float);
+}
+struct PeerScatter {
+  int world, rank, parity;        // world == 0: no exchange
+  unsigned char* base[kMaxPeers]; // every rank's buffer as mapped here
+};
+
 struct FlashMergeParams {
   int H, KVH, S_per_tile;
   // ragged batch: device lengths (else null), their bound, the tile size and S
@@ -67,6 +78,7 @@ struct FlashMergeParams {
   float* m_star;       // [B,H] or nullptr
   int* vrows;          // [B,KVH] or nullptr
   float* partial_out;  // [B,H,130] or nullptr
+  PeerScatter px;      // also store the partial into every rank's exchange buffer
 };
 
 cudaError_t launch_flash(const StreamParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,
@@ -119,6 +131,10 @@ struct RopeAppendParams {
 cudaError_t launch_rope_append(const RopeAppendParams& p, int dtype, cudaStream_t stream);
 
 // Cross-device combine of G unnormalised partials [G][BH][130].
+// Wait for `world` partials of one parity in the local exchange buffer, then combine them.
+cudaError_t launch_lse_combine_wait(unsigned char* local_base, int world, int parity, unsigned expected, int BH,
+                                    int S_per_tile, int dtype, void* out, float* m_star, int* status,
+                                    cudaStream_t stream);
 cudaError_t launch_lse_combine(const float* partials, int G, int BH, int S_per_tile, int dtype, void* out,
                                float* m_star, cudaStream_t stream);
 

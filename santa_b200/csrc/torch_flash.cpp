@@ -16,6 +16,7 @@
 #include <stdexcept>
 #include <string>
 #include <tuple>
+#include <vector>
 #include <type_traits>
 
 #include "santa_b200.h"
@@ -211,6 +212,67 @@ at::Tensor decode_systematic_partial(at::Tensor q_h, at::Tensor K_g, at::Tensor 
   return part;
 }
 
+santa_peer_exchange make_peer(const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch) {
+  SANTA_CHECK(!peer_ptrs.empty() && peer_ptrs.size() <= 16, "peer_ptrs must hold 1..16 buffer addresses");
+  SANTA_CHECK(rank >= 0 && rank < (int64_t)peer_ptrs.size() && epoch >= 1, "bad rank / epoch of the peer exchange");
+  santa_peer_exchange px{};
+  px.world = (int)peer_ptrs.size();
+  px.rank = (int)rank;
+  px.epoch = (uint32_t)epoch;
+  for (size_t r = 0; r < peer_ptrs.size(); ++r) px.peer_buffer[r] = reinterpret_cast<void*>(peer_ptrs[r]);
+  return px;
+}
+
+// Sequence-sharded decode whose partial goes straight into every rank's exchange buffer (peer-mapped
+// device memory) instead of through a collective; `lse_combine_wait` is the receiving half.
+void decode_systematic_exchange(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g, int64_t S, uint64_t seed,
+                                int64_t block_n, int64_t valid_len, int64_t batch_offset, int64_t tile_offset,
+                                int64_t s_per_tile, std::vector<int64_t> peer_ptrs, int64_t rank, int64_t epoch) {
+  const ShapeInfo info = check_inputs(q_h, K_g, V_g);
+  SANTA_CHECK(info.batched, "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
+  const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
+  const int L = (valid_len > 0) ? (int)valid_len : L_storage;
+  SANTA_CHECK(L <= L_storage, "valid_len exceeds storage length: valid_len=", L, " storage=", L_storage);
+  SANTA_CHECK(D == 128 && H % KVH == 0 && H / KVH == 4, "This build supports only D=128 and GH=4 (H/KVH)");
+  const int bn = santa_block_n_rule(L, (int)block_n);
+  SANTA_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
+  const santa_peer_exchange px = make_peer(peer_ptrs, rank, epoch);
+  const c10::cuda::CUDAGuard guard(q_h.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto q = q_h.contiguous();
+  const size_t ws_bytes = santa_flash_workspace_bytes(B, KVH, L, bn);
+  SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
+  at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  santa_flash_ext ext{};
+  ext.batch_offset = (int)batch_offset;
+  ext.tile_offset = (int)tile_offset;
+  ext.s_per_tile_override = (int)s_per_tile;
+  ext.peer = &px;
+  const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
+                                    q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, B, H, KVH,
+                                    D, L, L_storage, S, seed, bn, nullptr, nullptr, nullptr, ws.data_ptr(),
+                                    (size_t)ws.numel(), &ext, (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
+              ")");
+}
+
+std::tuple<at::Tensor, at::Tensor> lse_combine_wait(std::vector<int64_t> peer_ptrs, int64_t rank, int64_t epoch,
+                                                    int64_t B, int64_t H, int64_t s_per_tile, bool bf16,
+                                                    at::Tensor status) {
+  SANTA_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1,
+              "status must be a CUDA int32 tensor");
+  const santa_peer_exchange px = make_peer(peer_ptrs, rank, epoch);
+  const c10::cuda::CUDAGuard guard(status.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  at::Tensor out = at::empty({B, H, 128}, status.options().dtype(bf16 ? at::kBFloat16 : at::kHalf));
+  at::Tensor m_star = at::empty({B, H}, status.options().dtype(at::kFloat));
+  const int rc = santa_lse_combine_wait(&px, (int)(B * H), 128, (int)s_per_tile,
+                                        bf16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, out.data_ptr(),
+                                        m_star.data_ptr<float>(), status.data_ptr<int>(), (void*)stream.stream());
+  SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ")");
+  return std::make_tuple(out, m_star);
+}
+
 // Fold partials [G,B,H,130] fp32 of G disjoint tile sets into (out [B,H,128], m_star [B,H]).
 std::tuple<at::Tensor, at::Tensor> lse_combine(at::Tensor partials, int64_t s_per_tile, bool bf16) {
   SANTA_CHECK(partials.is_cuda() && partials.scalar_type() == at::kFloat && partials.is_contiguous() &&
@@ -234,6 +296,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_systematic_partial", &decode_systematic_partial, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("valid_len") = -1,
         py::arg("batch_offset") = 0, py::arg("tile_offset") = 0, py::arg("s_per_tile") = -1);
+  m.def("decode_systematic_exchange", &decode_systematic_exchange, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
+        py::arg("S"), py::arg("seed"), py::arg("block_n"), py::arg("valid_len"), py::arg("batch_offset"),
+        py::arg("tile_offset"), py::arg("s_per_tile"), py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"));
+  m.def("lse_combine_wait", &lse_combine_wait, py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("B"),
+        py::arg("H"), py::arg("s_per_tile"), py::arg("bf16"), py::arg("status"));
   m.def("lse_combine", &lse_combine, py::arg("partials"), py::arg("s_per_tile"), py::arg("bf16") = true);
   m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0,

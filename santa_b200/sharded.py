@@ -36,10 +36,47 @@ def shard_plan(L_total: int, world: int, S: int, block_n: int = 0):
     return bn, T_c, spt, plan
 
 
+class PeerExchange:
+    """Exchange buffers of a sequence-sharded decode in peer-mapped device memory (NVLink): every rank
+    allocates one buffer through torch's symmetric memory, maps all ranks' buffers, and the decode
+    kernels store their partials straight into them -- no collective call per step.  One object serves
+    one (B, H) problem shape on one stream; the ranks must call in lock-step (as with a collective)."""
+
+    def __init__(self, B: int, H: int, device, group=None):
+        self.B, self.H = int(B), int(H)
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        nbytes = int(capi.lib().santa_peer_exchange_bytes(self.world, self.B * self.H))
+        if nbytes <= 0:
+            raise RuntimeError("santa_b200: a peer exchange takes 1..16 ranks")
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+            g = group if group is not None else dist.group.WORLD
+            self.buf = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self.buf.zero_()
+            self._handle = symm.rendezvous(self.buf, g.group_name)
+            self.ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)                      # every buffer is zero before anyone writes
+        else:
+            self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self.ptrs = [self.buf.data_ptr()]
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def check(self) -> None:
+        """Synchronise and raise if a wait ran out (a rank never delivered its partial)."""
+        code = int(self.status.item())
+        if code != 0:
+            raise RuntimeError(f"santa_b200: peer exchange failed with device status {code}")
+
+
 def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0, group=None,
-                             gather_buf: Optional[torch.Tensor] = None):
+                             gather_buf: Optional[torch.Tensor] = None, exchange: Optional[PeerExchange] = None):
     """q [B,H,128] (replicated), K_shard/V_shard [B,L_r,KVH,128]: this rank's rows of the cache, as
-    given by ``shard_plan``.  Returns (out [B,H,128], m_star [B,H]) on every rank."""
+    given by ``shard_plan``.  Returns (out [B,H,128], m_star [B,H]) on every rank.  With ``exchange`` the
+    partials travel through peer-mapped memory (``PeerExchange``) instead of an all-gather."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     bn, T_c, spt, plan = shard_plan(L_total, world, S, block_n)
@@ -48,6 +85,16 @@ def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0
         raise RuntimeError(f"rank {rank}: shard holds {K_shard.size(1)} rows, plan needs {row1 - row0}")
     B, H = q.size(0), q.size(1)
     mod = _flash_module()   # the compiled module: a few microseconds of host time per call
+    if exchange is not None:
+        if row1 <= row0:
+            raise RuntimeError("the peer exchange needs at least one tile per rank")
+        if (exchange.B, exchange.H, exchange.world, exchange.rank) != (B, H, world, rank):
+            raise RuntimeError("PeerExchange was built for another problem shape or group")
+        exchange.epoch += 1
+        mod.decode_systematic_exchange(q, K_shard, V_shard, S, seed, bn, row1 - row0, 0, tile0, spt,
+                                       exchange.ptrs, rank, exchange.epoch)
+        return mod.lse_combine_wait(exchange.ptrs, rank, exchange.epoch, B, H, spt, q.dtype == torch.bfloat16,
+                                    exchange.status)
     if row1 > row0:
         part = mod.decode_systematic_partial(q, K_shard, V_shard, S, seed=seed, block_n=bn, valid_len=row1 - row0,
                                              tile_offset=tile0, s_per_tile=spt)

@@ -612,3 +612,42 @@ def test_prop_config2_full_size_properties():
         for kv in range(8):
             ev[4 * kv:4 * kv + 4] = tr.counts[b, 4 * kv:4 * kv + 4, :Lb].float() @ V[b, :Lb, kv].float()
         assert close(out[b], ev / S)
+
+
+def test_peer_exchange_on_one_device():
+    """The peer-exchange path with every 'rank' on this GPU: three shards deliver their partials into
+    three exchange buffers (all local), each buffer's owner then waits and combines.  Epochs alternate
+    the buffer halves; a wait for a partial that nobody sent runs out and reports, without hanging."""
+    import santa_b200
+    from santa_b200 import capi, sharded
+    santa_b200.enable_dropin()
+    import santa_flash_batch_cuda as mod
+    q, K, V = cases.make_qkv(2, 9000, 8, "bf16", 71, 1.0, True)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    L, S, G, B, H = 8700, 300, 3, 2, 32
+    bn, T_c, spt, plan = sharded.shard_plan(L, G, S)
+    nbytes = capi.lib().santa_peer_exchange_bytes(G, B * H)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev()) for _ in range(G)]
+    ptrs = [b.data_ptr() for b in bufs]
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    full = ops().flash_decode(q, K, V, S, seed=9, valid_len=L)
+    for epoch in (1, 2, 3):
+        qe = q if epoch != 2 else (q * 0.5).to(torch.bfloat16)           # another step, other data
+        ref = full if epoch != 2 else ops().flash_decode(qe, K, V, S, seed=9, valid_len=L)
+        for r, (row0, row1, tile0) in enumerate(plan):
+            mod.decode_systematic_exchange(qe, K[:, row0:row1].contiguous(), V[:, row0:row1].contiguous(), S, 9, bn,
+                                           row1 - row0, 0, tile0, spt, ptrs, r, epoch)
+        for r in range(G):
+            o, m = mod.lse_combine_wait(ptrs, r, epoch, B, H, spt, True, status)
+            assert close(o, ref[0]) and bits_eq(m, ref[1])
+        assert status.item() == 0
+    # nobody sends epoch 4: the wait gives up after its bound and says so
+    o, m = mod.lse_combine_wait(ptrs, 0, 4, B, H, spt, True, status)
+    torch.cuda.synchronize()
+    assert status.item() == 4 and (o == 0).all()
+    # the one-rank object goes through the same kernels
+    ex = sharded.PeerExchange(B, H, dev())
+    one = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L, exchange=ex)
+    two = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L, exchange=ex)
+    ex.check()
+    assert close(one[0], full[0]) and bits_eq(one[1], full[1]) and torch.equal(one[0], two[0])
