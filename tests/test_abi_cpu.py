@@ -101,3 +101,28 @@ def test_argument_validation_of_the_entries_around_the_path():
         ops.prop_decode_ragged(q, K, K, [16, 16], 4)
     with pytest.raises(RuntimeError, match="q_h must be CUDA"):
         ops.flash_decode_ragged(q, K, K, [16, 16], 4)
+
+
+def test_peer_exchange_layout_and_validation():
+    lib = capi.lib()
+    assert lib.santa_peer_exchange_bytes(0, 32) == 0 and lib.santa_peer_exchange_bytes(17, 32) == 0
+    assert lib.santa_peer_exchange_bytes(2, 0) == 0
+    for world, BH in ((1, 32), (2, 32), (8, 64), (16, 1024)):
+        n = lib.santa_peer_exchange_bytes(world, BH)
+        assert n % 256 == 0 and n >= 256 + 2 * world * BH * 130 * 4 and n < 256 + 2 * world * BH * 130 * 4 + 256
+    px = capi.PeerExchange(world=2, rank=0, epoch=0)
+    px.peer_buffer[0], px.peer_buffer[1] = 256, 512
+    cw = lib.santa_lse_combine_wait
+    assert cw(ctypes.byref(px), 32, 128, 1, 0, 256, None, None, None) == -8          # epoch 0
+    px.epoch = 1
+    assert cw(ctypes.byref(px), 32, 64, 1, 0, 256, None, None, None) == -2           # D
+    assert cw(ctypes.byref(px), 32, 128, 1, 9, 256, None, None, None) == -1          # dtype
+    px.rank = 2
+    assert cw(ctypes.byref(px), 32, 128, 1, 0, 256, None, None, None) == -8          # rank outside world
+    # a decode call that names a malformed exchange is refused before any CUDA work
+    px.rank, px.world = 0, 17
+    ext = capi.FlashExt(batch_offset=0, tile_offset=0, s_per_tile_override=-1)
+    ext.peer = ctypes.pointer(px)
+    rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 128, 16, 16, 4, 1, 0, None, None, None, None, 0,
+                                ctypes.byref(ext), None)
+    assert rc == -8
