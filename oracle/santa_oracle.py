@@ -9,7 +9,6 @@ fp16 share one code path; ``to16`` / ``from16`` convert.
 from __future__ import annotations
 
 import ctypes as C
-import math
 import os
 import subprocess
 from dataclasses import dataclass

@@ -20,7 +20,6 @@ step graph-capturable while the cache grows.
 """
 from __future__ import annotations
 
-import math
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence

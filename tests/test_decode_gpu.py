@@ -2,7 +2,6 @@
 (oracle/_ref), the golden fixtures and the CPU oracle.  Integer results are compared bit-for-bit;
 attention outputs within max-abs 2e-2 / mean-abs 2e-3 (the tolerance the task states for bf16)."""
 import os
-import sys
 
 import numpy as np
 import pytest

@@ -3,10 +3,8 @@ shard plan, the all-gather of per-rank partials and the log-sum-exp merge rule. 
 come from the CPU oracle (the CUDA kernels need a GPU); the merged result must equal the unsharded
 oracle result."""
 import os
-import sys
 
 import numpy as np
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

@@ -7,7 +7,6 @@ regular entry point (same kernels, so the same bits; the assertion uses the suit
 on two calls in a row because every call reuses the same scratch, and it must refuse problems whose
 scratch need exceeds the fixed array.  This file sorts last so that a failure here cannot hide another
 test's result in a run that stops at the first failure."""
-import ctypes as C
 
 import pytest
 import torch
