@@ -359,7 +359,8 @@ def main():
         t3x, x_note, ex = None, None, None
         try:
             if world > 1:
-                import torch.distributed._symmetric_memory  # noqa: F401
+                import importlib
+                importlib.import_module("torch.distributed._symmetric_memory")
         except Exception as exc:  # noqa: BLE001
             x_note = f"peer exchange unavailable: {str(exc)[:120]}"
         if max_over_ranks(1.0 if x_note else 0.0, world, dev) != 0.0:
