@@ -75,11 +75,14 @@ SANTA_API float santa_u01(uint64_t seed, int head_index, int tile_index);
  * with a bound, until all `world` partials of the same epoch have arrived in its own buffer and folds
  * them.  `epoch` counts the steps (1, 2, 3, ...; the same value on every rank for the same step);
  * buffers alternate with its parity, so the ranks only have to stay within one step of each other --
- * which the wait itself guarantees.  No counterpart in the reference (single device). */
+ * which the wait itself guarantees.  epoch == 0 on every rank selects device-counted epochs: each
+ * buffer carries its own step counter, read by the kernels and advanced by santa_lse_combine_wait, so
+ * that a decode + wait pair captured once in a CUDA graph can be replayed for every step (a wait that
+ * ran out does not advance the counter).  No counterpart in the reference (single device). */
 typedef struct santa_peer_exchange {
   int world;             /* ranks taking part, 1..16 */
   int rank;              /* this rank */
-  uint32_t epoch;        /* >= 1 */
+  uint32_t epoch;        /* >= 1, or 0 = counted on the device */
   uint32_t reserved;
   void* peer_buffer[16]; /* [world] used */
 } santa_peer_exchange;

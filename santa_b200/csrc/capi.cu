@@ -294,8 +294,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   if (!out && !want_partial && !want_peer) return SANTA_E_ARG;
   if (want_peer) {
     const santa_peer_exchange* px = ext->peer;
-    if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world || px->epoch == 0)
-      return SANTA_E_ARG;
+    if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world) return SANTA_E_ARG;
     for (int r = 0; r < px->world; ++r)
       if (!px->peer_buffer[r] || (reinterpret_cast<uintptr_t>(px->peer_buffer[r]) & 255u)) return SANTA_E_ARG;
   }
@@ -358,7 +357,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
     const santa_peer_exchange* px = ext->peer;
     mp.px.world = px->world;
     mp.px.rank = px->rank;
-    mp.px.parity = int(px->epoch & 1u);
+    mp.px.parity = px->epoch == 0 ? -1 : int(px->epoch & 1u);
     for (int r = 0; r < px->world; ++r) mp.px.base[r] = static_cast<unsigned char*>(px->peer_buffer[r]);
   }
 
@@ -578,15 +577,11 @@ int santa_lse_combine_wait(const santa_peer_exchange* px, int BH, int D, int S_p
   if (dtype != SANTA_DTYPE_BF16 && dtype != SANTA_DTYPE_F16) return SANTA_E_DTYPE;
   if (!px || !out || BH <= 0) return SANTA_E_ARG;
   if (D != santa::kD) return SANTA_E_SHAPE;
-  if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world || px->epoch == 0)
-    return SANTA_E_ARG;
+  if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world) return SANTA_E_ARG;
   if (!px->peer_buffer[px->rank]) return SANTA_E_ARG;
-  const int parity = int(px->epoch & 1u);
-  // every sender has added BH to its counter of this parity once per epoch of that parity so far
-  const unsigned uses = (px->epoch + unsigned(parity)) >> 1;
   cudaError_t e = santa::launch_lse_combine_wait(static_cast<unsigned char*>(px->peer_buffer[px->rank]), px->world,
-                                                 parity, uses * unsigned(BH), BH, S_per_tile, dtype, out, m_star,
-                                                 status, static_cast<cudaStream_t>(stream));
+                                                 px->epoch, BH, S_per_tile, dtype, out, m_star, status,
+                                                 static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   return SANTA_OK;
 }

@@ -43,11 +43,18 @@ __global__ void __launch_bounds__(32) lse_combine_kernel(const float* __restrict
 // g's arrival counter (every sender adds 1 per row it has delivered, `expected` in total by this epoch)
 // with system-scope acquire loads and a bounded, sleeping wait; then the rows are combined as above.
 template <typename TK>
-__global__ void __launch_bounds__(32) lse_combine_wait_kernel(unsigned char* __restrict__ base, int world, int parity,
-                                                              unsigned expected, int BH, int S_per_tile,
+__global__ void __launch_bounds__(32) lse_combine_wait_kernel(unsigned char* __restrict__ base, int world,
+                                                              unsigned epoch_arg, int BH, int S_per_tile,
                                                               TK* __restrict__ out, float* __restrict__ m_star,
                                                               int* __restrict__ status) {
   const int bh = blockIdx.x, lane = threadIdx.x;
+  int* ctl = reinterpret_cast<int*>(base);
+  // epoch 0: count the epochs on the device (the same launch, replayed from a graph, serves every step)
+  const bool counted = epoch_arg == 0;
+  const unsigned epoch = counted ? unsigned(__ldcg(ctl + kPeerStepIndex)) + 1u : epoch_arg;
+  const int parity = int(epoch & 1u);
+  // every sender has added BH to its counter of this parity once per epoch of that parity so far
+  const unsigned expected = ((epoch + unsigned(parity)) >> 1) * unsigned(BH);
   bool ok = true;
   if (lane < world) {
     const int* flag = reinterpret_cast<const int*>(base) + parity * kMaxPeers + lane;
@@ -64,7 +71,7 @@ __global__ void __launch_bounds__(32) lse_combine_wait_kernel(unsigned char* __r
   }
   ok = __all_sync(0xffffffffu, ok);
   TK* op = out + size_t(bh) * kD + 4 * lane;
-  if (!ok) {  // report and leave a defined result; nothing was consumed
+  if (!ok) {  // report and leave a defined result; nothing was consumed, the step counter stays
     if (lane == 0 && status != nullptr) atomicExch(status, kStatusPeerTimeout);
     *reinterpret_cast<uint2*>(op) = make_uint2(0u, 0u);
     if (lane == 0 && m_star != nullptr) m_star[bh] = -CUDART_INF_F;
@@ -91,16 +98,25 @@ __global__ void __launch_bounds__(32) lse_combine_wait_kernel(unsigned char* __r
   wv.y = uint32_t(Store16<TK>::bits(acc.z * inv)) | (uint32_t(Store16<TK>::bits(acc.w * inv)) << 16);
   *reinterpret_cast<uint2*>(op) = wv;
   if (lane == 0 && m_star != nullptr) m_star[bh] = ms;
+  if (counted && lane == 0) {
+    // the last row to finish advances the step counter: every row has read it by then
+    __threadfence();
+    if (atomicAdd(ctl + kPeerDoneIndex, 1) == BH - 1) {
+      ctl[kPeerDoneIndex] = 0;
+      __threadfence();
+      atomicAdd(ctl + kPeerStepIndex, 1);
+    }
+  }
 }
 
-cudaError_t launch_lse_combine_wait(unsigned char* local_base, int world, int parity, unsigned expected, int BH,
+cudaError_t launch_lse_combine_wait(unsigned char* local_base, int world, unsigned epoch, int BH,
                                     int S_per_tile, int dtype, void* out, float* m_star, int* status,
                                     cudaStream_t stream) {
   if (dtype == 0)
-    lse_combine_wait_kernel<__nv_bfloat16><<<BH, 32, 0, stream>>>(local_base, world, parity, expected, BH, S_per_tile,
+    lse_combine_wait_kernel<__nv_bfloat16><<<BH, 32, 0, stream>>>(local_base, world, epoch, BH, S_per_tile,
                                                                  static_cast<__nv_bfloat16*>(out), m_star, status);
   else
-    lse_combine_wait_kernel<__half><<<BH, 32, 0, stream>>>(local_base, world, parity, expected, BH, S_per_tile,
+    lse_combine_wait_kernel<__half><<<BH, 32, 0, stream>>>(local_base, world, epoch, BH, S_per_tile,
                                                           static_cast<__half*>(out), m_star, status);
   return cudaGetLastError();
 }

@@ -186,8 +186,11 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
       // the same partial into every rank's exchange buffer: plain peer stores, made visible system-wide,
       // then one arrival count per receiver (released after the whole row is out)
       const int BH = int(gridDim.x);
+      int parity = p.px.parity;
+      if (parity < 0)  // device-counted epochs: this step is (steps completed so far) + 1
+        parity = (__ldcg(reinterpret_cast<const int*>(p.px.base[p.px.rank]) + kPeerStepIndex) + 1) & 1;
       for (int r = 0; r < p.px.world; ++r) {
-        float* po = reinterpret_cast<float*>(p.px.base[r] + peer_data_offset(p.px.parity, p.px.world, p.px.rank, BH)) +
+        float* po = reinterpret_cast<float*>(p.px.base[r] + peer_data_offset(parity, p.px.world, p.px.rank, BH)) +
                     bh * (kD + 2);
         po[4 * lane + 0] = acc.x;
         po[4 * lane + 1] = acc.y;
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(128) flash_merge_kernel(const FlashMergeParams
       __threadfence_system();
       __syncwarp();
       if (lane < p.px.world)
-        atomicAdd_system(reinterpret_cast<int*>(p.px.base[lane]) + p.px.parity * kMaxPeers + p.px.rank, 1);
+        atomicAdd_system(reinterpret_cast<int*>(p.px.base[lane]) + parity * kMaxPeers + p.px.rank, 1);
     }
     if (p.out != nullptr) {
       const float inv = (spt > 0 && zs > 0.f) ? 1.0f / (zs * (float)spt) : 0.f;

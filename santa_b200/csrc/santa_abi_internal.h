@@ -61,8 +61,10 @@ constexpr size_t kPeerFlagBytes = 256;  // int32 counters [2 parities][kMaxPeers
 __host__ __device__ inline size_t peer_data_offset(int parity, int world, int sender, int BH) {
   return kPeerFlagBytes + ((size_t(parity) * world + sender) * BH) * 130 * sizeof(float);
 }
+constexpr int kPeerDoneIndex = 32;   // int32 slots of the flag area: rows finished by the wait kernel
+constexpr int kPeerStepIndex = 33;   //   and the steps completed so far (device-counted epochs)
 struct PeerScatter {
-  int world, rank, parity;        // world == 0: no exchange
+  int world, rank, parity;        // world == 0: no exchange; parity < 0: epoch = local step counter + 1
   unsigned char* base[kMaxPeers]; // every rank's buffer as mapped here
 };
 
@@ -132,7 +134,8 @@ cudaError_t launch_rope_append(const RopeAppendParams& p, int dtype, cudaStream_
 
 // Cross-device combine of G unnormalised partials [G][BH][130].
 // Wait for `world` partials of one parity in the local exchange buffer, then combine them.
-cudaError_t launch_lse_combine_wait(unsigned char* local_base, int world, int parity, unsigned expected, int BH,
+// epoch == 0: the epoch is the buffer's own step counter + 1, advanced by the kernel when it is done.
+cudaError_t launch_lse_combine_wait(unsigned char* local_base, int world, unsigned epoch, int BH,
                                     int S_per_tile, int dtype, void* out, float* m_star, int* status,
                                     cudaStream_t stream);
 cudaError_t launch_lse_combine(const float* partials, int G, int BH, int S_per_tile, int dtype, void* out,

@@ -214,7 +214,7 @@ at::Tensor decode_systematic_partial(at::Tensor q_h, at::Tensor K_g, at::Tensor 
 
 santa_peer_exchange make_peer(const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch) {
   SANTA_CHECK(!peer_ptrs.empty() && peer_ptrs.size() <= 16, "peer_ptrs must hold 1..16 buffer addresses");
-  SANTA_CHECK(rank >= 0 && rank < (int64_t)peer_ptrs.size() && epoch >= 1, "bad rank / epoch of the peer exchange");
+  SANTA_CHECK(rank >= 0 && rank < (int64_t)peer_ptrs.size() && epoch >= 0, "bad rank / epoch of the peer exchange");
   santa_peer_exchange px{};
   px.world = (int)peer_ptrs.size();
   px.rank = (int)rank;

@@ -42,7 +42,10 @@ class PeerExchange:
     kernels store their partials straight into them -- no collective call per step.  One object serves
     one (B, H) problem shape on one stream; the ranks must call in lock-step (as with a collective)."""
 
-    def __init__(self, B: int, H: int, device, group=None):
+    def __init__(self, B: int, H: int, device, group=None, device_counted: bool = False):
+        # device_counted: the buffers count the steps themselves, so that the two calls of a step can be
+        # captured once in a CUDA graph and replayed (every rank must choose the same mode)
+        self.device_counted = bool(device_counted)
         self.B, self.H = int(B), int(H)
         self.device = torch.device(device)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -91,9 +94,10 @@ def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0
         if (exchange.B, exchange.H, exchange.world, exchange.rank) != (B, H, world, rank):
             raise RuntimeError("PeerExchange was built for another problem shape or group")
         exchange.epoch += 1
+        epoch = 0 if exchange.device_counted else exchange.epoch
         mod.decode_systematic_exchange(q, K_shard, V_shard, S, seed, bn, row1 - row0, 0, tile0, spt,
-                                       exchange.ptrs, rank, exchange.epoch)
-        return mod.lse_combine_wait(exchange.ptrs, rank, exchange.epoch, B, H, spt, q.dtype == torch.bfloat16,
+                                       exchange.ptrs, rank, epoch)
+        return mod.lse_combine_wait(exchange.ptrs, rank, epoch, B, H, spt, q.dtype == torch.bfloat16,
                                     exchange.status)
     if row1 > row0:
         part = mod.decode_systematic_partial(q, K_shard, V_shard, S, seed=seed, block_n=bn, valid_len=row1 - row0,

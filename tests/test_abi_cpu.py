@@ -110,11 +110,9 @@ def test_peer_exchange_layout_and_validation():
     for world, BH in ((1, 32), (2, 32), (8, 64), (16, 1024)):
         n = lib.santa_peer_exchange_bytes(world, BH)
         assert n % 256 == 0 and n >= 256 + 2 * world * BH * 130 * 4 and n < 256 + 2 * world * BH * 130 * 4 + 256
-    px = capi.PeerExchange(world=2, rank=0, epoch=0)
+    px = capi.PeerExchange(world=2, rank=0, epoch=1)
     px.peer_buffer[0], px.peer_buffer[1] = 256, 512
     cw = lib.santa_lse_combine_wait
-    assert cw(ctypes.byref(px), 32, 128, 1, 0, 256, None, None, None) == -8          # epoch 0
-    px.epoch = 1
     assert cw(ctypes.byref(px), 32, 64, 1, 0, 256, None, None, None) == -2           # D
     assert cw(ctypes.byref(px), 32, 128, 1, 9, 256, None, None, None) == -1          # dtype
     px.rank = 2

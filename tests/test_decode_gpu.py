@@ -644,6 +644,38 @@ def test_peer_exchange_on_one_device():
     o, m = mod.lse_combine_wait(ptrs, 0, 4, B, H, spt, True, status)
     torch.cuda.synchronize()
     assert status.item() == 4 and (o == 0).all()
+    # device-counted epochs: the same two calls, captured once in a CUDA graph, serve every step
+    bufs2 = [torch.zeros(nbytes, dtype=torch.uint8, device=dev()) for _ in range(G)]
+    ptrs2 = [b.data_ptr() for b in bufs2]
+    qs = q.clone()
+    shards = [(K[:, r0:r1].contiguous(), V[:, r0:r1].contiguous(), r1 - r0, t0) for r0, r1, t0 in plan]
+
+    def step_all_ranks():
+        for r, (Ks, Vs, n, t0) in enumerate(shards):
+            mod.decode_systematic_exchange(qs, Ks, Vs, S, 9, bn, n, 0, t0, spt, ptrs2, r, 0)
+        return [mod.lse_combine_wait(ptrs2, r, 0, B, H, spt, True, status) for r in range(G)]
+
+    status.zero_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        warm = step_all_ranks()                                            # step 1, eager
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    assert close(warm[0][0], full[0])
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        outs = step_all_ranks()
+    for k in range(3):                                                     # steps 2, 3, 4: replays
+        qs.copy_(q if k != 1 else (q * 0.5).to(torch.bfloat16))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = full if k != 1 else ops().flash_decode(qs, K, V, S, seed=9, valid_len=L)
+        for r in range(G):
+            assert close(outs[r][0], ref[0]) and bits_eq(outs[r][1], ref[1])
+    assert status.item() == 0
+    steps_done = bufs2[0][4 * 33:4 * 34].view(torch.int32).item()
+    assert steps_done == 4
     # the one-rank object goes through the same kernels
     ex = sharded.PeerExchange(B, H, dev())
     one = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L, exchange=ex)
