@@ -383,6 +383,32 @@ def main():
             ex.check()
         elif x_note is None:
             x_note = "peer exchange unavailable on another rank"
+        # ... and with the two calls of a step captured once in a CUDA graph (device-counted epochs)
+        t3g = None
+        if t3x is not None:
+            exg = sharded.PeerExchange(1, H, dev, device_counted=True)
+            q3 = qp3[0].clone()
+            side3 = torch.cuda.Stream()
+            side3.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side3):
+                for _ in range(2):
+                    sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
+            torch.cuda.current_stream().wait_stream(side3)
+            torch.cuda.synchronize()
+            graph3 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph3, stream=side3):
+                out3 = sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
+            graph3.replay()
+            exg.check()
+            same = torch.equal(out3[0], got3)
+            if max_over_ranks(0.0 if same else 1.0, world, dev) == 0.0:
+                def graph_step(i):
+                    q3.copy_(qp3[i % QPOOL])
+                    graph3.replay()
+
+                t3g = timed_loop(graph_step, n3, 5, world, dev)
+                exg.check()
+            del graph3
         if rank == 0:
             kb = L3 * KVH * D * 2
             line["seq_sharded_512k"] = {
@@ -393,7 +419,8 @@ def main():
                 "peer_exchange": ({"what": "partials stored into every rank's peer-mapped buffer by the merge kernel, "
                                            "bounded wait + combine kernel; no collective call",
                                    "steps_per_s": n3 / t3x, "ms_per_step": t3x / n3 * 1e3,
-                                   "k_gbs_total": kb / (t3x / n3) / 1e9} if t3x else x_note)}
+                                   "k_gbs_total": kb / (t3x / n3) / 1e9,
+                                   "ms_per_step_graph_replay": (t3g / n3 * 1e3) if t3g else None} if t3x else x_note)}
 
     # ---- extra: santa_prop on the ragged batch (BASELINE configs[2]), scalar entry point per sequence -----
     if not args.no_prop:
