@@ -242,7 +242,7 @@ const char* santa_strerror(int code) {
 }
 
 int santa_last_cuda_error(void) { return g_last_cuda_error; }
-int santa_abi_version(void) { return 1; }
+int santa_abi_version(void) { return 2; }
 
 int santa_block_n_rule(int L_valid, int block_n) {
   if (block_n > 0) return block_n;
