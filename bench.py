@@ -271,13 +271,27 @@ def main():
         stage_dev.copy_(stage_host, non_blocking=True)
         K[:, L - 1].copy_(k_new_dev)  # append this step's key/value row in place (fixed valid_len)
         V[:, L - 1].copy_(v_new_dev)
-        out = flash_mod.decode_systematic_batched(q_dev, K, V, S, seed=SEED, want_vrows=False, valid_len=L)[0]
-        out_host.copy_(out, non_blocking=True)
+        if direct_out:   # the merge kernel stores the result straight into the pinned host buffer
+            ops.flash_decode(q_dev, K, V, S, seed=SEED, valid_len=L, out=out_host)
+        else:
+            out = flash_mod.decode_systematic_batched(q_dev, K, V, S, seed=SEED, want_vrows=False, valid_len=L)[0]
+            out_host.copy_(out, non_blocking=True)
 
     # The whole step (copies in, KV append, decode, copy out) is captured once into a CUDA graph, as a
     # serving loop would do, and replayed per step; the step's q is first written into the pinned staging
     # buffer by the host.  If capture is not possible the step runs eagerly.
     q_stage.copy_(q_host[0])
+    # first through the reference-facing module + an explicit copy out (the reference's calling pattern),
+    # to have its result; then the timed variant, whose output goes straight to the host buffer
+    direct_out = False
+    e2e_body()
+    torch.cuda.synchronize()
+    module_out = out_host.clone()
+    direct_out = True
+    out_host.zero_()
+    e2e_body()
+    torch.cuda.synchronize()
+    assert torch.equal(module_out, out_host), "direct-to-host output differs from the module's output"
     graph = None
     try:
         side = torch.cuda.Stream()
@@ -300,7 +314,7 @@ def main():
         graph = None
         e2e_note = f"eager (graph capture failed: {str(exc)[:80]})"
     else:
-        e2e_note = "cuda graph replay per step"
+        e2e_note = "cuda graph replay per step; result stored by the merge kernel into the pinned host buffer"
 
     def e2e_step(i):
         q_stage.copy_(q_host[i % QPOOL])  # host-side write of this step's q into the staging buffer

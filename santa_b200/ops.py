@@ -86,10 +86,12 @@ def _check_flash_inputs(q_h, K_g, V_g):
 
 
 def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_len=-1, *,
-                 batch_offset=0, tile_offset=0, s_per_tile=None, partial=False, trace=False):
+                 batch_offset=0, tile_offset=0, s_per_tile=None, partial=False, trace=False, out=None):
     """S2ANTA-Flash decode.  Returns ``(out, m_star, vrows)``; with ``partial=True``
     the first element is the unnormalised partial ``[B,H,130]`` fp32 instead of
-    ``out``; with ``trace=True`` a ``FlashTrace`` is appended."""
+    ``out``; with ``trace=True`` a ``FlashTrace`` is appended.  ``out`` may name the result buffer: a
+    contiguous tensor of q's shape and dtype on q's device, or in PINNED HOST memory -- the merge kernel
+    then stores the result straight into the caller's host buffer (no separate device-to-host copy)."""
     batched, B, H, D, L_storage, KVH = _check_flash_inputs(q_h, K_g, V_g)
     if seed < 0:
         raise TypeError("seed must be a non-negative 64-bit integer")
@@ -112,7 +114,14 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
         nbytes = lib.santa_flash_workspace_bytes(B, KVH, L, bn)
         ws = _workspace("flash", dev, nbytes)
         fopt = dict(device=dev, dtype=torch.float32)
-        out = None if partial else torch.empty((B, H, D) if batched else (H, D), device=dev, dtype=q.dtype)
+        if out is not None:
+            _check(not partial, "out= and partial=True exclude each other")
+            _check(out.dtype == q.dtype and tuple(out.shape) == ((B, H, D) if batched else (H, D))
+                   and out.is_contiguous(), "out must be a contiguous tensor of q's shape and dtype")
+            _check((out.is_cuda and out.device == dev) or (not out.is_cuda and out.is_pinned()),
+                   "out must live on q's device or in pinned host memory")
+        elif not partial:
+            out = torch.empty((B, H, D) if batched else (H, D), device=dev, dtype=q.dtype)
         m_star = torch.empty((B, H) if batched else (H,), **fopt)
         vrows = torch.empty((B, KVH) if (want_vrows and batched) else ((KVH,) if want_vrows else (0,)),
                             device=dev, dtype=torch.int32)
