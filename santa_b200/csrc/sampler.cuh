@@ -122,7 +122,8 @@ struct RowTrace {
 // Returns the number of gathered rows.
 // ROUNDED: sb already holds values of the storage type (Prop's second pass reads them from the
 // stash), so the rounding step is skipped.
-template <typename TK, bool ROUNDED = false>
+// TWO: two chunks per iteration (more instruction-level parallelism, more registers) or one.
+template <typename TK, bool ROUNDED = false, bool TWO = true>
 __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, const float (&invdel)[kGH],
                                            const float (&a0)[kGH], const RowTrace& tr) {
   const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
@@ -135,14 +136,14 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
   // the eight (chunk, head) chains are issued back to back and their latencies overlap.  Only the
   // final additions of B need A's chunk total (the carried prefix).
 #pragma unroll 1
-  for (int ch = 0; ch < nch; ch += 2) {
+  for (int ch = 0; ch < nch; ch += (TWO ? 2 : 1)) {
     const int remainA = tile_len - ch * kChunkRows;
     const int remainB = remainA - kChunkRows;  // <= 0 when chunk B does not exist
-    const bool hasB = remainB > 0;
+    const bool hasB = TWO && remainB > 0;
     const int lastA = remainA > 32 ? 31 : remainA - 1;
     const int lastB = remainB > 32 ? 31 : (hasB ? remainB - 1 : 0);
     const bool validA = lane < remainA;
-    const bool validB = lane < remainB;
+    const bool validB = TWO && lane < remainB;
     const float4 uA4 = sb[ch * kChunkRows + lane];
     const float4 uB4 = hasB ? sb[(ch + 1) * kChunkRows + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
     const float uA[kGH] = {uA4.x, uA4.y, uA4.z, uA4.w};
