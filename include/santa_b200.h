@@ -129,7 +129,8 @@ SANTA_API size_t santa_flash_workspace_bytes(int B, int KVH, int L_valid, int bl
  *
  *   q      [B,H,D]            storage dtype, contiguous
  *   K, V   [B,L_storage,KVH,D] storage dtype, contiguous; rows [0,L_valid) are used
- *   out    [B,H,D]            storage dtype
+ *   out    [B,H,D]            storage dtype; device memory, or pinned (device-accessible) host memory --
+ *                             the merge kernel then stores the result over the bus, no separate copy
  *   m_star [B,H]              fp32, max scaled score per head
  *   vrows  [B,KVH] int32 or NULL: number of distinct V rows gathered
  * Requires D == 128, H == 4*KVH, block_n in {0,32,64,256}, 16-byte aligned q/K/V/out.
