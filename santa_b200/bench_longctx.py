@@ -30,7 +30,7 @@ def parse_args(argv=None):
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--max-new-tokens", type=int, default=32)
     ap.add_argument("--prefill-chunk-size", type=int, default=512)
-    ap.add_argument("--backends", nargs="+", default=["santa_flash"], choices=["santa_flash", "sdpa"])
+    ap.add_argument("--backends", nargs="+", default=["santa_flash"], choices=["santa_flash", "santa_prop", "sdpa"])
     ap.add_argument("--santa-s", type=int, default=256)
     ap.add_argument("--santa-seed", type=int, default=1690)
     ap.add_argument("--santa-block-n", type=int, default=0)
@@ -61,7 +61,7 @@ def run_batch(rt: DecodeRuntime, args, batch_id: int, prompt_ids: torch.Tensor):
         last = rt.prefill(prompt_ids, chunk=args.prefill_chunk_size)
     torch.cuda.synchronize(dev)
     prefill_s = time.perf_counter() - w0
-    res = rt.generate(last, args.prompt_len, args.max_new_tokens, use_graph=(rt.attention == "santa_flash"))
+    res = rt.generate(last, args.prompt_len, args.max_new_tokens, use_graph=(rt.attention != "sdpa"))
     torch.cuda.synchronize(dev)
     wall_s = time.perf_counter() - w0
     toks = res["generated_token_ids_all"].tolist()
@@ -104,7 +104,7 @@ def main(argv=None) -> None:
                 batch_rows.extend(rows)
                 summary = report.run_metric(rows)
                 summary.update({"phase": phase, "run_idx": run_idx, "backend": backend,
-                                "backend_actual_mode": "ragged-device-lengths" if backend == "santa_flash" else "dense"})
+                                "backend_actual_mode": "dense" if backend == "sdpa" else "ragged-device-lengths"})
                 run_rows.append(summary)
                 print(f"[{phase} run {run_idx}] backend={backend:<12} decode={summary['decode_time_s']:.3f}s "
                       f"output_tok/s={summary['output_tokens_per_s']:.2f} tpot_ms={summary['tpot_ms']:.3f}")

@@ -47,7 +47,8 @@ class LlamaShape:
 class DecodeRuntime:
     """Random-initialised (or externally loaded) Llama-style model with NHD caches.
 
-    attention: "santa_flash" (S samples per head, this package's kernels) or "sdpa" (dense
+    attention: "santa_flash" / "santa_prop" (S samples per head, this package's kernels; fixed per-tile
+    budget / budget proportional to the tiles' softmax mass, 256-row tiles) or "sdpa" (dense
     ``scaled_dot_product_attention`` over the cache, the reference's SDPABackend,
     tutorial_code/attention_backends.py:76-89).
     """
@@ -57,7 +58,7 @@ class DecodeRuntime:
                  block_n: int = 0, init_std: float = 0.02):
         if shape.head_dim != 128 or shape.heads != 4 * shape.kv_heads:
             raise RuntimeError("This build supports only D=128 and GH=4 (H/KVH)")
-        if attention not in ("santa_flash", "sdpa"):
+        if attention not in ("santa_flash", "santa_prop", "sdpa"):
             raise ValueError(f"unknown attention backend {attention!r}")
         self.shape, self.B, self.T = shape, int(batch), int(total_len)
         self.dev, self.dtype = torch.device(device), dtype
@@ -95,11 +96,12 @@ class DecodeRuntime:
         self._graph_max_len = 0
         self._graph_stream: Optional[torch.cuda.Stream] = None
         self.attn_events: Optional[list] = None   # filled by eager steps when profiling is on
-        if attention == "santa_flash":
+        if attention in ("santa_flash", "santa_prop"):
             import santa_b200
             santa_b200.enable_dropin()
             import santa_flash_batch_cuda
-            self._flash = santa_flash_batch_cuda
+            import santa_prop_batch_cuda
+            self._flash, self._prop = santa_flash_batch_cuda, santa_prop_batch_cuda
         self._bn = 0  # tile size the captured graph was planned for
 
     # ------------------------------------------------------------------ helpers
@@ -193,6 +195,10 @@ class DecodeRuntime:
             return self._flash.decode_systematic_ragged(q_bhd, self.k_cache[li], self.v_cache[li], self.seq_lens,
                                                         self.S, seed=self.attn_seed, block_n=self._bn,
                                                         want_vrows=False, max_len=max_len)[0]
+        if self.attention == "santa_prop":
+            return self._prop.decode_systematic_ragged(q_bhd, self.k_cache[li], self.v_cache[li], self.seq_lens,
+                                                       self.S, seed=self.attn_seed, want_vrows=False,
+                                                       max_len=max_len)[0]
         # dense reference backend over the valid prefix (host-known bound; eager only)
         L = int(max_len)
         kk = self.k_cache[li][:, :L].permute(0, 2, 1, 3)
@@ -232,8 +238,8 @@ class DecodeRuntime:
     def capture(self, max_len: int) -> None:
         """Capture the step for caches up to ``max_len`` rows long (the tile size is fixed per capture:
         the reference's rule applied to ``max_len``)."""
-        if self.attention != "santa_flash":
-            raise RuntimeError("only the santa_flash step is graph-capturable (its lengths live on the device)")
+        if self.attention == "sdpa":
+            raise RuntimeError("only the sampled-attention steps are graph-capturable (their lengths live on the device)")
         self._bn = self._plan_tile(max_len)
         saved = (self.pos.clone(), self.tok.clone())
         stream = torch.cuda.Stream(device=self.dev)
@@ -276,7 +282,7 @@ class DecodeRuntime:
         cur_logits = prefill_logits_last.to(dev).float().contiguous()
         self.pos.fill_(prompt_len)
         max_len = prompt_len + max_new_tokens
-        if use_graph and self.attention == "santa_flash" and (self._graph is None or max_len > self._graph_max_len):
+        if use_graph and self.attention != "sdpa" and (self._graph is None or max_len > self._graph_max_len):
             self.capture(max_len)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
@@ -293,7 +299,7 @@ class DecodeRuntime:
             if lockstep_stop_mode == "all_finished" and bool(finished.all().item()):
                 break
             self.tok.copy_(next_ids)
-            if use_graph and self.attention == "santa_flash":
+            if use_graph and self.attention != "sdpa":
                 self.step(max_len)
             else:
                 self._bn = self._plan_tile(prompt_len + step + 1)

@@ -29,12 +29,13 @@ def test_decode_steps_equal_prefill_of_the_extended_prompt():
     assert torch.equal(last.argmax(-1), toks[:, 0])
 
 
-def test_graph_replay_of_the_sampled_step_equals_eager_and_stops_in_lockstep():
+@pytest.mark.parametrize("backend", ["santa_flash", "santa_prop"])
+def test_graph_replay_of_the_sampled_step_equals_eager_and_stops_in_lockstep(backend):
     dev = torch.device("cuda:0")
     B, L, new = 3, 700, 6
     outs = []
     for use_graph in (False, True):
-        rt = DecodeRuntime(SHAPE, B, 1024, dev, attention="santa_flash", S=64, init_std=0.05)
+        rt = DecodeRuntime(SHAPE, B, 1024, dev, attention=backend, S=64, init_std=0.05)
         rt.fill_cache_synthetic(L, seed=4)
         first = torch.zeros(B, 1000, device=dev)
         first[:, 7] = 1.0
@@ -46,7 +47,7 @@ def test_graph_replay_of_the_sampled_step_equals_eager_and_stops_in_lockstep():
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert torch.equal(outs[0][2], outs[1][2])
     # stop tokens: a finished sequence keeps emitting the stop token; "all_finished" ends the loop early
-    rt = DecodeRuntime(SHAPE, B, 1024, dev, attention="santa_flash", S=64, init_std=0.05)
+    rt = DecodeRuntime(SHAPE, B, 1024, dev, attention=backend, S=64, init_std=0.05)
     rt.fill_cache_synthetic(L, seed=4)
     first = torch.zeros(B, 1000, device=dev)
     first[:, 7] = 1.0
