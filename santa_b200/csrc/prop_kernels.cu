@@ -310,9 +310,25 @@ constexpr bool kPass2TwoChunks = true;
 
 // One warp per (kv-head, tile range): counts from the stash, compaction,
 // sparse V sum (santa_cuda_kernel.cu:771-863), tiles in ascending order.
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// dynamic shared memory of one pass-2 CTA: per warp a tile of unpacked weights (later the emit
+// list), the raw stash rows of the tile being fetched, and that tile's four steps and offsets
+constexpr int kPass2RawBytes = kMaxTileRows * 8;
+constexpr int kPass2WarpSmem = kMaxTileRows * 16 + kPass2RawBytes + 32;
+constexpr int kPass2Smem = kPass2Warps * kPass2WarpSmem;
+
 template <typename TK>
 __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_kernel(const Pass2Params p) {
-  __shared__ __align__(16) float4 s_buf[kPass2Warps][kMaxTileRows];
+  extern __shared__ __align__(16) unsigned char s_dyn[];
   __shared__ int s_start[kMaxRaggedSeqs + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool ragged = p.seq_lens != nullptr;
@@ -330,8 +346,11 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
   const int vg = blockIdx.x * kPass2Warps + warp;
   if (vg >= nvg) return;
   const long long lo = range_lo(vg, items, nvg), hi = range_lo(vg + 1, items, nvg);
-  float4* sb = s_buf[warp];
+  float4* sb = reinterpret_cast<float4*>(s_dyn + size_t(warp) * kPass2WarpSmem);
+  uint2* raw = reinterpret_cast<uint2*>(s_dyn + size_t(warp) * kPass2WarpSmem + kMaxTileRows * 16);
+  float* par = reinterpret_cast<float*>(s_dyn + size_t(warp) * kPass2WarpSmem + kMaxTileRows * 16 + kPass2RawBytes);
   const size_t row_stride = size_t(p.KVH) * kRowBytes;
+  const size_t ls = size_t(p.len_stride);
 
   long long it = lo;
   while (it < hi) {
@@ -352,6 +371,7 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
     const size_t bh0 = size_t(b) * p.H + h0;
     const unsigned char* vcol =
         static_cast<const unsigned char*>(p.V) + (size_t(b) * p.L_storage * p.KVH + kv) * kRowBytes;
+    const uint2* stash_col = reinterpret_cast<const uint2*>(p.stash) + (size_t(b) * p.KVH + kv) * ls;
     float acc[kGH][4];
 #pragma unroll
     for (int g = 0; g < kGH; ++g)
@@ -359,32 +379,50 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
       for (int i = 0; i < 4; ++i) acc[g][i] = 0.f;
     int vrow_count = 0;
 
-#pragma unroll 1
-    for (int t = t_lo; t < t_hi; ++t) {
-      float invdel[kGH], a0[kGH];
-#pragma unroll
-      for (int g = 0; g < kGH; ++g) invdel[g] = __ldcg(p.invdelta + (bh0 + g) * p.tile_stride + t);
-      // a tile without budget on any of its four heads samples nothing: every count is zero
-      if (!(invdel[0] > 0.f || invdel[1] > 0.f || invdel[2] > 0.f || invdel[3] > 0.f)) continue;
-#pragma unroll
-      for (int g = 0; g < kGH; ++g) a0[g] = __ldcg(p.a0 + (bh0 + g) * p.tile_stride + t);
+    // Asynchronous fetch of a tile's stash rows (one 8-byte word per row) and of its four steps and
+    // offsets into this warp's shared memory: issued one tile ahead, so that the latency of the
+    // second pass's only streamed input hides behind the previous tile's counting and gathering.
+    auto fetch = [&](int t) {
       const int n0 = t * p.bn;
       const int tile_len = (L_b - n0 < p.bn) ? (L_b - n0) : p.bn;
-      const size_t ls = size_t(p.len_stride);
-      // the tile's rounded weights: one 8-byte word per row, all loads in flight together
-      const uint2* sp = reinterpret_cast<const uint2*>(p.stash) + (size_t(b) * p.KVH + kv) * ls + n0;
-      uint2 w[kMaxTileRows / kChunkRows];
 #pragma unroll
       for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
         const int r = ch * kChunkRows + lane;
-        w[ch] = (r < tile_len) ? __ldcg(sp + r) : make_uint2(0u, 0u);
+        if (r < tile_len) cp_async8(raw + r, stash_col + n0 + r);
       }
-#pragma unroll
-      for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
-        const float2 f01 = Store16<TK>::unpack(w[ch].x), f23 = Store16<TK>::unpack(w[ch].y);
-        sb[ch * kChunkRows + lane] = make_float4(f01.x, f01.y, f23.x, f23.y);
+      if (lane < 2 * kGH) {
+        const float* src = (lane < kGH ? p.invdelta : p.a0) + (bh0 + (lane & (kGH - 1))) * p.tile_stride + t;
+        cp_async4(par + lane, src);
       }
+    };
+    fetch(t_lo);
+
+#pragma unroll 1
+    for (int t = t_lo; t < t_hi; ++t) {
+      cp_async_wait_all();
       __syncwarp();
+      float invdel[kGH], a0[kGH];
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        invdel[g] = par[g];
+        a0[g] = par[kGH + g];
+      }
+      const int n0 = t * p.bn;
+      const int tile_len = (L_b - n0 < p.bn) ? (L_b - n0) : p.bn;
+      // a tile without budget on any of its four heads samples nothing: every count is zero
+      const bool empty = !(invdel[0] > 0.f || invdel[1] > 0.f || invdel[2] > 0.f || invdel[3] > 0.f);
+      if (!empty) {
+#pragma unroll
+        for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
+          const int r = ch * kChunkRows + lane;
+          const uint2 w = (r < tile_len) ? raw[r] : make_uint2(0u, 0u);
+          const float2 f01 = Store16<TK>::unpack(w.x), f23 = Store16<TK>::unpack(w.y);
+          sb[r] = make_float4(f01.x, f01.y, f23.x, f23.y);
+        }
+      }
+      __syncwarp();                      // raw and par are consumed: the next tile may land
+      if (t + 1 < t_hi) fetch(t + 1);
+      if (empty) continue;
       RowTrace tr;
       tr.head_stride = ls;
       tr.u16 = nullptr;
@@ -543,6 +581,7 @@ static cudaError_t launch_dependent(KernelT kernel, dim3 grid, dim3 block, size_
 template <typename TK>
 static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t stream) {
   static bool configured[64] = {};
+  static bool configured2[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   cudaError_t e;
@@ -613,7 +652,12 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   p2.dbg_c = p.dbg_c;
   p2.rowmask = p.rowmask;
   const int grid2 = (p2.ws.nvg + kPass2Warps - 1) / kPass2Warps;
-  e = launch_dependent(prop_pass2_kernel<TK>, dim3(grid2), dim3(kPass2Warps * 32), 0, stream, p2);
+  if (dev >= 0 && dev < 64 && !configured2[dev]) {
+    e = cudaFuncSetAttribute(prop_pass2_kernel<TK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPass2Smem);
+    if (e != cudaSuccess) return e;
+    configured2[dev] = true;
+  }
+  e = launch_dependent(prop_pass2_kernel<TK>, dim3(grid2), dim3(kPass2Warps * 32), kPass2Smem, stream, p2);
   if (e != cudaSuccess) return e;
 
   PropMergeParams pm{};
