@@ -76,3 +76,35 @@ def test_longctx_harness_writes_the_reference_files(tmp_path):
     assert [r["backend"] for r in rows] == ["santa_flash", "sdpa"] and rows[0]["runs"] == "2"
     agree = json.load(open(out / "backend_agreement.json"))
     assert agree[0]["backend_a"] == "santa_flash" and agree[0]["comparable_examples"] == 4
+
+
+def test_backend_objects_follow_the_reference_adapter_contract():
+    """decode(q_bhd, k_nhd, v_nhd, valid_len) of the backend objects: Flash equals the module call; Prop's
+    single ragged call equals the reference adapter's per-sequence loop in tolerance; dense sdpa is close
+    to a large-S sampled estimate; valid_len may be a device tensor."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import cases
+    from santa_b200 import backends
+    dev = torch.device("cuda:0")
+    q, K, V = cases.make_qkv(3, 6000, 8, "bf16", 99, 1.0, True)
+    q, K, V = q.to(dev), K.to(dev), V.to(dev)
+    L = 5000
+    fb = backends.make_backend("santa_flash", santa_s=256, santa_seed=7)
+    out = fb.decode(q, K, V, L)
+    assert fb.actual_mode == "batch" and out.shape == (3, 32, 128) and fb.info()["module"] == "santa_flash_batch_cuda"
+    assert torch.equal(out, fb.module.decode_systematic_batched(q, K, V, 256, seed=7, valid_len=L)[0])
+    lens = torch.full((3,), L, dtype=torch.int32, device=dev)
+    out_t = fb.decode(q, K, V, lens)
+    assert fb.actual_mode == "batch_ragged" and (out_t.float() - out.float()).abs().max().item() <= 2e-2
+    pb = backends.make_backend("santa_prop", santa_s=256, santa_seed=7)
+    pl = backends.SantaPropBackend(S=256, seed=7, loop=True)
+    o_r, o_l = pb.decode(q, K, V, L), pl.decode(q, K, V, L)
+    assert (pb.actual_mode, pl.actual_mode) == ("batch_ragged", "single_loop_fallback")
+    assert (o_r.float() - o_l.float()).abs().max().item() <= 2e-2
+    dense = backends.make_backend("sdpa").decode(q, K, V, L)
+    big = backends.SantaFlashBackend(S=L * 8, seed=7).decode(q, K, V, L)
+    assert (big.float() - dense.float()).abs().mean().item() < 0.05
+    with pytest.raises(backends.BackendError):
+        backends.make_backend("fa2")
