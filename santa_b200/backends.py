@@ -35,6 +35,24 @@ class DecodeAttentionBackend:
     def info(self) -> Dict[str, Any]:
         return {"name": self.name, "exact_attention": self.exact_attention}
 
+    def smoke_test(self, *, device, dtype, num_heads: int, num_kv_heads: int, head_dim: int,
+                   valid_len: int = 16) -> Dict[str, Any]:
+        """Two random sequences of ``valid_len`` cached tokens through ``decode``; the output must have
+        the query's shape and be finite (the reference's start-up check of a backend,
+        attention_backends.py:41-67, which looks at the shape only)."""
+        B = 2
+        q = torch.randn(B, num_heads, head_dim, device=device, dtype=dtype)
+        k = torch.randn(B, valid_len, num_kv_heads, head_dim, device=device, dtype=dtype)
+        v = torch.randn(B, valid_len, num_kv_heads, head_dim, device=device, dtype=dtype)
+        out = self.decode(q, k, v, valid_len)
+        if tuple(out.shape) != (B, num_heads, head_dim):
+            raise BackendError(f"Smoke test returned wrong shape for {self.name}: got {tuple(out.shape)}, "
+                               f"expected {(B, num_heads, head_dim)}")
+        if not bool(torch.isfinite(out.float()).all()):
+            raise BackendError(f"Smoke test of {self.name} produced non-finite values")
+        return {"backend": self.name, "batch_size": B, "valid_len": int(valid_len),
+                "output_shape": list(out.shape), **self.info()}
+
 
 class SDPABackend(DecodeAttentionBackend):
     """Dense, exact attention over the valid prefix (the reference's CPU-runnable backend)."""

@@ -4,7 +4,7 @@
         --max-new-tokens 32 --backends santa_flash sdpa --timed-runs 3
 
 Writes ``config.json``, ``batch_metrics.jsonl``, ``run_metrics.jsonl``, ``generations.jsonl``,
-``aggregates.json``, ``aggregates.csv`` and ``backend_agreement.json`` into the output directory, with
+``aggregates.json``, ``aggregates.csv``, ``backend_agreement.json`` and ``invocation.json`` into the output directory, with
 the field names of tutorial_code/benchmark_longctx.py (:350-369, :396-425, :486-530, :656-722) of
 the reference.  The model is random-initialised from the given shape and the prompts are uniform
 random token ids: there are no weights, tokenizer or evaluation prompts to load, so text and
@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import sys
 import time
 
 import torch
@@ -118,6 +119,8 @@ def main(argv=None) -> None:
     report.write_aggregate_csv(os.path.join(args.out_dir, "aggregates.csv"), agg)
     report.write_json(os.path.join(args.out_dir, "backend_agreement.json"),
                       report.token_agreement([r for r in gen_rows if r["phase"] == "timed"]))
+    report.write_json(os.path.join(args.out_dir, "invocation.json"),
+                      {"argv": list(sys.argv if argv is None else argv), "args": vars(args)})
     report.write_json(os.path.join(args.out_dir, "config.json"), {
         "model_name": f"random-init Llama shape {vars(shape)}", "dataset": "uniform random token ids",
         "batch_size": args.batch_size, "warmup_runs": args.warmup_runs, "timed_runs": args.timed_runs,

@@ -64,7 +64,7 @@ def test_longctx_harness_writes_the_reference_files(tmp_path):
                         "--backends", "santa_flash", "sdpa", "--timed-runs", "2", "--warmup-runs", "1",
                         "--layers", "2", "--hidden", "512", "--heads", "4", "--kv-heads", "1",
                         "--intermediate", "1024", "--vocab", "1000", "--prefill-chunk-size", "128"])
-    names = {"config.json", "batch_metrics.jsonl", "run_metrics.jsonl", "generations.jsonl", "aggregates.json",
+    names = {"invocation.json", "config.json", "batch_metrics.jsonl", "run_metrics.jsonl", "generations.jsonl", "aggregates.json",
              "aggregates.csv", "backend_agreement.json"}
     assert names <= {p.name for p in out.iterdir()}
     runs = [json.loads(x) for x in open(out / "run_metrics.jsonl")]
@@ -108,3 +108,7 @@ def test_backend_objects_follow_the_reference_adapter_contract():
     assert (big.float() - dense.float()).abs().mean().item() < 0.05
     with pytest.raises(backends.BackendError):
         backends.make_backend("fa2")
+    # the start-up check of the reference (two sequences of 16 cached tokens): 32-row tiles, one tile
+    for b in (fb, pb, pl, backends.make_backend("sdpa")):
+        rep = b.smoke_test(device=dev, dtype=torch.bfloat16, num_heads=32, num_kv_heads=8, head_dim=128, valid_len=16)
+        assert rep["output_shape"] == [2, 32, 128] and rep["backend"] == b.name
