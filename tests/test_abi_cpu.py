@@ -124,3 +124,14 @@ def test_peer_exchange_layout_and_validation():
     rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 128, 16, 16, 4, 1, 0, None, None, None, None, 0,
                                 ctypes.byref(ext), None)
     assert rc == -8
+
+
+def test_public_header_is_plain_c():
+    """include/santa_b200.h is what a cgo / JNI / FFI binding includes: it must compile as C and as C++."""
+    import shutil
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "santa_b200.h")
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", hdr])
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", hdr])
