@@ -135,3 +135,18 @@ def test_public_header_is_plain_c():
         pytest.skip("no gcc")
     subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", hdr])
     subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", hdr])
+
+
+def test_library_is_self_contained():
+    """The C-ABI library depends on neither PyTorch nor Python, and exports nothing but its santa_* API."""
+    import shutil
+    import subprocess
+    if shutil.which("ldd") is None or shutil.which("nm") is None:
+        pytest.skip("no binutils")
+    deps = subprocess.check_output(["ldd", capi.LIB_PATH], text=True)
+    for forbidden in ("torch", "c10", "python", "libcuda.so"):
+        assert forbidden not in deps, deps
+    syms = subprocess.check_output(["nm", "-D", "--defined-only", capi.LIB_PATH], text=True).split("\n")
+    funcs = [ln.split()[-1] for ln in syms if " T " in ln]
+    assert funcs and all(f.startswith("santa_") for f in funcs), funcs
+    assert sorted(funcs) == sorted(capi.EXPORTS)
