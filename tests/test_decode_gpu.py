@@ -14,6 +14,7 @@ from oracle import santa_oracle as so
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+HERE = os.path.dirname(os.path.abspath(__file__))
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 HAVE_REF = ref_gpu.available()
 needs_ref = pytest.mark.skipif(not HAVE_REF, reason="oracle/_ref not built (needs the reference tree)")
@@ -682,3 +683,36 @@ def test_peer_exchange_on_one_device():
     two = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L, exchange=ex)
     ex.check()
     assert close(one[0], full[0]) and bits_eq(one[1], full[1]) and torch.equal(one[0], two[0])
+
+
+def test_c_abi_from_a_plain_cxx_host(tmp_path):
+    """tests/capi_host.cu -- a C++ program without PyTorch -- linked against libsanta_b200.so: its output
+    equals the Python mirror's on the same generated bits."""
+    import shutil
+    import subprocess
+    from santa_b200 import capi
+    if shutil.which("nvcc") is None:
+        pytest.skip("no nvcc on this box")
+    exe = str(tmp_path / "capi_host")
+    libdir = os.path.dirname(capi.LIB_PATH)
+    subprocess.check_call(["nvcc", "-O1", "-std=c++17", "-o", exe, os.path.join(HERE, "capi_host.cu"),
+                           "-L" + libdir, "-lsanta_b200", "-Xlinker", "-rpath," + libdir])
+    B, L, KVH, S, seed = 2, 3000, 2, 96, 1690
+    txt = subprocess.check_output([exe, str(B), str(L), str(KVH), str(S), str(seed)], text=True, timeout=120)
+    lines = dict(ln.split(" ", 1) for ln in txt.strip().split("\n"))
+    assert lines["status"] == "0"
+    # the same recurrence in Python
+    n = B * 4 * KVH * 128 + 2 * B * L * KVH * 128
+    st, vals = 12345, np.empty(n, dtype=np.float32)
+    for i in range(n):
+        st = (st * 1664525 + 1013904223) & 0xffffffff
+        vals[i] = (((st >> 16) & 0xff) - 128) / 64.0
+    t = torch.from_numpy(vals).to(torch.bfloat16)
+    nq, nk = B * 4 * KVH * 128, B * L * KVH * 128
+    q = t[:nq].view(B, 4 * KVH, 128).to(dev())
+    K = t[nq:nq + nk].view(B, L, KVH, 128).to(dev())
+    V = t[nq + nk:].view(B, L, KVH, 128).to(dev())
+    out, m_star, vrows = ops().flash_decode(q, K, V, S, seed=seed, want_vrows=True)
+    assert [int(x) for x in lines["vrows"].split()] == vrows.flatten().tolist()
+    got = np.array([int(x) for x in lines["out"].split()], dtype=np.uint16)
+    assert (got == cases.bits(out).reshape(-1)).all()
