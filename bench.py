@@ -3,18 +3,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N=1): the configuration the headline metric is quoted on -- santa_flash, B=8
-sequences, Hq=32, Hkv=8, head_dim=128, context 32768, S=256, seed 1690, bf16, K/V ~ N(0,1)
-with 1% planted heavy hitters, a fresh q every step (pool of 16).  One "step" is one decode call
-over the whole batch.  N>1 (torchrun, one rank per GPU): every rank owns its own batch of 8
-sequences (batch sharding, no data-path collective, weak scaling); the time is the max over ranks.
+Workload (N=1): santa_flash, B=8 sequences, Hq=32, Hkv=8, head_dim=128, context 32768, S=256,
+seed 1690, bf16, K/V ~ N(0,1) with 1% planted heavy hitters, a fresh q every step (pool of 16).
+One "step" is one decode call over the whole batch.  N>1 (torchrun, one rank per GPU): every rank
+owns its own batch of 8 sequences (batch sharding, no data-path collective, weak scaling).
+
+Timing: W warm-up steps, then blocks of exactly K steps, each block between a barrier +
+synchronize on both sides and timed by CUDA events on the launching stream; blocks are repeated
+until about a second of device time has passed.  `ms_per_step` is the median block (max over the
+ranks' medians), with min / max / repeats and -- at N>1 -- every rank's median beside it.  SM clocks
+and throttle reasons are sampled through NVML every few milliseconds during the timed region.
 
 The JSON line carries: `value` = steps/s with inputs resident in HBM (C-ABI path), `e2e` = the same
 through the reference-facing module santa_flash_batch_cuda with this step's q / new k,v rows copied
-from pinned host memory and the output copied back inside the timed region (the KV cache itself is
-resident device state, as in the reference's runtime), `roofline` for the streaming kernel against
-the measured HBM copy peak, `cpu_baseline` (dense SDPA on the host cores, the reference's only
-CPU-runnable backend) and, as extra evidence, the sequence-sharded 512k-context case.
+from pinned host memory and the output stored to host memory inside the timed region (the KV cache
+itself is resident device state, as in the reference's runtime), `roofline` for the streaming
+kernel against the measured HBM copy peak, `cpu_baseline` (dense SDPA on the host cores, the
+reference's only CPU-runnable backend), `vs_reference_cuda_kernels` (the reference's own kernels,
+compiled unmodified for sm_100a, timed in the same process on the same inputs) and, as extra
+evidence, the ragged santa_prop batch, the sequence-sharded 512k-context case and an end-to-end
+Llama-3.1-8B-shaped decode.
 """
 from __future__ import annotations
 
@@ -24,6 +32,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -33,7 +42,10 @@ import torch  # noqa: E402
 
 B, H, KVH, D, L, S, SEED = 8, 32, 8, 128, 32768, 256, 1690
 QPOOL = 16
-WORKLOAD = f"santa_flash B={B} Hq={H} Hkv={KVH} D={D} L={L} S={S} seed={SEED} bf16 (BASELINE configs[1])"
+WORKLOAD = f"santa_flash B={B} Hq={H} Hkv={KVH} D={D} L={L} S={S} seed={SEED} bf16, 1% heavy hitters"
+PROP_WORKLOAD = "santa_prop B=16 ragged L in [8192,65536] (seed-7 draw, sum 562962) S=256"
+MIN_TIMED_S = 1.0      # device time to accumulate over the repeated K-step blocks
+MAX_BLOCKS = 2000
 
 
 def measured_peak_gbs():
@@ -63,48 +75,103 @@ def make_inputs(dev, seed, batch=B, length=L, heavy=True):
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples of one GPU during the timed region."""
+    """SM clock / throttle-reason samples of one GPU, read through NVML (what nvidia-smi reads) by a
+    thread every few milliseconds; `nvidia-smi -lms` is the fallback.  Only reads, never sets."""
 
-    def __init__(self, index):
-        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
+
+    def __init__(self, cuda_index, period_s=0.004):
+        self.samples = []          # (t, sm_mhz, reason mask)
+        self.marks = []            # (t0, t1) windows that count
+        self.sm_max = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._smi = None
         try:
-            self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={q}",
-                                       "--format=csv,noheader,nounits", "-lms", "100"],
-                                      stdout=self.f, stderr=subprocess.DEVNULL)
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+                h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+                idx = cuda_index
+                if vis and all(p.strip().isdigit() for p in vis.split(",")):
+                    idx = int(vis.split(",")[cuda_index])
+                h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+            def run():
+                while not self._stop.is_set():
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                        mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        self.samples.append((time.perf_counter(), float(mhz), int(mask)))
+                    except Exception:
+                        pass
+                    time.sleep(period_s)
+
+            self._thread = threading.Thread(target=run, daemon=True)
+            self._thread.start()
         except Exception:
-            self.p = None
+            self._start_smi(cuda_index)
+
+    def _start_smi(self, index):
+        self._f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self._smi = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=self._f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self._smi = None
+
+    def mark(self, t0, t1):
+        self.marks.append((t0, t1))
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.p is None:
-            return out
-        self.p.terminate()
-        try:
-            self.p.wait(timeout=5)
-        except Exception:
-            self.p.kill()
-        self.f.flush()
-        self.f.seek(0)
-        rows = [r.strip().split(", ") for r in self.f.read().strip().splitlines() if r.strip()]
-        self.f.close()
-        os.unlink(self.f.name)
-        sm, names = [], ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = set()
-        for r in rows[2:-1] if len(rows) > 4 else rows:  # drop the ramp-up / ramp-down samples
+        out = {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0, "sm_mhz_min": None}
+        sm, reasons = [], set()
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            lo = min((a for a, _ in self.marks), default=0.0)
+            hi = max((b for _, b in self.marks), default=float("inf"))
+            for t, mhz, mask in self.samples:
+                if lo <= t <= hi:
+                    sm.append(mhz)
+                    for name, bit in self.REASONS:
+                        if mask & bit:
+                            reasons.add(name)
+        elif self._smi is not None:
+            self._smi.terminate()
             try:
-                sm.append(float(r[0]))
-                out["sm_max_mhz"] = float(r[1])
-                for n, v in zip(names, r[3:7]):
-                    if v.strip() == "Active":
-                        reasons.add(n)
+                self._smi.wait(timeout=5)
             except Exception:
-                pass
+                self._smi.kill()
+            self._f.flush()
+            self._f.seek(0)
+            rows = [r.strip().split(", ") for r in self._f.read().strip().splitlines() if r.strip()]
+            self._f.close()
+            os.unlink(self._f.name)
+            names = [n for n, _ in self.REASONS]
+            for r in rows[1:-1] if len(rows) > 3 else rows:
+                try:
+                    sm.append(float(r[0]))
+                    out["sm_max_mhz"] = float(r[1])
+                    for n, v in zip(names, r[2:6]):
+                        if v.strip() == "Active":
+                            reasons.add(n)
+                except Exception:
+                    pass
         if sm:
             sm.sort()
             out["sm_mhz"] = sm[len(sm) // 2]
+            out["sm_mhz_min"] = sm[0]
         out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
         return out
@@ -143,22 +210,71 @@ def max_over_ranks(x, world, dev):
     return float(t.item())
 
 
-def timed_loop(fn, steps, warmup, world, dev):
-    """W warm-up steps, then exactly K steps between barriers; device time by CUDA events on the
-    launching stream; returns seconds (max over ranks)."""
+def gather_ranks(x, world, dev):
+    if world == 1:
+        return [x]
+    import torch.distributed as dist
+
+    t = torch.tensor([x], device=dev, dtype=torch.float64)
+    out = torch.empty(world, device=dev, dtype=torch.float64)
+    dist.all_gather_into_tensor(out, t)
+    return [float(v) for v in out.tolist()]
+
+
+def timed_blocks(fn, steps, warmup, world, dev, min_s=MIN_TIMED_S, sampler=None):
+    """W warm-up steps, then blocks of exactly K steps; every block sits between barrier + synchronize
+    on both sides and is timed by CUDA events on the launching stream.  Blocks repeat until `min_s`
+    seconds of device time have passed on the slowest rank.  Returns a dict: `s_per_block` is the
+    median block of the slowest rank; `per_rank_ms_per_step` lists every rank's median."""
     for i in range(warmup):
         fn(i)
-    barrier_sync(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        fn(warmup + i)
-    e1.record()
-    barrier_sync(world)
-    return max_over_ranks(e0.elapsed_time(e1) * 1e-3, world, dev)
+    blocks, spent, i0 = [], 0.0, warmup
+    while True:
+        barrier_sync(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_host0 = time.perf_counter()
+        e0.record()
+        for i in range(steps):
+            fn(i0 + i)
+        e1.record()
+        barrier_sync(world)
+        if sampler is not None:
+            sampler.mark(t_host0, time.perf_counter())
+        i0 += steps
+        dt = e0.elapsed_time(e1) * 1e-3
+        blocks.append(dt)
+        spent += max_over_ranks(dt, world, dev)   # every rank takes the same decision
+        if spent >= min_s or len(blocks) >= MAX_BLOCKS:
+            break
+    srt = sorted(blocks)
+    med = srt[len(srt) // 2]
+    per_rank = gather_ranks(med, world, dev)
+    return {"s_per_block": max(per_rank), "ms_per_step": max(per_rank) / steps * 1e3,
+            "ms_per_step_min": max_over_ranks(srt[0], world, dev) / steps * 1e3,
+            "ms_per_step_max": max_over_ranks(srt[-1], world, dev) / steps * 1e3,
+            "repeats": len(blocks), "timed_s": spent,
+            "per_rank_ms_per_step": [t / steps * 1e3 for t in per_rank]}
 
 
-def cpu_dense_baseline(budget_s=12.0):
+def graphed(fn, dev):
+    """Capture one call of `fn` in a CUDA graph (after eager warm-up on a side stream) and return a
+    function that replays it: both arms of a kernel-to-kernel comparison then run without host time."""
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize(dev)
+    return g
+
+
+def cpu_dense_baseline(budget_s=12.0, length=L, batch=B):
     """Dense SDPA decode (the reference's CPU-runnable backend) on one sequence of the workload's
     shape, fp32, all host threads; scaled to whole-batch steps/s."""
     from oracle.dense_sdpa import sdpa_decode
@@ -167,19 +283,19 @@ def cpu_dense_baseline(budget_s=12.0):
     torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(SEED)
     q = torch.randn(1, H, D, generator=g)
-    K = torch.randn(1, L, KVH, D, generator=g)
-    V = torch.randn(1, L, KVH, D, generator=g)
-    sdpa_decode(q, K, V, L)
+    K = torch.randn(1, length, KVH, D, generator=g)
+    V = torch.randn(1, length, KVH, D, generator=g)
+    sdpa_decode(q, K, V, length)
     times, t_start = [], time.perf_counter()
     while (len(times) < 5 or time.perf_counter() - t_start < budget_s) and len(times) < 200:
         t0 = time.perf_counter()
-        sdpa_decode(q, K, V, L)
+        sdpa_decode(q, K, V, length)
         times.append(time.perf_counter() - t0)
     times.sort()
     t_seq = times[len(times) // 2]
-    return {"value": 1.0 / (t_seq * B), "unit": "steps/s", "cores": cores, "kind": "port",
-            "sample": f"dense fp32 SDPA decode of 1 of the {B} sequences (L={L}), median of {len(times)} runs, "
-                      f"scaled by 1/{B} to a whole-batch step"}
+    return {"value": 1.0 / (t_seq * batch), "unit": "steps/s", "cores": cores, "kind": "port",
+            "sample": f"dense fp32 SDPA decode of 1 of the {batch} sequences (L={length}), median of {len(times)} runs, "
+                      f"scaled by 1/{batch} to a whole-batch step"}
 
 
 def reference_arm(args):
@@ -198,18 +314,26 @@ def reference_arm(args):
         "e2e": {"value": cb["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
     }
-    # Extra evidence: the reference's CUDA kernels, compiled unmodified for sm_100a, on the same inputs.
-    try:
-        from oracle import ref_gpu
-
-        if torch.cuda.is_available() and ref_gpu.available():
-            dev = torch.device("cuda", 0)
-            qpool, K, V = make_inputs(dev, SEED)
-            t = timed_loop(lambda i: ref_gpu.flash_decode(qpool[i % QPOOL], K, V, S, seed=SEED), 20, 3, 1, dev)
-            line["reference_cuda_kernels_on_b200"] = {"steps_per_s": 20 / t, "ms_per_step": t / 20 * 1e3}
-    except Exception as exc:  # noqa: BLE001
-        line["reference_cuda_kernels_on_b200"] = {"unavailable": str(exc)[:200]}
     print(json.dumps(line))
+
+
+def reference_cuda_flash(dev, qpool, K, V, steps, world):
+    """The reference's Flash kernels (compiled unmodified for sm_100a; checker infrastructure) on this
+    workload, one captured launch sequence replayed per step."""
+    from oracle import ref_gpu
+
+    if not ref_gpu.available():
+        return None
+    q = qpool[0].clone()
+    g = graphed(lambda: ref_gpu.flash_decode(q, K, V, S, seed=SEED), dev)
+
+    def step(i):
+        q.copy_(qpool[i % QPOOL])
+        g.replay()
+
+    r = timed_blocks(step, steps, 3, world, dev, min_s=0.5)
+    del g
+    return r
 
 
 def main():
@@ -222,7 +346,11 @@ def main():
     ap.add_argument("--no-prop", action="store_true", help="skip the santa_prop ragged-batch extra")
     ap.add_argument("--no-e2e-model", action="store_true",
                     help="skip the end-to-end Llama-3.1-8B-shaped decode extra (needs ~160 GB of HBM)")
+    ap.add_argument("--no-ref-kernels", action="store_true", help="skip timing the reference's CUDA kernels")
+    ap.add_argument("--no-b32", action="store_true", help="skip the B=32 variant of the headline workload")
     ap.add_argument("--e2e-model-batch", type=int, default=32)
+    ap.add_argument("--e2e-prefill", action="store_true",
+                    help="run the real 512-token-chunk prefill of the end-to-end extra instead of a synthetic cache")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -237,6 +365,7 @@ def main():
     rank, local, world = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
     steps, warmup = args.steps, max(3, args.warmup)
+    sampler = ClockSampler(local)      # sampling starts before the warm-up
     qpool, K, V = make_inputs(dev, SEED + rank)
 
     # algorithmic bytes of one step: every valid K row once per kv-head + the distinct sampled V rows
@@ -246,9 +375,9 @@ def main():
     alg_bytes = B * L * KVH * D * 2 + vrows_total * D * 2 + 2 * B * H * D * 2 + B * H * 4
 
     # ---- kernel-resident measurement (C ABI, inputs in HBM) -----------------------------------
-    sampler = ClockSampler(local)
-    t_dev = timed_loop(lambda i: ops.flash_decode(qpool[i % QPOOL], K, V, S, seed=SEED, batch_offset=rank * B),
-                       steps, warmup, world, dev)
+    out_dev = torch.empty(B, H, D, device=dev, dtype=torch.bfloat16)
+    tm = timed_blocks(lambda i: ops.flash_decode(qpool[i % QPOOL], K, V, S, seed=SEED, batch_offset=rank * B,
+                                                 out=out_dev), steps, warmup, world, dev, sampler=sampler)
     clocks = sampler.stop()
     status = ops.workspace_status("flash", dev)
 
@@ -277,7 +406,7 @@ def main():
             out = flash_mod.decode_systematic_batched(q_dev, K, V, S, seed=SEED, want_vrows=False, valid_len=L)[0]
             out_host.copy_(out, non_blocking=True)
 
-    # The whole step (copies in, KV append, decode, copy out) is captured once into a CUDA graph, as a
+    # The whole step (copies in, KV append, decode, result out) is captured once into a CUDA graph, as a
     # serving loop would do, and replayed per step; the step's q is first written into the pinned staging
     # buffer by the host.  If capture is not possible the step runs eagerly.
     q_stage.copy_(q_host[0])
@@ -294,17 +423,8 @@ def main():
     assert torch.equal(module_out, out_host), "direct-to-host output differs from the module's output"
     graph = None
     try:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                e2e_body()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            e2e_body()
-        eager_out = out_host.clone()  # from the eager warm-up calls above (same q, same seed)
+        graph = graphed(e2e_body, dev)
+        eager_out = out_host.clone()  # from the calls above (same q, same seed)
         out_host.zero_()
         graph.replay()
         torch.cuda.synchronize()
@@ -324,180 +444,109 @@ def main():
             e2e_body()
         torch.cuda.current_stream().synchronize()  # the caller consumes the result every step
 
-    e2e_steps = max(20, steps // 4)
-    t_e2e = timed_loop(e2e_step, e2e_steps, 3, world, dev)
+    te = timed_blocks(e2e_step, steps, 3, world, dev, min_s=0.5)
     h2d = stage_host.numel() * 2
     d2h = out_host.numel() * 2
 
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
-        ms_step = t_dev / steps * 1e3
-        ach = alg_bytes / (t_dev / steps) / 1e9
+        s_step = tm["s_per_block"] / steps
+        ach = alg_bytes / s_step / 1e9
         line = {
-            "metric": "decode_attn_steps_per_sec", "value": world * steps / t_dev, "unit": "steps/s",
-            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+            "metric": "decode_attn_steps_per_sec", "value": world / s_step, "unit": "steps/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": tm["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": B, "parallelism": f"batch-sharded x{world}, no collective",
                        "l2": "inputs (1 GiB of K+V per GPU) exceed the 126 MB L2", "q": f"pool of {QPOOL} cycled"},
+            "timing": {"what": f"median of {tm['repeats']} blocks of {steps} steps (max over ranks of the rank medians)",
+                       "ms_per_step_min": tm["ms_per_step_min"], "ms_per_step_max": tm["ms_per_step_max"],
+                       "repeats": tm["repeats"], "timed_s": tm["timed_s"],
+                       "per_rank_ms_per_step": tm["per_rank_ms_per_step"]},
             "sampled_kv_gbs_per_gpu": ach, "sampled_kv_gbs_total": ach * world,
             "pct_of_measured_hbm_peak": 100.0 * ach / peak, "pct_of_8tbs": 100.0 * ach / 8000.0,
             "algorithmic_bytes_per_step": alg_bytes, "vrows_total": vrows_total,
-            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": {"value": world * e2e_steps / t_e2e, "unit": "steps/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": t_e2e / e2e_steps * 1e3,
-                    "mode": e2e_note},
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
+                       "samples": clocks["samples"], "sm_mhz_min": clocks["sm_mhz_min"],
+                       "ms_per_step_x_sm_ghz": (tm["ms_per_step"] * clocks["sm_mhz"] / 1e3) if clocks["sm_mhz"] else None},
+            "e2e": {"value": world * steps / te["s_per_block"], "unit": "steps/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": te["ms_per_step"],
+                    "repeats": te["repeats"], "mode": e2e_note},
             "gpu_launches": 2 * steps,
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
-                         "kernel": "stream_kernel<bf16,256,flash> (+ flash_merge_kernel, <2% of the step)"},
+                         "kernel": "stream_kernel<bf16,256,flash> (+ flash_merge_kernel, a few percent of the step)"},
             "device_status_word": status,
         }
 
-    # ---- extra: one 512k-token sequence, KV sharded along the sequence over the N GPUs -----------
-    if not args.no_seq_sharded:
-        L3, S3 = 524288, 1024
+    # ---- the reference's own CUDA kernels on the same inputs, same process ----------------------
+    if not args.no_ref_kernels:
+        rr = None
+        try:
+            rr = reference_cuda_flash(dev, qpool, K, V, steps, world)
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                line["vs_reference_cuda_kernels"] = {"flash": {"unavailable": str(exc)[:200]}}
+        if rank == 0 and rr is not None:
+            line["vs_reference_cuda_kernels"] = {"flash": {
+                "what": "reference Flash kernels compiled unmodified for sm_100a, launch sequence replayed from a "
+                        "CUDA graph, same inputs / steps / timing blocks",
+                "reference_ms_per_step": rr["ms_per_step"], "ours_ms_per_step": tm["ms_per_step"],
+                "speedup": rr["ms_per_step"] / tm["ms_per_step"], "repeats": rr["repeats"]}}
+        elif rank == 0 and "vs_reference_cuda_kernels" not in line:
+            line["vs_reference_cuda_kernels"] = {"flash": {"unavailable": "oracle/_ref is not built"}}
+
+    # ---- extra: the same workload at B=32 (the fixed per-call cost amortised over 4x the tiles) --
+    if not args.no_b32:
         del K, V, qpool
         torch.cuda.empty_cache()
-        bn, T_c, spt, plan = sharded.shard_plan(L3, world, S3)
-        row0, row1, _ = plan[rank]
-        # every rank draws the same full-length stream and keeps its rows (same data at every N)
-        qp3, K3, V3 = make_inputs(dev, SEED + 3, batch=1, length=L3)
-        K3, V3 = K3[:, row0:row1].contiguous(), V3[:, row0:row1].contiguous()
-        gbuf = torch.empty(world, 1, H, 130, device=dev, dtype=torch.float32)
-        n3 = max(20, steps // 5)
-        t3 = timed_loop(lambda i: sharded.seq_sharded_flash_decode(qp3[i % QPOOL], K3, V3, S3, SEED, L3,
-                                                                    gather_buf=gbuf), n3, 5, world, dev)
-        # the same step with the partials exchanged through peer-mapped memory instead of the all-gather
-        t3x, x_note, ex = None, None, None
-        try:
-            if world > 1:
-                import importlib
-                importlib.import_module("torch.distributed._symmetric_memory")
-        except Exception as exc:  # noqa: BLE001
-            x_note = f"peer exchange unavailable: {str(exc)[:120]}"
-        if max_over_ranks(1.0 if x_note else 0.0, world, dev) != 0.0:
-            x_note = x_note or "peer exchange unavailable on another rank"
-        try:
-            if x_note:
-                raise RuntimeError(x_note)
-            ex = sharded.PeerExchange(1, H, dev)
-            ref3 = sharded.seq_sharded_flash_decode(qp3[0], K3, V3, S3, SEED, L3, gather_buf=gbuf)[0]
-            got3 = sharded.seq_sharded_flash_decode(qp3[0], K3, V3, S3, SEED, L3, exchange=ex)[0]
-            ex.check()
-            if not torch.equal(ref3, got3):
-                raise RuntimeError("peer exchange result differs from the all-gather result")
-        except Exception as exc:  # noqa: BLE001  (symmetric memory may be unavailable on a box)
-            x_note = x_note or f"peer exchange unavailable: {str(exc)[:120]}"
-        # every rank must agree before entering a timed loop with barriers
-        if max_over_ranks(1.0 if x_note else 0.0, world, dev) == 0.0:
-            t3x = timed_loop(lambda i: sharded.seq_sharded_flash_decode(qp3[i % QPOOL], K3, V3, S3, SEED, L3,
-                                                                         exchange=ex), n3, 5, world, dev)
-            ex.check()
-        elif x_note is None:
-            x_note = "peer exchange unavailable on another rank"
-        # ... and with the two calls of a step captured once in a CUDA graph (device-counted epochs)
-        t3g = None
-        if t3x is not None:
-            exg = sharded.PeerExchange(1, H, dev, device_counted=True)
-            q3 = qp3[0].clone()
-            side3 = torch.cuda.Stream()
-            side3.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side3):
-                for _ in range(2):
-                    sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
-            torch.cuda.current_stream().wait_stream(side3)
-            torch.cuda.synchronize()
-            graph3 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph3, stream=side3):
-                out3 = sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
-            graph3.replay()
-            exg.check()
-            same = torch.equal(out3[0], got3)
-            if max_over_ranks(0.0 if same else 1.0, world, dev) == 0.0:
-                def graph_step(i):
-                    q3.copy_(qp3[i % QPOOL])
-                    graph3.replay()
-
-                t3g = timed_loop(graph_step, n3, 5, world, dev)
-                exg.check()
-            del graph3
+        qp32, K32, V32 = make_inputs(dev, SEED + 32 + rank, batch=32)
+        vr32 = int(ops.flash_decode(qp32[0], K32, V32, S, seed=SEED, want_vrows=True)[2].sum().item())
+        o32 = torch.empty(32, H, D, device=dev, dtype=torch.bfloat16)
+        t32 = timed_blocks(lambda i: ops.flash_decode(qp32[i % QPOOL], K32, V32, S, seed=SEED, out=o32),
+                           max(5, steps // 4), 3, world, dev, min_s=0.5)
         if rank == 0:
-            kb = L3 * KVH * D * 2
-            line["seq_sharded_512k"] = {
-                "workload": f"santa_flash B=1 L={L3} S={S3}, KV sharded over {world} GPU(s), all-gather of "
-                            "(partial, m, Z) + local combine inside the timed step",
-                "steps_per_s": n3 / t3, "ms_per_step": t3 / n3 * 1e3, "k_gbs_total": kb / (t3 / n3) / 1e9,
-                "scaling": "strong",
-                "peer_exchange": ({"what": "partials stored into every rank's peer-mapped buffer by the merge kernel, "
-                                           "bounded wait + combine kernel; no collective call",
-                                   "steps_per_s": n3 / t3x, "ms_per_step": t3x / n3 * 1e3,
-                                   "k_gbs_total": kb / (t3x / n3) / 1e9,
-                                   "ms_per_step_graph_replay": (t3g / n3 * 1e3) if t3g else None} if t3x else x_note)}
+            b32 = 32 * L * KVH * D * 2 + vr32 * D * 2 + 2 * 32 * H * D * 2 + 32 * H * 4
+            peak, _ = measured_peak_gbs()
+            line["flash_b32"] = {"workload": WORKLOAD.replace(f"B={B} ", "B=32 "), "ms_per_step": t32["ms_per_step"],
+                                 "sampled_kv_gbs_per_gpu": b32 / (t32["ms_per_step"] * 1e-3) / 1e9,
+                                 "frac_of_measured_hbm_peak": b32 / (t32["ms_per_step"] * 1e-3) / 1e9 / peak,
+                                 "repeats": t32["repeats"]}
+        del K32, V32, qp32
+        torch.cuda.empty_cache()
+    else:
+        del K, V, qpool
+        torch.cuda.empty_cache()
 
-    # ---- extra: santa_prop on the ragged batch (BASELINE configs[2]), scalar entry point per sequence -----
+    # ---- extra: one 512k-token sequence, KV sharded along the sequence over the N GPUs -----------
+    if not args.no_seq_sharded:
+        res3 = seq_sharded_extra(dev, rank, world, steps, sharded, ops)
+        if rank == 0:
+            line["seq_sharded_512k"] = res3
+
+    # ---- extra: santa_prop on the ragged batch, scalar entry point per sequence and one ragged call
     if not args.no_prop:
-        import santa_prop_batch_cuda as prop_mod
-
-        lengths = torch.randint(8192, 65537, (16,), generator=torch.Generator().manual_seed(7)).tolist()
-        qp2, K2, V2 = make_inputs(dev, SEED + 2 + rank, batch=1, length=sum(lengths))
-        offs = [0]
-        for n in lengths:
-            offs.append(offs[-1] + n)
-        Ks = [K2[0, offs[i]:offs[i + 1]] for i in range(16)]   # contiguous [L_b, KVH, D] views, as the adapter passes
-        Vs = [V2[0, offs[i]:offs[i + 1]] for i in range(16)]
-        vr2 = sum(int(prop_mod.decode_systematic_scalar(qp2[0][0], Ks[i], Vs[i], S, seed=SEED, want_vrows=True)[2]
-                      .sum().item()) for i in range(16))
-
-        def prop_step(i):
-            q = qp2[i % QPOOL][0]
-            for b in range(16):
-                prop_mod.decode_systematic_scalar(q, Ks[b], Vs[b], S, seed=SEED, want_vrows=False)
-
-        n2 = max(20, steps // 10)
-        t2 = timed_loop(prop_step, n2, 3, world, dev)
-        # the same 16 sequences as one padded cache [16, 65536, KVH, D] and ONE ragged call per step
-        Lmax = 65536
-        Kr = torch.zeros(16, Lmax, KVH, D, device=dev, dtype=torch.bfloat16)
-        Vr = torch.zeros(16, Lmax, KVH, D, device=dev, dtype=torch.bfloat16)
-        for b in range(16):
-            Kr[b, :lengths[b]].copy_(Ks[b])
-            Vr[b, :lengths[b]].copy_(Vs[b])
-        del K2, V2, Ks, Vs
-        torch.cuda.empty_cache()
-        lens_dev = torch.tensor(lengths, dtype=torch.int32, device=dev)
-        qr = [qp2[i][0].unsqueeze(0).expand(16, H, D).contiguous() for i in range(QPOOL)]
-        vr3 = int(prop_mod.decode_systematic_ragged(qr[0], Kr, Vr, lens_dev, S, seed=SEED, want_vrows=True)[2]
-                  .sum().item())
-        t2r = timed_loop(lambda i: prop_mod.decode_systematic_ragged(qr[i % QPOOL], Kr, Vr, lens_dev, S, seed=SEED),
-                         n2, 3, world, dev)
+        res2 = prop_extra(dev, rank, world, steps, args)
         if rank == 0:
-            fixed = 16 * (2 * H * D * 2 + H * 4)
-            pb = sum(lengths) * KVH * D * 2 + vr2 * D * 2 + fixed
-            pbr = sum(lengths) * KVH * D * 2 + vr3 * D * 2 + fixed
-            line["prop_ragged_config2"] = {
-                "workload": "santa_prop B=16 ragged L in [8192,65536] (seed-7 draw, sum 562962) S=256",
-                "ragged_call": {
-                    "what": "one decode_systematic_ragged call per step (4 kernels), lengths in device memory",
-                    "steps_per_s": world * n2 / t2r, "ms_per_step": t2r / n2 * 1e3,
-                    "sampled_kv_gbs_per_gpu": pbr / (t2r / n2) / 1e9, "algorithmic_bytes_per_step": pbr},
-                "per_sequence_loop": {
-                    "what": "16 decode_systematic_scalar calls per step (the reference adapter's loop, 4 kernels each)",
-                    "steps_per_s": world * n2 / t2, "ms_per_step": t2 / n2 * 1e3,
-                    "sampled_kv_gbs_per_gpu": pb / (t2 / n2) / 1e9, "algorithmic_bytes_per_step": pb},
-                "scaling": "weak"}
-        del qp2, Kr, Vr, qr
-        torch.cuda.empty_cache()
+            line["prop_ragged_config2"] = res2
+            if "reference" in res2:
+                line.setdefault("vs_reference_cuda_kernels", {})["prop"] = res2.pop("reference")
 
-    # ---- extra: end-to-end decode of a Llama-3.1-8B-shaped model (BASELINE configs[4]) -----------------
+    # ---- extra: end-to-end decode of a Llama-3.1-8B-shaped model -----------------------------------
     if not args.no_e2e_model:
-        res4 = e2e_model_decode(dev, args.e2e_model_batch, world)
+        res4 = e2e_model_decode(dev, args.e2e_model_batch, world, prefill=args.e2e_prefill)
         if rank == 0:
             line["e2e_llama8b_decode"] = res4
 
     if rank == 0:
-        line["cpu_baseline"] = cpu_dense_baseline() if world == 1 else None
+        if world == 1:
+            line["cpu_baseline"] = cpu_dense_baseline()
+            c0 = cpu_dense_baseline(budget_s=3.0, length=4096, batch=1)
+            c0["sample"] = "dense fp32 SDPA decode, B=1 Hq=32 Hkv=8 D=128 L=4096 (the reference's CPU-runnable case)"
+            line["cpu_baseline_b1_l4096"] = c0
+        else:
+            line["cpu_baseline"] = None
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
@@ -506,25 +555,231 @@ def main():
         dist.destroy_process_group()
 
 
-def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128):
+def seq_sharded_extra(dev, rank, world, steps, sharded, ops):
+    """B=1, L=524288, S=1024 (Flash rule), the KV cache split along the sequence over the ranks; the
+    step includes the exchange of the per-head partials and the combine.  Strong scaling."""
+    L3, S3 = 524288, 1024
+    bn, T_c, spt, plan = sharded.shard_plan(L3, world, S3)
+    row0, row1, _ = plan[rank]
+    # every rank draws the same full-length stream and keeps its rows (same data at every N)
+    qp3, K3f, V3f = make_inputs(dev, SEED + 3, batch=1, length=L3)
+    # the unsharded result, computed by every rank on the whole sequence before it keeps its shard
+    whole = [ops.flash_decode(qp3[i], K3f, V3f, S3, seed=SEED)[0].clone() for i in range(2)]
+    K3, V3 = K3f[:, row0:row1].contiguous(), V3f[:, row0:row1].contiguous()
+    del K3f, V3f
+    torch.cuda.empty_cache()
+    gbuf = torch.empty(world, 1, H, 130, device=dev, dtype=torch.float32)
+    n3 = max(20, steps // 5)
+    checks = {}
+    for i in range(2):
+        got = sharded.seq_sharded_flash_decode(qp3[i], K3, V3, S3, SEED, L3, gather_buf=gbuf)[0]
+        err = (got.float() - whole[i].float()).abs().max().item()
+        checks[f"allgather_vs_unsharded_maxabs_q{i}"] = max_over_ranks(err, world, dev)
+    t3 = timed_blocks(lambda i: sharded.seq_sharded_flash_decode(qp3[i % QPOOL], K3, V3, S3, SEED, L3, gather_buf=gbuf),
+                      n3, 5, world, dev, min_s=0.3)
+    # the same step with the partials exchanged through peer-mapped memory instead of the all-gather
+    t3x, x_note, ex, t3g = None, None, None, None
+    try:
+        if world > 1:
+            import importlib
+            importlib.import_module("torch.distributed._symmetric_memory")
+    except Exception as exc:  # noqa: BLE001
+        x_note = f"peer exchange unavailable: {str(exc)[:120]}"
+    if max_over_ranks(1.0 if x_note else 0.0, world, dev) != 0.0:
+        x_note = x_note or "peer exchange unavailable on another rank"
+    try:
+        if x_note:
+            raise RuntimeError(x_note)
+        ex = sharded.PeerExchange(1, H, dev)
+        for i in range(2):
+            got3 = sharded.seq_sharded_flash_decode(qp3[i], K3, V3, S3, SEED, L3, exchange=ex)[0]
+            ex.check()
+            err = (got3.float() - whole[i].float()).abs().max().item()
+            checks[f"peer_vs_unsharded_maxabs_q{i}"] = err
+            if err > 2e-2:
+                raise RuntimeError(f"peer exchange result differs from the unsharded result by {err}")
+    except Exception as exc:  # noqa: BLE001  (symmetric memory may be unavailable on a box)
+        x_note = x_note or f"peer exchange unavailable: {str(exc)[:120]}"
+    # every rank must agree before entering a timed loop with barriers
+    if max_over_ranks(1.0 if x_note else 0.0, world, dev) == 0.0:
+        t3x = timed_blocks(lambda i: sharded.seq_sharded_flash_decode(qp3[i % QPOOL], K3, V3, S3, SEED, L3, exchange=ex),
+                           n3, 5, world, dev, min_s=0.3)
+        ex.check()
+    elif x_note is None:
+        x_note = "peer exchange unavailable on another rank"
+    # ... and with the calls of a step captured once in a CUDA graph (device-counted epochs)
+    if t3x is not None:
+        exg = sharded.PeerExchange(1, H, dev, device_counted=True)
+        q3 = qp3[0].clone()
+        side3 = torch.cuda.Stream()
+        side3.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side3):
+            for _ in range(2):
+                sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
+        torch.cuda.current_stream().wait_stream(side3)
+        torch.cuda.synchronize()
+        graph3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph3, stream=side3):
+            out3 = sharded.seq_sharded_flash_decode(q3, K3, V3, S3, SEED, L3, exchange=exg)
+        graph3.replay()
+        exg.check()
+        same = (out3[0].float() - whole[0].float()).abs().max().item() <= 2e-2
+        if max_over_ranks(0.0 if same else 1.0, world, dev) == 0.0:
+            def graph_step(i):
+                q3.copy_(qp3[i % QPOOL])
+                graph3.replay()
+
+            t3g = timed_blocks(graph_step, n3, 5, world, dev, min_s=0.3)
+            exg.check()
+        del graph3
+    res = None
+    if rank == 0:
+        kb = L3 * KVH * D * 2
+        res = {
+            "workload": f"santa_flash B=1 L={L3} S={S3}, KV sharded over {world} GPU(s); the step includes the "
+                        "exchange of (partial, m, Z) and the combine",
+            "scaling": "strong", "checks": checks,
+            "allgather": {"what": "NCCL all-gather of [1,32,130] fp32 per rank + local combine",
+                          "ms_per_step": t3["ms_per_step"], "k_gbs_total": kb / (t3["ms_per_step"] * 1e-3) / 1e9,
+                          "per_rank_ms_per_step": t3["per_rank_ms_per_step"]},
+            "peer_exchange": ({"what": "partials stored into every rank's peer-mapped buffer by the merge kernel, "
+                                       "bounded wait + combine kernel; no collective call",
+                               "ms_per_step": t3x["ms_per_step"], "k_gbs_total": kb / (t3x["ms_per_step"] * 1e-3) / 1e9,
+                               "per_rank_ms_per_step": t3x["per_rank_ms_per_step"],
+                               "ms_per_step_graph_replay": t3g["ms_per_step"] if t3g else None} if t3x else x_note),
+            "ms_per_step": min(t3["ms_per_step"], t3x["ms_per_step"]) if t3x else t3["ms_per_step"]}
+    del K3, V3, qp3
+    torch.cuda.empty_cache()
+    return res
+
+
+def prop_extra(dev, rank, world, steps, args):
+    """santa_prop on 16 ragged sequences, S=256: the adapter's loop of 16 scalar calls, one ragged call,
+    and -- for a kernel-to-kernel comparison -- the reference's own Prop kernels in the same loop."""
+    import santa_prop_batch_cuda as prop_mod
+
+    lengths = torch.randint(8192, 65537, (16,), generator=torch.Generator().manual_seed(7)).tolist()
+    qp2, K2, V2 = make_inputs(dev, SEED + 2 + rank, batch=1, length=sum(lengths))
+    offs = [0]
+    for n in lengths:
+        offs.append(offs[-1] + n)
+    Ks = [K2[0, offs[i]:offs[i + 1]] for i in range(16)]   # contiguous [L_b, KVH, D] views, as the adapter passes
+    Vs = [V2[0, offs[i]:offs[i + 1]] for i in range(16)]
+    vr2 = sum(int(prop_mod.decode_systematic_scalar(qp2[0][0], Ks[i], Vs[i], S, seed=SEED, want_vrows=True)[2]
+                  .sum().item()) for i in range(16))
+
+    def prop_step(i):
+        q = qp2[i % QPOOL][0]
+        for b in range(16):
+            prop_mod.decode_systematic_scalar(q, Ks[b], Vs[b], S, seed=SEED, want_vrows=False)
+
+    n2 = max(20, steps // 10)
+    t2 = timed_blocks(prop_step, n2, 3, world, dev, min_s=0.4)
+    # the same loop replayed from a CUDA graph, and the reference's own kernels likewise
+    ref_res = None
+    try:
+        qg = qp2[0][0].clone()
+        g_ours = graphed(lambda: [prop_mod.decode_systematic_scalar(qg, Ks[b], Vs[b], S, seed=SEED) for b in range(16)],
+                         dev)
+
+        def ours_graph_step(i):
+            qg.copy_(qp2[i % QPOOL][0])
+            g_ours.replay()
+
+        t2g = timed_blocks(ours_graph_step, n2, 3, world, dev, min_s=0.4)
+        del g_ours
+        if not args.no_ref_kernels:
+            from oracle import ref_gpu
+
+            if ref_gpu.available():
+                g_ref = graphed(lambda: [ref_gpu.prop_decode(qg, Ks[b], Vs[b], S, seed=SEED) for b in range(16)], dev)
+
+                def ref_graph_step(i):
+                    qg.copy_(qp2[i % QPOOL][0])
+                    g_ref.replay()
+
+                tr = timed_blocks(ref_graph_step, n2, 3, world, dev, min_s=0.4)
+                del g_ref
+                ref_res = {"what": "reference Prop kernels compiled unmodified for sm_100a, the adapter's loop of 16 "
+                                   "per-sequence launch sequences replayed from a CUDA graph; ours likewise",
+                           "reference_ms_per_step": tr["ms_per_step"], "ours_loop_ms_per_step": t2g["ms_per_step"]}
+    except Exception as exc:  # noqa: BLE001
+        ref_res = {"unavailable": str(exc)[:200]}
+        t2g = None
+    # the same 16 sequences as one padded cache [16, 65536, KVH, D] and ONE ragged call per step
+    Lmax = 65536
+    Kr = torch.zeros(16, Lmax, KVH, D, device=dev, dtype=torch.bfloat16)
+    Vr = torch.zeros(16, Lmax, KVH, D, device=dev, dtype=torch.bfloat16)
+    for b in range(16):
+        Kr[b, :lengths[b]].copy_(Ks[b])
+        Vr[b, :lengths[b]].copy_(Vs[b])
+    del K2, V2, Ks, Vs
+    torch.cuda.empty_cache()
+    lens_dev = torch.tensor(lengths, dtype=torch.int32, device=dev)
+    qr = [qp2[i][0].unsqueeze(0).expand(16, H, D).contiguous() for i in range(QPOOL)]
+    vr3 = int(prop_mod.decode_systematic_ragged(qr[0], Kr, Vr, lens_dev, S, seed=SEED, want_vrows=True)[2]
+              .sum().item())
+    t2r = timed_blocks(lambda i: prop_mod.decode_systematic_ragged(qr[i % QPOOL], Kr, Vr, lens_dev, S, seed=SEED),
+                       n2, 3, world, dev, min_s=0.4)
+    res = None
+    if rank == 0:
+        fixed = 16 * (2 * H * D * 2 + H * 4)
+        pb = sum(lengths) * KVH * D * 2 + vr2 * D * 2 + fixed
+        pbr = sum(lengths) * KVH * D * 2 + vr3 * D * 2 + fixed
+        res = {
+            "workload": PROP_WORKLOAD,
+            "ragged_call": {
+                "what": "one decode_systematic_ragged call per step (4 kernels), lengths in device memory",
+                "steps_per_s": world / (t2r["ms_per_step"] * 1e-3), "ms_per_step": t2r["ms_per_step"],
+                "sampled_kv_gbs_per_gpu": pbr / (t2r["ms_per_step"] * 1e-3) / 1e9, "algorithmic_bytes_per_step": pbr,
+                "repeats": t2r["repeats"]},
+            "per_sequence_loop": {
+                "what": "16 decode_systematic_scalar calls per step (the reference adapter's loop, 4 kernels each)",
+                "steps_per_s": world / (t2["ms_per_step"] * 1e-3), "ms_per_step": t2["ms_per_step"],
+                "ms_per_step_graph_replay": t2g["ms_per_step"] if t2g else None,
+                "sampled_kv_gbs_per_gpu": pb / (t2["ms_per_step"] * 1e-3) / 1e9, "algorithmic_bytes_per_step": pb},
+            "scaling": "weak"}
+        if ref_res is not None:
+            if "reference_ms_per_step" in ref_res:
+                ref_res["ours_ragged_ms_per_step"] = t2r["ms_per_step"]
+                ref_res["speedup_loop_vs_loop"] = ref_res["reference_ms_per_step"] / ref_res["ours_loop_ms_per_step"]
+                ref_res["speedup_ragged_vs_reference_loop"] = ref_res["reference_ms_per_step"] / t2r["ms_per_step"]
+            res["reference"] = ref_res
+    del qp2, Kr, Vr, qr
+    torch.cuda.empty_cache()
+    return res
+
+
+def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefill=False):
     """Random-init (seed 0) Llama-3.1-8B-shaped decoder, `batch` sequences with `prompt_len` cached tokens
-    each, `new_tokens` greedy tokens with santa_flash S=256; one replica per GPU.  The caches are filled
-    with seeded N(0,1) values instead of running the prefill (random weights: the prefill would produce
-    values of no more meaning, and only the decode phase is the metric).  Returns per-replica numbers;
-    the whole-job token rate is world x the replica's."""
+    each, `new_tokens` greedy tokens with santa_flash S=256; one replica per GPU.  By default the caches
+    are filled with seeded N(0,1) values instead of running the prefill (random weights: the prefill
+    would produce values of no more meaning, and only the decode phase is the metric); `prefill=True`
+    runs the real 512-token-chunk prefill of uniform-random token ids first.  Returns per-replica
+    numbers; the whole-job token rate is world x the replica's."""
     import torch.distributed as dist
     from santa_b200.runtime import DecodeRuntime, LlamaShape
 
     torch.cuda.empty_cache()
     out = {"workload": f"Llama-3.1-8B shape, random init seed 0, B={batch} x {prompt_len} cached tokens, "
                        f"{new_tokens} greedy tokens, santa_flash S={S}, CUDA-graph step, 1 replica per GPU",
-           "cache": "synthetic N(0,1) fill (no prefill run)"}
+           "cache": "real chunked prefill (512-token chunks)" if prefill else "synthetic N(0,1) fill (no prefill run)"}
     try:
         rt = DecodeRuntime(LlamaShape(), batch, prompt_len + new_tokens, dev, attention="santa_flash", S=S,
                            attn_seed=SEED, weight_seed=0)
-        rt.fill_cache_synthetic(prompt_len, seed=SEED + 4)
-        first = torch.zeros(batch, rt.shape.vocab, device=dev)
-        first[:, 1] = 1.0
+        if prefill:
+            ids = torch.randint(0, rt.shape.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(11))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            first = rt.prefill(ids.to(dev), chunk=512)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            out["prefill_s"] = e0.elapsed_time(e1) * 1e-3
+            out["prefill_tokens_per_s"] = batch * prompt_len / out["prefill_s"]
+        else:
+            rt.fill_cache_synthetic(prompt_len, seed=SEED + 4)
+            first = torch.zeros(batch, rt.shape.vocab, device=dev)
+            first[:, 1] = 1.0
         rt.capture(prompt_len + new_tokens)
         rt.generate(first, prompt_len, 4)                           # warm-up replays
         if world > 1:
@@ -566,8 +821,8 @@ def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128):
     return out
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from
-# the ncu capture summarised in profiles/stream_kernel_flash_config1.md (557.92 MB + 7.83 MB).
+# dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from one
+# ncu capture of that kernel (read 557.92 MB + write 7.83 MB).
 TRAFFIC_BYTES_PER_LAUNCH = 565_754_112
 
 if __name__ == "__main__":

@@ -8,7 +8,14 @@ Differences, all in the direction of fewer launches:
   * ``SantaPropBackend`` decodes the whole batch with one ragged call
     (``santa_prop_batch_cuda.decode_systematic_ragged``, ``actual_mode == "batch_ragged"``) where the
     reference loops over the sequences (``"single_loop_fallback"``, :491-500); every sequence still uses
-    the head index ``h`` in the random stream, as in that loop.  ``loop=True`` reproduces the loop.
+    the head index ``h`` in the random stream, as in that loop.  The ragged call always works on
+    256-row tiles, so it is only taken when the reference's tile-size rule
+    (santa_fused_proportional_tile_budgets/santa_cuda.cpp:61-77) gives 256 for the call: an integer
+    ``valid_len`` above 3072 with no explicit ``block_n``, or ``block_n == 256``.  Shorter contexts
+    and other tile sizes go through the per-sequence loop and sample exactly what the reference
+    adapter samples.  ``loop=True`` forces the loop.  With per-sequence lengths on the device (see
+    below) the host cannot apply the rule: the ragged call is used and sequences of at most 3072
+    tokens are sampled on 256-row tiles instead of the rule's 32 / 64 rows.
   * ``valid_len`` may be an int (the reference's contract) or an int32 device tensor ``[B]`` of
     per-sequence lengths; the tensor form never touches the host and is what a captured CUDA graph needs.
 """
@@ -118,7 +125,12 @@ class SantaPropBackend(_SantaBackend):
 
     def decode(self, q_bhd, k_nhd, v_nhd, valid_len):
         B = int(q_bhd.shape[0])
-        ragged_ok = self.block_n in (None, 0, 256) and not self.loop
+        if isinstance(valid_len, torch.Tensor):
+            ragged_ok = self.block_n in (None, 0, 256) and not self.loop
+        else:  # the ragged call's 256-row tiles must be what the reference's rule picks for this length
+            from . import capi
+            bn = capi.block_n_rule(int(valid_len), 0 if self.block_n is None else self.block_n)
+            ragged_ok = bn == 256 and not self.loop
         if ragged_ok:
             self.actual_mode = "batch_ragged"
             lens = self._lengths(valid_len, B, q_bhd.device)
@@ -126,10 +138,10 @@ class SantaPropBackend(_SantaBackend):
                                                         want_vrows=False)[0]
         # the reference adapter's per-sequence loop over contiguous prefixes
         self.actual_mode = "single_loop_fallback"
-        L = int(valid_len)
+        lens = [int(n) for n in valid_len.tolist()] if isinstance(valid_len, torch.Tensor) else [int(valid_len)] * B
         kw = {} if self.block_n is None else {"block_n": self.block_n}
-        outs = [self.module.decode_systematic_scalar(q_bhd[b].contiguous(), k_nhd[b, :L].contiguous(),
-                                                     v_nhd[b, :L].contiguous(), self.S, seed=self.seed,
+        outs = [self.module.decode_systematic_scalar(q_bhd[b].contiguous(), k_nhd[b, :lens[b]].contiguous(),
+                                                     v_nhd[b, :lens[b]].contiguous(), self.S, seed=self.seed,
                                                      want_vrows=False, **kw)[0] for b in range(B)]
         return torch.stack(outs, dim=0).contiguous()
 

@@ -138,9 +138,11 @@ class DecodeRuntime:
 
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()
-    def prefill(self, input_ids: torch.Tensor, chunk: int = 512) -> torch.Tensor:
+    def prefill(self, input_ids: torch.Tensor, chunk: int = 512, seqs_per_pass: int = 4) -> torch.Tensor:
         """Chunked dense prefill of ``input_ids [B,L]``; K (rotated) and V of every chunk go straight
-        into the caches.  Returns the last position's logits ``[B,V]`` (fp32)."""
+        into the caches.  ``seqs_per_pass`` sequences are run at a time, so that the dense attention
+        of a chunk against a long prefix stays a few GB whatever the batch size.  Returns the last
+        position's logits ``[B,V]`` (fp32)."""
         if chunk <= 0:
             raise ValueError(f"prefill_chunk_size must be > 0, got {chunk}")
         s, B = self.shape, self.B
@@ -148,35 +150,39 @@ class DecodeRuntime:
         if input_ids.shape[0] != B or L > self.T:
             raise RuntimeError("prompt does not fit the runtime's batch / cache length")
         H, KVH, D = s.heads, s.kv_heads, s.head_dim
-        last = None
-        for start in range(0, L, chunk):
-            end = min(L, start + chunk)
-            n = end - start
-            x = self.embed[input_ids[:, start:end].to(self.dev)]                       # [B,n,hidden]
-            positions = torch.arange(start, end, device=self.dev)
-            cos, sin = self._tables(positions)                                          # [n,D]
-            cos, sin = cos[None, :, None, :], sin[None, :, None, :]
-            mask = None
-            if start > 0:  # keys [0,end) against queries [start,end): causal inside the chunk only
-                kidx = torch.arange(end, device=self.dev)[None, :]
-                mask = kidx <= positions[:, None]
-            for li, lw in enumerate(self.layers):
-                h = self._norm(x, lw["norm1"])
-                qkv = F.linear(h, lw["wqkv"]).view(B, n, H + 2 * KVH, D)
-                q, k, v = qkv[:, :, :H], qkv[:, :, H:H + KVH], qkv[:, :, H + KVH:]
-                q = _rope_seq(q, cos, sin)
-                k = _rope_seq(k, cos, sin)
-                self.k_cache[li][:, start:end].copy_(k)
-                self.v_cache[li][:, start:end].copy_(v)
-                kk = self.k_cache[li][:, :end].permute(0, 2, 1, 3)                     # [B,KVH,end,D] view
-                vv = self.v_cache[li][:, :end].permute(0, 2, 1, 3)
-                a = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), kk, vv, attn_mask=mask,
-                                                   is_causal=(mask is None), enable_gqa=True)
-                a = a.permute(0, 2, 1, 3).reshape(B, n, H * D)
-                x = x + F.linear(a, lw["wo"])
-                x = x + self._mlp(self._norm(x, lw["norm2"]), lw)
-            if end == L:
-                last = F.linear(self._norm(x[:, -1], self.final_norm), self.lm_head).float()
+        last = torch.empty(B, s.vocab, device=self.dev, dtype=torch.float32)
+        step_b = max(1, int(seqs_per_pass))
+        for b0 in range(0, B, step_b):
+            b1 = min(B, b0 + step_b)
+            nb = b1 - b0
+            for start in range(0, L, chunk):
+                end = min(L, start + chunk)
+                n = end - start
+                x = self.embed[input_ids[b0:b1, start:end].to(self.dev)]                   # [nb,n,hidden]
+                positions = torch.arange(start, end, device=self.dev)
+                cos, sin = self._tables(positions)                                          # [n,D]
+                cos, sin = cos[None, :, None, :], sin[None, :, None, :]
+                mask = None
+                if start > 0:  # keys [0,end) against queries [start,end): causal inside the chunk only
+                    kidx = torch.arange(end, device=self.dev)[None, :]
+                    mask = kidx <= positions[:, None]
+                for li, lw in enumerate(self.layers):
+                    h = self._norm(x, lw["norm1"])
+                    qkv = F.linear(h, lw["wqkv"]).view(nb, n, H + 2 * KVH, D)
+                    q, k, v = qkv[:, :, :H], qkv[:, :, H:H + KVH], qkv[:, :, H + KVH:]
+                    q = _rope_seq(q, cos, sin)
+                    k = _rope_seq(k, cos, sin)
+                    self.k_cache[li][b0:b1, start:end].copy_(k)
+                    self.v_cache[li][b0:b1, start:end].copy_(v)
+                    kk = self.k_cache[li][b0:b1, :end].permute(0, 2, 1, 3)                 # [nb,KVH,end,D] view
+                    vv = self.v_cache[li][b0:b1, :end].permute(0, 2, 1, 3)
+                    a = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), kk, vv, attn_mask=mask,
+                                                       is_causal=(mask is None), enable_gqa=True)
+                    a = a.permute(0, 2, 1, 3).reshape(nb, n, H * D)
+                    x = x + F.linear(a, lw["wo"])
+                    x = x + self._mlp(self._norm(x, lw["norm2"]), lw)
+                if end == L:
+                    last[b0:b1] = F.linear(self._norm(x[:, -1], self.final_norm), self.lm_head).float()
         self.pos.fill_(L)
         return last
 
@@ -240,6 +246,7 @@ class DecodeRuntime:
         the reference's rule applied to ``max_len``)."""
         if self.attention == "sdpa":
             raise RuntimeError("only the sampled-attention steps are graph-capturable (their lengths live on the device)")
+        max_len = min(int(max_len), self.T)         # the lengths can never exceed the cache
         self._bn = self._plan_tile(max_len)
         saved = (self.pos.clone(), self.tok.clone())
         stream = torch.cuda.Stream(device=self.dev)

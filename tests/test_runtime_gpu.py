@@ -108,6 +108,14 @@ def test_backend_objects_follow_the_reference_adapter_contract():
     assert (big.float() - dense.float()).abs().mean().item() < 0.05
     with pytest.raises(backends.BackendError):
         backends.make_backend("fa2")
+    # short contexts: the default Prop backend must sample what the reference adapter's loop samples
+    # (32-row tiles up to 1536 tokens, 64-row tiles up to 3072), not the ragged call's 256-row tiles
+    for Ls in (700, 2500):
+        o_d, o_l = pb.decode(q, K, V, Ls), pl.decode(q, K, V, Ls)
+        assert pb.actual_mode == "single_loop_fallback" and torch.equal(o_d, o_l)
+    p256 = backends.SantaPropBackend(S=256, seed=7, block_n=256)
+    p256.decode(q, K, V, 700)
+    assert p256.actual_mode == "batch_ragged"
     # the start-up check of the reference (two sequences of 16 cached tokens): 32-row tiles, one tile
     for b in (fb, pb, pl, backends.make_backend("sdpa")):
         rep = b.smoke_test(device=dev, dtype=torch.bfloat16, num_heads=32, num_kv_heads=8, head_dim=128, valid_len=16)
