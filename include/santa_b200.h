@@ -4,9 +4,11 @@
  * Plain pointers and sizes only; every pointer is a DEVICE pointer unless the
  * comment says otherwise; `stream` is a cudaStream_t passed as void*.  All
  * entry points are asynchronous on `stream`, never synchronise the host, and
- * never allocate: scratch memory is a caller-provided workspace.  Return value:
- * 0 on success, a negative SANTA_E_* code otherwise (santa_strerror() gives
- * the text).  There is no CPU fallback anywhere in the library.
+ * never allocate: scratch memory is a caller-provided workspace (one entry
+ * point, santa_flash_decode_noalloc, brings its own fixed scratch instead).
+ * Return value: 0 on success, a negative SANTA_E_* code otherwise
+ * (santa_strerror() gives the text).  There is no CPU fallback anywhere in the
+ * library.
  *
  * Each entry point names the reference interface it replaces, by file:line in
  * the OPUSLab/SANTA tree:
@@ -77,15 +79,33 @@ SANTA_API float santa_u01(uint64_t seed, int head_index, int tile_index);
  * buffers alternate with its parity, so the ranks only have to stay within one step of each other --
  * which the wait itself guarantees.  epoch == 0 on every rank selects device-counted epochs: each
  * buffer carries its own step counter, read by the kernels and advanced by santa_lse_combine_wait, so
- * that a decode + wait pair captured once in a CUDA graph can be replayed for every step (a wait that
- * ran out does not advance the counter).  No counterpart in the reference (single device). */
+ * that a decode + wait pair captured once in a CUDA graph can be replayed for every step.
+ * With SANTA_PEER_COMBINE in `flags` the decode call does the receiving half itself: the kernel that
+ * stored a row waits (bounded) for the same row from every other rank and writes the combined `out` /
+ * `m_star` of santa_flash_decode -- one call per step, no santa_lse_combine_wait.  A wait that ran out
+ * leaves zeros in its rows and 4 in the workspace's status word and in santa_peer_exchange_status();
+ * the step still counts, so that this rank stays in step with the others; after such a failure all
+ * ranks re-zero their buffers behind a barrier before the exchange is used again.
+ * No counterpart in the reference (single device). */
+#define SANTA_PEER_COMBINE 1u
 typedef struct santa_peer_exchange {
   int world;             /* ranks taking part, 1..16 */
   int rank;              /* this rank */
   uint32_t epoch;        /* >= 1, or 0 = counted on the device */
-  uint32_t reserved;
+  uint32_t flags;        /* 0 or SANTA_PEER_COMBINE */
   void* peer_buffer[16]; /* [world] used */
 } santa_peer_exchange;
+
+/* How the scores q.K are formed (santa_flash_ext.score_mode, santa_prop_ext.score_mode).
+ *   SANTA_SCORE_EXACT   fp32 multiply-adds in the reference's order (F.cu:161-221, P.cu:317-379): the
+ *                       sampled row counts equal the reference's bit for bit.  The default.
+ *   SANTA_SCORE_TENSOR  tensor cores (mma.sync m16n8k16, fp32 accumulate); the fp32-scaled query is
+ *                       split into two 16-bit parts, so the scores agree with the exact ones to about
+ *                       1e-6 relative, but not bit for bit: on rare rows a sampled count moves to a
+ *                       neighbouring row.  Takes the score arithmetic off the fp32 pipe, which is
+ *                       what bounds the exact mode.  Opt-in; never chosen by the library itself. */
+#define SANTA_SCORE_EXACT 0
+#define SANTA_SCORE_TENSOR 1
 
 typedef struct santa_flash_ext {
   /* Added to the batch index in the RNG key (head index b*H+h, F.cu:281) so that a batch-sharded
@@ -96,7 +116,7 @@ typedef struct santa_flash_ext {
   /* If >= 0, replaces the S_per_tile computed from S and this call's own tile count (a sequence
    * shard must use the budget of the WHOLE sequence).  -1 = reference rule. */
   int s_per_tile_override;
-  int reserved0;
+  int score_mode; /* SANTA_SCORE_EXACT (0, the reference's arithmetic) or SANTA_SCORE_TENSOR */
   /* If not NULL: [B,H,130] fp32 unnormalised partial result per head -- A[128], m, Z -- such that
    * out = A / (Z * S_per_tile) and partials of disjoint tile sets combine with santa_lse_combine().
    * `out` may then be NULL. */
@@ -155,24 +175,35 @@ SANTA_API int32_t* santa_workspace_status(void* workspace);
  * servers that give all free device memory to their KV-cache pool at start-up and forbid any
  * allocation on the decode path (cudaMalloc stalls the whole device and may fail once memory is
  * fragmented), and plain C / cgo hosts that have no device allocator of their own.  The scratch
- * lives in a fixed SANTA_NOALLOC_SCRATCH_BYTES array inside the library (every GPU that loads the
- * library holds it until the process exits); the entry point calls no cudaMalloc, cudaFree or any
- * allocating routine.  This entry point has no counterpart in the reference.
+ * lives in a fixed SANTA_NOALLOC_SCRATCH_BYTES array inside the library; the entry point calls no
+ * cudaMalloc, cudaFree or any allocating routine.  This entry point has no counterpart in the
+ * reference.
  *
  * Arguments, results and error codes are those of santa_flash_decode without the workspace pair.
  * A problem whose scratch need (santa_flash_workspace_bytes) exceeds SANTA_NOALLOC_SCRATCH_BYTES is
  * rejected with SANTA_E_TOO_LARGE before anything is launched; with 8 kv-heads that is roughly
  * more than 100 sequences per call.
  *
- * The first call on a device looks up the device address of the array (with that device current);
- * make that first call outside any stream capture.  All calls on a device share the one array: the
- * entry point clears the part that must start at zero on `stream` before launching, and two calls
- * whose kernels may overlap on the GPU (different streams, no ordering) race on it -- order them.
+ * The first call on a device looks up the device address of the array (with that device current).
+ * Under CUDA's lazy module loading that first call is also the moment the device sets the array's
+ * 4 MiB aside -- from then on every such GPU holds them until the process exits -- so make it
+ * before the device's free memory is given away (a KV-cache pool sized to "all that is left"), and
+ * outside any stream capture.  All calls on a device share the one array and nothing in it is
+ * cleared between calls: every call overwrites what it reads, except the status word, which starts
+ * at zero when the module is loaded and from then on only changes when a bounded wait inside a
+ * kernel ran out (1 or 2, see santa_workspace_status; the result of that call is invalid).  Read it
+ * through santa_noalloc_status() after synchronising the stream; a caller that has seen a non-zero
+ * value puts it back to zero itself (cudaMemsetAsync on that address).  Two calls whose kernels
+ * may overlap on the GPU (different streams, no ordering) race on the array -- order them.
  */
 #define SANTA_NOALLOC_SCRATCH_BYTES (4u << 20)
 SANTA_API int santa_flash_decode_noalloc(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH,
                                int D, int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
                                float* m_star, int32_t* vrows, const santa_flash_ext* ext, void* stream);
+
+/* Device address of the status word santa_flash_decode_noalloc uses on the CURRENT device, or NULL
+ * before that entry point's first call on it.  No counterpart in the reference. */
+SANTA_API int32_t* santa_noalloc_status(void);
 
 /* Bytes of workspace santa_flash_decode_ragged needs on the current device (0 on bad arguments). */
 SANTA_API size_t santa_flash_ragged_workspace_bytes(int B, int KVH, int max_len, int block_n);
@@ -227,6 +258,10 @@ typedef struct santa_prop_ext {
   int32_t* S_tiles;
   float* invdelta;
   float* a0;
+  /* SANTA_SCORE_EXACT (0) or SANTA_SCORE_TENSOR: applies to the streaming first pass (block_n == 256);
+   * the small-tile first pass already is the reference's own tensor-core arithmetic. */
+  int score_mode;
+  int reserved;
 } santa_prop_ext;
 
 /* Bytes of workspace santa_prop_decode needs on the current device for this problem. */
@@ -311,15 +346,12 @@ SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const vo
 
 /* ---- split-KV combine ------------------------------------------------------- */
 
-/*
- * Combine G unnormalised Flash partials (santa_flash_ext.partial_out of G calls over disjoint tile
- * sets of the same sequences): partials is [G][BH][130] fp32 -- A[128], m, Z.  Writes
- * out [BH,128] (storage dtype) = sum_r e^{m_r-m*} A_r / (S_per_tile * sum_r e^{m_r-m*} Z_r) and
- * m_star [BH] (may be NULL).  This is the reference's finalize (F.cu:386-470) over the union of the
- * tiles; the reference itself has no multi-device path.
- */
 /* Bytes of one rank's exchange buffer for `world` ranks and BH = B*H (batch x heads) partial rows. */
 SANTA_API size_t santa_peer_exchange_bytes(int world, int BH);
+
+/* Device address of the int32 inside an exchange buffer (this rank's own) that becomes 4 when a
+ * bounded wait on that buffer ran out.  Read it after synchronising the stream. */
+SANTA_API int32_t* santa_peer_exchange_status(void* own_buffer);
 
 /*
  * The receiving half of the peer exchange: wait until the partials of px->epoch from all px->world
@@ -331,6 +363,13 @@ SANTA_API size_t santa_peer_exchange_bytes(int world, int BH);
 SANTA_API int santa_lse_combine_wait(const santa_peer_exchange* px, int BH, int D, int S_per_tile, int dtype,
                                      void* out, float* m_star, int32_t* status, void* stream);
 
+/*
+ * Combine G unnormalised Flash partials (santa_flash_ext.partial_out of G calls over disjoint tile
+ * sets of the same sequences): partials is [G][BH][130] fp32 -- A[128], m, Z.  Writes
+ * out [BH,128] (storage dtype) = sum_r e^{m_r-m*} A_r / (S_per_tile * sum_r e^{m_r-m*} Z_r) and
+ * m_star [BH] (may be NULL).  This is the reference's finalize (F.cu:386-470) over the union of the
+ * tiles; the reference itself has no multi-device path.
+ */
 SANTA_API int santa_lse_combine(const float* partials, int G, int BH, int D, int S_per_tile, int dtype, void* out,
                       float* m_star, void* stream);
 

@@ -14,6 +14,9 @@ LIB_PATH = os.path.join(_PKG, "lib", "libsanta_b200.so")
 
 SANTA_DTYPE_BF16 = 0
 SANTA_DTYPE_F16 = 1
+SANTA_PEER_COMBINE = 1
+SANTA_SCORE_EXACT = 0
+SANTA_SCORE_TENSOR = 1
 
 
 class SantaError(RuntimeError):
@@ -31,7 +34,7 @@ class PeerExchange(C.Structure):
         ("world", C.c_int),
         ("rank", C.c_int),
         ("epoch", C.c_uint32),
-        ("reserved", C.c_uint32),
+        ("flags", C.c_uint32),
         ("peer_buffer", C.c_void_p * 16),
     ]
 
@@ -43,7 +46,7 @@ class FlashExt(C.Structure):
         ("batch_offset", C.c_int),
         ("tile_offset", C.c_int),
         ("s_per_tile_override", C.c_int),
-        ("reserved0", C.c_int),
+        ("score_mode", C.c_int),
         ("partial_out", C.c_void_p),
         ("m_tiles", C.c_void_p),
         ("ell_tiles", C.c_void_p),
@@ -69,6 +72,8 @@ class PropExt(C.Structure):
         ("S_tiles", C.c_void_p),
         ("invdelta", C.c_void_p),
         ("a0", C.c_void_p),
+        ("score_mode", C.c_int),
+        ("reserved", C.c_int),
     ]
 
 
@@ -89,6 +94,8 @@ EXPORTS = (
     "santa_prop_decode",
     "santa_lse_combine",
     "santa_flash_decode_noalloc",
+    "santa_noalloc_status",
+    "santa_peer_exchange_status",
     "santa_prop_ragged_workspace_bytes",
     "santa_prop_decode_ragged",
     "santa_flash_ragged_workspace_bytes",
@@ -182,6 +189,12 @@ def lib() -> C.CDLL:
     if hasattr(L, "santa_flash_decode_noalloc"):
         L.santa_flash_decode_noalloc.restype = C.c_int
         L.santa_flash_decode_noalloc.argtypes = L.santa_flash_decode.argtypes[:16] + [C.POINTER(FlashExt), C.c_void_p]
+    if hasattr(L, "santa_noalloc_status"):
+        L.santa_noalloc_status.restype = C.c_void_p
+        L.santa_noalloc_status.argtypes = []
+    if hasattr(L, "santa_peer_exchange_status"):
+        L.santa_peer_exchange_status.restype = C.c_void_p
+        L.santa_peer_exchange_status.argtypes = [C.c_void_p]
     if hasattr(L, "santa_lse_combine"):
         L.santa_lse_combine.restype = C.c_int
         L.santa_lse_combine.argtypes = [

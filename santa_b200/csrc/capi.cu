@@ -55,17 +55,20 @@ EncodeTiledFn encode_tiled_fn() {
 
 // Tensor map of a K cache [B][L_storage][KVH][128] of 16-bit elements with a
 // {128, 1, kStageRows, 1} box: one kv-head's rows of kStageRows tokens.
-int encode_k_map(CUtensorMap* tm, const void* K, int B, int L_storage, int KVH) {
+// swizzled: {64, 1, kStageRows, 1} boxes with the 128-byte swizzle (two per piece), the staging of
+// the tensor-core score path.
+int encode_k_map(CUtensorMap* tm, const void* K, int B, int L_storage, int KVH, bool swizzled = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return cuda_fail(cudaErrorNotSupported);
   const cuuint64_t dims[4] = {cuuint64_t(santa::kD), cuuint64_t(KVH), cuuint64_t(L_storage), cuuint64_t(B)};
   const cuuint64_t strides[3] = {cuuint64_t(santa::kRowBytes), cuuint64_t(KVH) * santa::kRowBytes,
                                  cuuint64_t(L_storage) * KVH * santa::kRowBytes};
-  const cuuint32_t box[4] = {cuuint32_t(santa::kD), 1u, cuuint32_t(santa::kStageRows), 1u};
+  const cuuint32_t box[4] = {cuuint32_t(swizzled ? santa::kD / 2 : santa::kD), 1u, cuuint32_t(santa::kStageRows), 1u};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(K), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
   return SANTA_OK;
 }
@@ -73,10 +76,12 @@ int encode_k_map(CUtensorMap* tm, const void* K, int B, int L_storage, int KVH) 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Deal (column group, tile) items to the 8 column slots of each persistent CTA.
-// Narrower column groups give more, smaller items.  The width that minimises
-// the busiest SM's load (in column-tiles) wins; on a tie the widest does, since
-// wide groups fetch whole token rows together.
+// Deal (column group, tile) items to the 8 column slots of each persistent CTA (the device side is
+// warp_work in sampler.cuh).  For every group width the items are cut into one range per virtual
+// group and the virtual groups are dealt to the CTAs in contiguous runs; the cost of a width is the
+// column-tiles of its busiest CTA.  Wide groups fetch whole token rows together, so a narrower width
+// only replaces a wider one when it takes at least 3 % off that cost -- which it does when the
+// problem has only one or two tiles per slot and whole tiles would otherwise be dealt unevenly.
 // `within` > 0 restricts the width to divisors of it (ragged batches: a column group must not
 // span two sequences, so the width has to divide KVH).
 santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid, int within = 0) {
@@ -88,11 +93,15 @@ santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid, int within = 
     const long long items = ncg * T_c;
     const long long slots = (long long)sms * (santa::kGroupWarps / gw);
     const long long nvg = items < slots ? items : slots;
-    const long long per = (items + nvg - 1) / nvg;           // items of the busiest virtual group
     const long long ctas = nvg < sms ? nvg : sms;
-    const long long groups_per_cta = (nvg + ctas - 1) / ctas;  // virtual groups on the busiest CTA
-    const long long load = per * groups_per_cta * gw;
-    if (best_load < 0 || load < best_load) {
+    long long busiest = 0;  // items of the busiest CTA
+    for (long long c = 0; c < ctas; ++c) {
+      const long long v0 = santa::range_lo(c, nvg, ctas), v1 = santa::range_lo(c + 1, nvg, ctas);
+      const long long n = santa::range_lo(v1, items, nvg) - santa::range_lo(v0, items, nvg);
+      busiest = n > busiest ? n : busiest;
+    }
+    const long long load = busiest * gw;
+    if (best_load < 0 || load * 100 < best_load * 97) {
       best_load = load;
       best.gw = gw;
       best.nvg = int(nvg);
@@ -242,7 +251,7 @@ const char* santa_strerror(int code) {
 }
 
 int santa_last_cuda_error(void) { return g_last_cuda_error; }
-int santa_abi_version(void) { return 2; }
+int santa_abi_version(void) { return 3; }
 
 int santa_block_n_rule(int L_valid, int block_n) {
   if (block_n > 0) return block_n;
@@ -297,9 +306,11 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
     if (px->world < 1 || px->world > santa::kMaxPeers || px->rank < 0 || px->rank >= px->world) return SANTA_E_ARG;
     for (int r = 0; r < px->world; ++r)
       if (!px->peer_buffer[r] || (reinterpret_cast<uintptr_t>(px->peer_buffer[r]) & 255u)) return SANTA_E_ARG;
+    if ((px->flags & SANTA_PEER_COMBINE) && !out) return SANTA_E_ARG;  // the combined result needs a place
   }
   if (ext && ((ext->u16 == nullptr) != (ext->counts == nullptr))) return SANTA_E_ARG;
   if (ext && ((ext->m_tiles == nullptr) != (ext->ell_tiles == nullptr))) return SANTA_E_ARG;
+  if (ext && ext->score_mode != SANTA_SCORE_EXACT && ext->score_mode != SANTA_SCORE_TENSOR) return SANTA_E_ARG;
   if (!aligned16(q) || !aligned16(K) || !aligned16(V) || (out && !aligned16(out))) return SANTA_E_ALIGN;
 
   FlashPlan pl;
@@ -313,7 +324,8 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   santa::StreamParams p{};
-  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH)) return rc;
+  p.score_mma = (ext && ext->score_mode == SANTA_SCORE_TENSOR) ? 1 : 0;
+  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH, p.score_mma != 0)) return rc;
   p.q = q;
   p.V = V;
   p.H = H;
@@ -353,11 +365,13 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   mp.m_star = m_star;
   mp.vrows = vrows;
   mp.partial_out = want_partial ? ext->partial_out : nullptr;
+  mp.status = p.status;
   if (ext && ext->peer) {
     const santa_peer_exchange* px = ext->peer;
     mp.px.world = px->world;
     mp.px.rank = px->rank;
-    mp.px.parity = px->epoch == 0 ? -1 : int(px->epoch & 1u);
+    mp.px.epoch = px->epoch;
+    mp.px.combine = (px->flags & SANTA_PEER_COMBINE) ? 1 : 0;
     for (int r = 0; r < px->world; ++r) mp.px.base[r] = static_cast<unsigned char*>(px->peer_buffer[r]);
   }
 
@@ -384,6 +398,7 @@ int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int d
     return SANTA_E_ARG;  // the sequence-sharding extensions belong to the uniform entry point
   if (ext && ((ext->u16 == nullptr) != (ext->counts == nullptr))) return SANTA_E_ARG;
   if (ext && ((ext->m_tiles == nullptr) != (ext->ell_tiles == nullptr))) return SANTA_E_ARG;
+  if (ext && ext->score_mode != SANTA_SCORE_EXACT && ext->score_mode != SANTA_SCORE_TENSOR) return SANTA_E_ARG;
   if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
 
   FlashPlan pl;
@@ -394,7 +409,8 @@ int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int d
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   santa::StreamParams p{};
-  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH)) return rc;
+  p.score_mma = (ext && ext->score_mode == SANTA_SCORE_TENSOR) ? 1 : 0;
+  if (int rc = encode_k_map(&p.tmK, K, B, L_storage, KVH, p.score_mma != 0)) return rc;
   p.q = q;
   p.V = V;
   p.H = H;
@@ -453,6 +469,7 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
   if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
   const int mode = ext ? ext->pass1_mode : 0;
   if (mode < 0 || mode > 2) return SANTA_E_ARG;
+  if (ext && ext->score_mode != SANTA_SCORE_EXACT && ext->score_mode != SANTA_SCORE_TENSOR) return SANTA_E_ARG;
   PropPlan pl;
   if (int rc = plan_prop(H, KVH, D, L, block_n, mode, &pl)) return rc;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
@@ -461,8 +478,9 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
 
   santa::PropParams p{};
   santa::StreamParams& sp = p.sp;
+  sp.score_mma = (pl.use_vec && ext && ext->score_mode == SANTA_SCORE_TENSOR) ? 1 : 0;
   if (pl.use_vec)
-    if (int rc = encode_k_map(&sp.tmK, K, 1, L, KVH)) return rc;
+    if (int rc = encode_k_map(&sp.tmK, K, 1, L, KVH, sp.score_mma != 0)) return rc;
   sp.q = q;
   sp.V = V;
   sp.H = H;
@@ -518,6 +536,7 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
   if (!aligned16(q) || !aligned16(K) || !aligned16(V) || !aligned16(out)) return SANTA_E_ALIGN;
   if (max_len <= 0 || max_len > L_storage) return SANTA_E_LENGTH;
   if (ext && ext->pass1_mode != 0 && ext->pass1_mode != 2) return SANTA_E_ARG;
+  if (ext && ext->score_mode != SANTA_SCORE_EXACT && ext->score_mode != SANTA_SCORE_TENSOR) return SANTA_E_ARG;
   PropRaggedPlan pl;
   if (int rc = plan_prop_ragged(B, H, KVH, D, max_len, &pl)) return rc;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < pl.total)
@@ -526,7 +545,8 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
 
   santa::PropParams p{};
   santa::StreamParams& sp = p.sp;
-  if (int rc = encode_k_map(&sp.tmK, K, B, L_storage, KVH)) return rc;
+  sp.score_mma = (ext && ext->score_mode == SANTA_SCORE_TENSOR) ? 1 : 0;
+  if (int rc = encode_k_map(&sp.tmK, K, B, L_storage, KVH, sp.score_mma != 0)) return rc;
   sp.q = q;
   sp.V = V;
   sp.H = H;
@@ -565,6 +585,10 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
   cudaError_t e = santa::launch_prop(p, dtype, pl.grid, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e);
   return SANTA_OK;
+}
+
+int32_t* santa_peer_exchange_status(void* own_buffer) {
+  return own_buffer ? static_cast<int32_t*>(own_buffer) + santa::kPeerStatusIndex : nullptr;
 }
 
 size_t santa_peer_exchange_bytes(int world, int BH) {
@@ -643,10 +667,17 @@ int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj
 // device, and is what the kernels receive.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SANTA_NOALLOC_SCRATCH_BYTES];
 
+static void* scratch_of_device[64] = {};
+
+int32_t* santa_noalloc_status(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return static_cast<int32_t*>(scratch_of_device[dev]);  // the status word is the array's first word
+}
+
 int santa_flash_decode_noalloc(const void* q, const void* K, const void* V, int dtype, int B, int H, int KVH, int D,
                                int L_valid, int L_storage, int64_t S, uint64_t seed, int block_n, void* out,
                                float* m_star, int32_t* vrows, const santa_flash_ext* ext, void* stream) {
-  static void* scratch_of_device[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -661,9 +692,9 @@ int santa_flash_decode_noalloc(const void* q, const void* K, const void* V, int 
   // sizes beyond the fixed array are refused; argument errors are left to the common path below
   const size_t need = santa_flash_workspace_bytes(B, KVH, L_valid, block_n);
   if (need > size_t(SANTA_NOALLOC_SCRATCH_BYTES)) return SANTA_E_TOO_LARGE;
-  // the array keeps the previous call's contents; only the status word has to start at zero
-  e = cudaMemsetAsync(scratch, 0, 256, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return cuda_fail(e);
+  // The array keeps the previous call's contents.  Every word a call reads it has written before,
+  // except the status word: that one is zero from the module's load image and is left alone here, so
+  // that a time-out reported by an earlier call stays readable (santa_noalloc_status).
   return santa_flash_decode(q, K, V, dtype, B, H, KVH, D, L_valid, L_storage, S, seed, block_n, out, m_star, vrows,
                             scratch, size_t(SANTA_NOALLOC_SCRATCH_BYTES), ext, stream);
 }

@@ -86,6 +86,29 @@ struct Store16<__half> {
   }
 };
 
+// ---------------------------------------------------------------- tensor-core step
+// One m16n8k16 step, fp32 accumulate, 16-bit operands of the storage type.
+template <typename TK>
+struct MmaOp;
+template <>
+struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+};
+template <>
+struct MmaOp<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  }
+};
+
 // ---------------------------------------------------------------- async staging
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -143,6 +166,79 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int 
       "[%6];" ::"r"(dst),
       "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
+}
+
+// ---------------------------------------------------------------- cross-device combine
+// int32 control words at the start of a rank's exchange buffer (after the arrival counters)
+constexpr int kPeerDoneIndex = 32;    // rows finished by the receiving side in this step
+constexpr int kPeerStepIndex = 33;    // steps completed so far (device-counted epochs)
+constexpr int kPeerStatusIndex = 34;  // 4 once a wait on this buffer ran out
+
+// Folds n raw Flash partials of one (sequence, head) row -- A[128], m, Z each, `stride` floats apart,
+// produced for disjoint tile sets -- in index order and writes the normalised row: the reference's
+// finalize (flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:386-470) over the union
+// of the tiles,
+//   m* = max_r m_r,  out = sum_r e^{m_r-m*} A_r / (S_per_tile * sum_r e^{m_r-m*} Z_r).
+// One warp per row, lane l owns dims 4l..4l+3.  Every operation is spelled out, so that all
+// translation units (whatever their floating-point flags) produce the same bits.
+template <typename TK>
+__device__ __forceinline__ void combine_rows(const float* rows, size_t stride, int n, int S_per_tile, int lane,
+                                             TK* out_row, float* m_star_row) {
+  constexpr int W = kD + 2;
+  (void)W;
+  float ms = -CUDART_INF_F;
+  for (int r = 0; r < n; ++r) ms = fmaxf(ms, __ldcg(rows + size_t(r) * stride + kD));
+  float zs = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < n; ++r) {
+    const float* p = rows + size_t(r) * stride;
+    const float e = __expf(__fsub_rn(__ldcg(p + kD), ms));
+    zs = __fmaf_rn(e, __ldcg(p + kD + 1), zs);
+    const float2 a01 = __ldcg(reinterpret_cast<const float2*>(p) + 2 * lane);
+    const float2 a23 = __ldcg(reinterpret_cast<const float2*>(p) + 2 * lane + 1);
+    acc.x = __fmaf_rn(e, a01.x, acc.x);
+    acc.y = __fmaf_rn(e, a01.y, acc.y);
+    acc.z = __fmaf_rn(e, a23.x, acc.z);
+    acc.w = __fmaf_rn(e, a23.y, acc.w);
+  }
+  const float inv = (S_per_tile > 0 && zs > 0.f) ? __frcp_rn(__fmul_rn(zs, (float)S_per_tile)) : 0.f;
+  uint2 wv;
+  wv.x = uint32_t(Store16<TK>::bits(__fmul_rn(acc.x, inv))) | (uint32_t(Store16<TK>::bits(__fmul_rn(acc.y, inv))) << 16);
+  wv.y = uint32_t(Store16<TK>::bits(__fmul_rn(acc.z, inv))) | (uint32_t(Store16<TK>::bits(__fmul_rn(acc.w, inv))) << 16);
+  *reinterpret_cast<uint2*>(out_row + 4 * lane) = wv;
+  if (lane == 0 && m_star_row != nullptr) *m_star_row = ms;
+}
+
+// Bounded wait of lanes 0..world-1 on one int32 word each (lane r: `word_of_lane`) until it holds
+// `want` or -- counters -- has passed it; system-scope acquire loads, sleeping between polls.
+// Returns true on every lane when all arrived within the limit (about a second).
+__device__ __forceinline__ bool peer_wait(const int* word_of_lane, bool polls, unsigned want, bool counter) {
+  bool ok = true;
+  if (polls) {
+    ok = false;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(word_of_lane) : "memory");
+      if (counter ? (int(unsigned(v) - want) >= 0) : (unsigned(v) == want)) {
+        ok = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+// The last row of a step to finish on the receiving side puts the row counter back to zero and
+// advances the buffer's step counter; rows whose wait ran out count too, so that the counters never
+// stay half-way and this rank stays in step with the others.
+__device__ __forceinline__ void peer_step_done(int* ctl, int rows_per_step) {
+  __threadfence();
+  if (atomicAdd(ctl + kPeerDoneIndex, 1) == rows_per_step - 1) {
+    ctl[kPeerDoneIndex] = 0;
+    __threadfence();
+    atomicAdd(ctl + kPeerStepIndex, 1);
+  }
 }
 
 // ---------------------------------------------------------------- work split

@@ -31,27 +31,6 @@
 namespace santa {
 
 // ------------------------------------------------------------------ pass 1, tensor-core path
-template <typename TK>
-struct MmaOp;
-template <>
-struct MmaOp<__nv_bfloat16> {
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-  }
-};
-template <>
-struct MmaOp<__half> {
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-  }
-};
-
 // One CTA per (tile, kv-head), one warp per 16 K rows.  The scores are formed
 // exactly like the reference's 16x16x16 WMMA steps (q*scale rounded to the
 // storage type, fp32 accumulation over 16-wide k steps in ascending order); a
@@ -588,20 +567,27 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   const int H = p.sp.H, KVH = p.sp.KVH, L = p.sp.L_valid;
   if (p.use_vec) {
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1, false>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
-      if (e != cudaSuccess) return e;
-      e = cudaFuncSetAttribute(stream_kernel<TK, 256, kModePropPass1, true>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
-      if (e != cudaSuccess) return e;
+      const void* kernels[4] = {(const void*)stream_kernel<TK, 256, kModePropPass1, false, false>,
+                                (const void*)stream_kernel<TK, 256, kModePropPass1, true, false>,
+                                (const void*)stream_kernel<TK, 256, kModePropPass1, false, true>,
+                                (const void*)stream_kernel<TK, 256, kModePropPass1, true, true>};
+      for (const void* k : kernels) {
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes);
+        if (e != cudaSuccess) return e;
+      }
       configured[dev] = true;
     }
-    if (p.sp.seq_lens != nullptr)
-      e = launch_dependent(stream_kernel<TK, 256, kModePropPass1, true>, dim3(grid), dim3(kCtaWarps * 32),
-                           kStreamSmemBytes, stream, p.sp);
+    const bool ragged = p.sp.seq_lens != nullptr;
+    if (p.sp.score_mma)
+      e = ragged ? launch_dependent(stream_kernel<TK, 256, kModePropPass1, true, true>, dim3(grid),
+                                    dim3(kCtaWarps * 32), kStreamSmemBytes, stream, p.sp)
+                 : launch_dependent(stream_kernel<TK, 256, kModePropPass1, false, true>, dim3(grid),
+                                    dim3(kCtaWarps * 32), kStreamSmemBytes, stream, p.sp);
     else
-      e = launch_dependent(stream_kernel<TK, 256, kModePropPass1, false>, dim3(grid), dim3(kCtaWarps * 32),
-                           kStreamSmemBytes, stream, p.sp);
+      e = ragged ? launch_dependent(stream_kernel<TK, 256, kModePropPass1, true, false>, dim3(grid),
+                                    dim3(kCtaWarps * 32), kStreamSmemBytes, stream, p.sp)
+                 : launch_dependent(stream_kernel<TK, 256, kModePropPass1, false, false>, dim3(grid),
+                                    dim3(kCtaWarps * 32), kStreamSmemBytes, stream, p.sp);
     if (e != cudaSuccess) return e;
   } else {
     const int nwarp = p.block_n / 16;

@@ -282,9 +282,14 @@ __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const 
 
 // ---------------------------------------------------------------- work split over column slots
 // A CTA has kGroupWarps column slots.  With group width gw (a power of two
-// <= 8) the slots form 8/gw slot groups of gw columns; slot group sg of CTA c
-// is virtual group vg = sg*ctas + c, which owns a contiguous balanced range
-// of the (column group, tile) items, column groups being gw consecutive columns.
+// <= 8) the slots form 8/gw slot groups of gw columns.  The (column group,
+// tile) items -- column groups being gw consecutive columns -- are cut into nvg
+// contiguous, balanced ranges, one per virtual group, and the virtual groups
+// are dealt to the CTAs in contiguous, balanced runs: CTA c runs the virtual
+// groups [lo(c), lo(c+1)) with lo(c) = floor(c * nvg / ctas), one per slot
+// group.  A CTA's slot groups therefore hold neighbouring item ranges and the
+// CTAs' item totals differ by at most one item, also when the virtual groups'
+// own sizes differ (a problem of few tiles per slot).
 struct WarpWork {
   int vg, col_in_group;
   long long lo, hi;
@@ -292,9 +297,10 @@ struct WarpWork {
 
 __device__ __forceinline__ WarpWork warp_work(const WorkSplit& w, int cta, int ctas, int slot) {
   WarpWork r;
-  // virtual groups are dealt round-robin to the CTAs, so that a problem with few groups still
-  // spreads over all SMs
-  r.vg = (slot / w.gw) * ctas + cta;
+  const int first = int(range_lo(cta, w.nvg, ctas));
+  const int count = int(range_lo(cta + 1, w.nvg, ctas)) - first;  // <= 8 / gw by construction of nvg
+  const int sg = slot / w.gw;
+  r.vg = (sg < count) ? first + sg : w.nvg;
   r.col_in_group = slot % w.gw;
   if (r.vg < w.nvg) {
     r.lo = range_lo(r.vg, w.items, w.nvg);

@@ -8,6 +8,8 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "common.cuh"
+
 namespace santa {
 
 // how (column group, tile) items are dealt to the column slots of the CTAs
@@ -21,7 +23,9 @@ struct WorkSplit {
 
 // Streaming kernels: Flash decode and Prop's first pass.
 struct StreamParams {
-  CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,32,1}
+  CUtensorMap tmK;  // K as a [B][L_storage][KVH][128] 16-bit tensor, box {128,1,32,1}; with score_mma
+                    // box {64,1,32,1} and the 128-byte swizzle
+  int score_mma;    // 1: scores from the tensor cores (opt-in), 0: the reference's fp32 order
   const void* q;    // [B,H,128]
   const void* V;    // [B,L_storage,KVH,128]
   int H, KVH;
@@ -56,15 +60,25 @@ struct StreamParams {
 };
 
 // Peer exchange: layout of one rank's buffer and what the kernels need of it.
+//   [0, 256)   int32 control words: arrival counters [2 parities][kMaxPeers senders], then the
+//              words named below
+//   then       int32 row flags [2 parities][world senders][BH rows]: the epoch of the row last stored
+//   then       fp32 rows      [2 parities][world senders][BH rows][130]
 constexpr int kMaxPeers = 16;
-constexpr size_t kPeerFlagBytes = 256;  // int32 counters [2 parities][kMaxPeers senders], then the data
-__host__ __device__ inline size_t peer_data_offset(int parity, int world, int sender, int BH) {
-  return kPeerFlagBytes + ((size_t(parity) * world + sender) * BH) * 130 * sizeof(float);
+constexpr size_t kPeerFlagBytes = 256;
+__host__ __device__ inline size_t peer_row_flags_bytes(int world, int BH) {
+  return (size_t(2) * world * BH * sizeof(int) + 255) / 256 * 256;
 }
-constexpr int kPeerDoneIndex = 32;   // int32 slots of the flag area: rows finished by the wait kernel
-constexpr int kPeerStepIndex = 33;   //   and the steps completed so far (device-counted epochs)
+__host__ __device__ inline size_t peer_row_flag_offset(int parity, int world, int sender, int BH) {
+  return kPeerFlagBytes + ((size_t(parity) * world + sender) * BH) * sizeof(int);
+}
+__host__ __device__ inline size_t peer_data_offset(int parity, int world, int sender, int BH) {
+  return kPeerFlagBytes + peer_row_flags_bytes(world, BH) + ((size_t(parity) * world + sender) * BH) * 130 * sizeof(float);
+}
 struct PeerScatter {
-  int world, rank, parity;        // world == 0: no exchange; parity < 0: epoch = local step counter + 1
+  int world, rank;                // world == 0: no exchange
+  unsigned epoch;                 // 0: the epoch is the local buffer's step counter + 1
+  int combine;                    // 1: the sending kernel also waits for the other ranks' rows and combines
   unsigned char* base[kMaxPeers]; // every rank's buffer as mapped here
 };
 
@@ -81,6 +95,7 @@ struct FlashMergeParams {
   int* vrows;          // [B,KVH] or nullptr
   float* partial_out;  // [B,H,130] or nullptr
   PeerScatter px;      // also store the partial into every rank's exchange buffer
+  int* status;         // the workspace's status word
 };
 
 cudaError_t launch_flash(const StreamParams& p, const FlashMergeParams& mp, int dtype, int block_n, int grid,

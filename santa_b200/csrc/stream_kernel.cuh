@@ -18,6 +18,8 @@
 // prop_kernels.cu (compiled without); each instantiates only its own mode.
 #pragma once
 
+#include <type_traits>
+
 #include "sampler.cuh"
 #include "stream_scores.cuh"
 
@@ -29,10 +31,15 @@ constexpr int kModePropPass1 = 1;
 constexpr int kStreamStages = 2;
 constexpr int kMaxTileRows = 256;
 constexpr int kScoreBytes = kMaxTileRows * kGH * 4;  // one score buffer: scores, then u, then the emit list
-constexpr int kSlotSmem = kStreamStages * kStageBytes + 2 * kScoreBytes + kRedFloats * 4;
+// Dynamic shared memory, from a 1024-byte aligned base (the swizzled staging of the tensor-core score
+// path needs it): the staging rings of the eight slots, then per slot two score buffers and the
+// exchange buffer of the exact score path, then the mbarriers.
+constexpr int kSlotRing = kStreamStages * kStageBytes;
+constexpr int kSlotRest = 2 * kScoreBytes + kRedFloats * 4;
 constexpr int kSlotBars = kStreamStages + 4;  // ring + full[2] + empty[2]
 constexpr int kCtaWarps = 2 * kGroupWarps;
-constexpr size_t kStreamSmemBytes = size_t(kGroupWarps) * kSlotSmem + size_t(kGroupWarps) * kSlotBars * 8;
+constexpr size_t kStreamSmemBytes =
+    1024 + size_t(kGroupWarps) * (kSlotRing + kSlotRest) + size_t(kGroupWarps) * kSlotBars * 8;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -40,20 +47,25 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // RAGGED: per-sequence lengths from p.seq_lens (a compile-time switch, so that the uniform kernel
 // carries none of the look-up state).
-template <typename TK, int BN, int MODE, bool RAGGED = false>
+// MMA: scores from the tensor cores (stream_scores.cuh, opt-in): p.tmK then describes swizzled
+// half-row boxes.  Everything after the scores is the same code.
+template <typename TK, int BN, int MODE, bool RAGGED = false, bool MMA = false>
 __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_constant__ StreamParams p) {
   constexpr int NW = (BN == 256) ? 8 : 4;  // warps of the reference block (fixes the ell order)
 
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int cta_warp = threadIdx.x >> 5;
   const int slot = cta_warp & (kGroupWarps - 1);
   const bool is_sampler = cta_warp >= kGroupWarps;
   const int lane = threadIdx.x & 31;
 
-  unsigned char* sbase = smem + size_t(slot) * kSlotSmem;
-  float* scorebufs = reinterpret_cast<float*>(sbase + kStreamStages * kStageBytes);
-  float* red = reinterpret_cast<float*>(sbase + kStreamStages * kStageBytes + 2 * kScoreBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kGroupWarps) * kSlotSmem) + slot * kSlotBars;
+  unsigned char* sbase = smem + size_t(slot) * kSlotRing;
+  unsigned char* srest = smem + size_t(kGroupWarps) * kSlotRing + size_t(slot) * kSlotRest;
+  float* scorebufs = reinterpret_cast<float*>(srest);
+  float* red = reinterpret_cast<float*>(srest + 2 * kScoreBytes);
+  uint64_t* bars =
+      reinterpret_cast<uint64_t*>(smem + size_t(kGroupWarps) * (kSlotRing + kSlotRest)) + slot * kSlotBars;
   const uint32_t bar_full = smem_u32(bars + kStreamStages);       // [2]
   const uint32_t bar_empty = smem_u32(bars + kStreamStages + 2);  // [2]
 
@@ -128,9 +140,12 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
       const int npieces = (row_end - row_base + kStageRows - 1) / kStageRows;
       int issued = 0;  // the K pieces do not depend on q: start them before fetching q
       for (; issued < kStreamStages && issued < npieces; ++issued)
-        ring.issue(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
-      QRegs Q;
-      load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
+        ring.template issue<MMA>(ring.count + issued, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
+      typename std::conditional<MMA, QFrag, QRegs>::type Q;
+      if constexpr (MMA)
+        load_q_frag<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
+      else
+        load_q<TK>(Qg + (size_t(b) * p.H + h0) * kD, p.q_scale, lane, Q);
 
 #pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t, ++handoff) {
@@ -151,10 +166,15 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             if (lane == 0) atomicExch(p.status, kStatusStageTimeout);
           }
           const unsigned char* st = ring.stage_ptr(ring.count);
-          score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
-          score_rows16<TK>(st + 16 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 16) * kGH, lane);
+          if constexpr (MMA) {
+            score_rows16_mma<TK>(smem_u32(st), 0, Q, scorebuf + (pc * kStageRows) * kGH, lane);
+            score_rows16_mma<TK>(smem_u32(st), 1, Q, scorebuf + (pc * kStageRows + 16) * kGH, lane);
+          } else {
+            score_rows16<TK>(st, Q, red, scorebuf + (pc * kStageRows) * kGH, lane);
+            score_rows16<TK>(st + 16 * kRowBytes, Q, red, scorebuf + (pc * kStageRows + 16) * kGH, lane);
+          }
           if (issued < npieces && !dead) {
-            ring.issue(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
+            ring.template issue<MMA>(ring.count + kStreamStages, &p.tmK, b, kv, row_base + issued * kStageRows, lane);
             ++issued;
           }
           ++ring.count;

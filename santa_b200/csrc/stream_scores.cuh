@@ -145,6 +145,69 @@ __device__ __forceinline__ void score_rows16(const unsigned char* __restrict__ r
   __syncwarp();
 }
 
+// ---------------------------------------------------------------- tensor-core scores (opt-in)
+// The same scores from the tensor cores: NOT the reference's floating-point order, hence an opt-in
+// mode whose sampled counts can differ from the reference's on rare rows.  The four query heads of
+// the group, scaled in fp32 like the exact path, are split into a high and a low 16-bit part
+// (q = hi + lo up to 2^-17 relative); the eight columns of an m16n8k16 step hold hi of heads 0..3
+// and lo of heads 0..3, the 16 rows are 16 K rows, and the score of (row, head) is the sum of the
+// two columns.  Products of two 16-bit values are exact in fp32, so the result differs from the
+// exact path only by the order and rounding of the fp32 accumulation inside the tensor core.
+//
+// Staging for this path: a 32-row piece arrives as two TMA boxes of 64 elements x 32 rows with the
+// 128-byte swizzle (16-byte chunk index XOR row mod 8), so that ldmatrix reads eight rows of one
+// k-chunk without bank conflicts.  Stage buffers are 1024-byte aligned.
+struct QFrag {
+  uint32_t b[kD / 16][2];  // B fragments of the eight k-steps
+};
+
+template <typename TK>
+__device__ __forceinline__ void load_q_frag(const TK* __restrict__ q_head0, float q_scale, int lane, QFrag& Q) {
+  const int n = lane >> 2;       // column of the fragment: heads 0..3 high parts, then their low parts
+  const int kk = 2 * (lane & 3);
+  const TK* qrow = q_head0 + (n & 3) * kD;
+#pragma unroll
+  for (int ks = 0; ks < kD / 16; ++ks)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const float2 f = Store16<TK>::unpack(*reinterpret_cast<const uint32_t*>(qrow + ks * 16 + half * 8 + kk));
+      const float x0 = f.x * q_scale, x1 = f.y * q_scale;
+      const float h0 = Store16<TK>::round(x0), h1 = Store16<TK>::round(x1);
+      const float v0 = (n < kGH) ? h0 : __fsub_rn(x0, h0);
+      const float v1 = (n < kGH) ? h1 : __fsub_rn(x1, h1);
+      Q.b[ks][half] = uint32_t(Store16<TK>::bits(v0)) | (uint32_t(Store16<TK>::bits(v1)) << 16);
+    }
+}
+
+// Scores of 16 consecutive rows of a swizzled piece.  `piece` is the shared-memory address of the
+// piece (1024-byte aligned: rows 0..31 x elements 0..63, then the same rows x elements 64..127),
+// `rb` selects its first or second 16 rows, `score_out` points at 64 floats laid out [row][head].
+template <typename TK>
+__device__ __forceinline__ void score_rows16_mma(uint32_t piece, int rb, const QFrag& Q,
+                                                 float* __restrict__ score_out, int lane) {
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const int row = rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // the row whose address this lane supplies
+#pragma unroll
+  for (int ks = 0; ks < kD / 16; ++ks) {
+    const int chunk = 2 * (ks & 3) + (lane >> 4);
+    const uint32_t addr = piece + (ks >> 2) * (kStageBytes / 2) + row * 128 + ((chunk ^ (row & 7)) << 4);
+    uint32_t a[4];
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                 : "r"(addr));
+    MmaOp<TK>::mma(c, a, Q.b[ks]);
+  }
+  // c0,c1: row lane/4, columns 2*(lane%4), +1;  c2,c3: row lane/4 + 8.  high + low part of a head
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] = __fadd_rn(c[i], __shfl_xor_sync(0xffffffffu, c[i], 2));
+  if ((lane & 3) < 2) {
+    float2* so = reinterpret_cast<float2*>(score_out);
+    so[(lane >> 2) * 2 + (lane & 3)] = make_float2(c[0], c[1]);
+    so[((lane >> 2) + 8) * 2 + (lane & 3)] = make_float2(c[2], c[3]);
+  }
+  __syncwarp();
+}
+
 // Per-warp staging ring: kStages pieces of kStageRows rows x 256 B, one mbarrier each.
 template <int kStages>
 struct WarpRing {
@@ -167,12 +230,21 @@ struct WarpRing {
   // box from the [B][L_storage][KVH][128] tensor `tmap` describes.  Rows past
   // the end of the storage read as zeros; the caller masks rows past the valid
   // length.
+  // SWZ: the map describes {64, 1, 32, 1} boxes with the 128-byte swizzle (tensor-core score path):
+  // two loads fill the slot, elements 0..63 of the rows first, elements 64..127 behind them.
+  template <bool SWZ = false>
   __device__ __forceinline__ void issue(uint32_t g, const void* tmap, int b, int kv, int row0, int lane) {
     if (lane == 0) {
       const uint32_t st = g % kStages;
       const uint32_t bar = bar0 + 8 * st;
       mbar_arrive_expect_tx(bar, kStageBytes);
-      tma_load_4d(smem_u32(data + st * kStageBytes), tmap, 0, kv, row0, b, bar);
+      const uint32_t dst = smem_u32(data + st * kStageBytes);
+      if (SWZ) {
+        tma_load_4d(dst, tmap, 0, kv, row0, b, bar);
+        tma_load_4d(dst + kStageBytes / 2, tmap, kD / 2, kv, row0, b, bar);
+      } else {
+        tma_load_4d(dst, tmap, 0, kv, row0, b, bar);
+      }
     }
   }
   __device__ __forceinline__ const unsigned char* stage_ptr(uint32_t g) const {

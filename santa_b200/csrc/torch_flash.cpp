@@ -96,7 +96,8 @@ at::Tensor& workspace_for(const at::Tensor& like, cudaStream_t stream, size_t by
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g,
                                                                  int64_t S, uint64_t seed, int64_t block_n,
-                                                                 bool want_vrows, int64_t valid_len) {
+                                                                 bool want_vrows, int64_t valid_len,
+                                                                 int64_t score_mode) {
   const ShapeInfo info = check_inputs(q_h, K_g, V_g);
   const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
   const int L = (valid_len > 0) ? (int)valid_len : L_storage;
@@ -124,11 +125,16 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
   SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
 
+  // score_mode: not part of the reference's signature; 0 (the default) is the reference's arithmetic
+  SANTA_CHECK(score_mode == SANTA_SCORE_EXACT || score_mode == SANTA_SCORE_TENSOR, "score_mode must be 0 or 1");
+  santa_flash_ext ext{};
+  ext.s_per_tile_override = -1;
+  ext.score_mode = (int)score_mode;
   const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
                                     q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, B, H, KVH,
                                     D, L, L_storage, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
                                     want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(),
-                                    nullptr, (void*)stream.stream());
+                                    score_mode ? &ext : nullptr, (void*)stream.stream());
   SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
               ")");
   return std::make_tuple(out, m_star, vrows);
@@ -140,7 +146,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic(at::Tensor q_h,
 std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tensor q_h, at::Tensor K_g,
                                                                         at::Tensor V_g, at::Tensor seq_lens,
                                                                         int64_t S, uint64_t seed, int64_t block_n,
-                                                                        bool want_vrows, int64_t max_len) {
+                                                                        bool want_vrows, int64_t max_len,
+                                                                        int64_t score_mode) {
   const ShapeInfo info = check_inputs(q_h, K_g, V_g);
   SANTA_CHECK(info.batched, "Ragged path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
   const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
@@ -167,10 +174,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tens
   const size_t ws_bytes = santa_flash_ragged_workspace_bytes(B, KVH, mlen, bn);
   SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  SANTA_CHECK(score_mode == SANTA_SCORE_EXACT || score_mode == SANTA_SCORE_TENSOR, "score_mode must be 0 or 1");
+  santa_flash_ext ext{};
+  ext.s_per_tile_override = -1;
+  ext.score_mode = (int)score_mode;
   const int rc = santa_flash_decode_ragged(
       q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16,
       B, H, KVH, D, L_storage, lens.data_ptr<int>(), mlen, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
-      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), nullptr,
+      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), score_mode ? &ext : nullptr,
       (void*)stream.stream());
   SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
               ")");
@@ -212,22 +223,29 @@ at::Tensor decode_systematic_partial(at::Tensor q_h, at::Tensor K_g, at::Tensor 
   return part;
 }
 
-santa_peer_exchange make_peer(const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch) {
+santa_peer_exchange make_peer(const std::vector<int64_t>& peer_ptrs, int64_t rank, int64_t epoch,
+                              bool combine = false) {
   SANTA_CHECK(!peer_ptrs.empty() && peer_ptrs.size() <= 16, "peer_ptrs must hold 1..16 buffer addresses");
   SANTA_CHECK(rank >= 0 && rank < (int64_t)peer_ptrs.size() && epoch >= 0, "bad rank / epoch of the peer exchange");
   santa_peer_exchange px{};
   px.world = (int)peer_ptrs.size();
   px.rank = (int)rank;
   px.epoch = (uint32_t)epoch;
+  px.flags = combine ? SANTA_PEER_COMBINE : 0u;
   for (size_t r = 0; r < peer_ptrs.size(); ++r) px.peer_buffer[r] = reinterpret_cast<void*>(peer_ptrs[r]);
   return px;
 }
 
 // Sequence-sharded decode whose partial goes straight into every rank's exchange buffer (peer-mapped
-// device memory) instead of through a collective; `lse_combine_wait` is the receiving half.
-void decode_systematic_exchange(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g, int64_t S, uint64_t seed,
-                                int64_t block_n, int64_t valid_len, int64_t batch_offset, int64_t tile_offset,
-                                int64_t s_per_tile, std::vector<int64_t> peer_ptrs, int64_t rank, int64_t epoch) {
+// device memory) instead of through a collective.  combine = true: the same call also waits for the
+// other ranks' rows and returns the combined (out, m_star); combine = false: it returns two empty
+// tensors and `lse_combine_wait` is the receiving half.
+std::tuple<at::Tensor, at::Tensor> decode_systematic_exchange(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g,
+                                                              int64_t S, uint64_t seed, int64_t block_n,
+                                                              int64_t valid_len, int64_t batch_offset,
+                                                              int64_t tile_offset, int64_t s_per_tile,
+                                                              std::vector<int64_t> peer_ptrs, int64_t rank,
+                                                              int64_t epoch, bool combine) {
   const ShapeInfo info = check_inputs(q_h, K_g, V_g);
   SANTA_CHECK(info.batched, "Batched path expects q_h [B,H,D], K_g/V_g [B,L,KVH,D]");
   const int B = info.B, H = info.H, D = info.D, KVH = info.KVH, L_storage = info.L_storage;
@@ -236,13 +254,16 @@ void decode_systematic_exchange(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g, 
   SANTA_CHECK(D == 128 && H % KVH == 0 && H / KVH == 4, "This build supports only D=128 and GH=4 (H/KVH)");
   const int bn = santa_block_n_rule(L, (int)block_n);
   SANTA_CHECK(bn == 32 || bn == 64 || bn == 256, "block_n must be 0 (auto) or one of {32,64,256}. Got block_n=", bn);
-  const santa_peer_exchange px = make_peer(peer_ptrs, rank, epoch);
+  const santa_peer_exchange px = make_peer(peer_ptrs, rank, epoch, combine);
   const c10::cuda::CUDAGuard guard(q_h.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   auto q = q_h.contiguous();
   const size_t ws_bytes = santa_flash_workspace_bytes(B, KVH, L, bn);
   SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  at::Tensor out = combine ? at::empty({B, H, D}, q.options()) : at::empty({0}, q.options());
+  at::Tensor m_star = combine ? at::empty({B, H}, q.options().dtype(at::kFloat))
+                              : at::empty({0}, q.options().dtype(at::kFloat));
   santa_flash_ext ext{};
   ext.batch_offset = (int)batch_offset;
   ext.tile_offset = (int)tile_offset;
@@ -250,10 +271,12 @@ void decode_systematic_exchange(at::Tensor q_h, at::Tensor K_g, at::Tensor V_g, 
   ext.peer = &px;
   const int rc = santa_flash_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
                                     q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, B, H, KVH,
-                                    D, L, L_storage, S, seed, bn, nullptr, nullptr, nullptr, ws.data_ptr(),
+                                    D, L, L_storage, S, seed, bn, combine ? out.data_ptr() : nullptr,
+                                    combine ? m_star.data_ptr<float>() : nullptr, nullptr, ws.data_ptr(),
                                     (size_t)ws.numel(), &ext, (void*)stream.stream());
   SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
               ")");
+  return std::make_tuple(out, m_star);
 }
 
 std::tuple<at::Tensor, at::Tensor> lse_combine_wait(std::vector<int64_t> peer_ptrs, int64_t rank, int64_t epoch,
@@ -298,15 +321,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("batch_offset") = 0, py::arg("tile_offset") = 0, py::arg("s_per_tile") = -1);
   m.def("decode_systematic_exchange", &decode_systematic_exchange, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("S"), py::arg("seed"), py::arg("block_n"), py::arg("valid_len"), py::arg("batch_offset"),
-        py::arg("tile_offset"), py::arg("s_per_tile"), py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"));
+        py::arg("tile_offset"), py::arg("s_per_tile"), py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"),
+        py::arg("combine") = false);
   m.def("lse_combine_wait", &lse_combine_wait, py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("B"),
         py::arg("H"), py::arg("s_per_tile"), py::arg("bf16"), py::arg("status"));
   m.def("lse_combine", &lse_combine, py::arg("partials"), py::arg("s_per_tile"), py::arg("bf16") = true);
   m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
         py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0,
-        py::arg("want_vrows") = false, py::arg("max_len") = -1);
+        py::arg("want_vrows") = false, py::arg("max_len") = -1, py::kw_only(), py::arg("score_mode") = 0);
+  // the reference's signature (santa_cuda.cpp:346-359), plus one keyword-only extra that defaults to its behaviour
   m.def("decode_systematic_scalar", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),
-        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1);
+        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1,
+        py::kw_only(), py::arg("score_mode") = 0);
   m.def("decode_systematic_batched", &decode_systematic, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"), py::arg("S"),
-        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1);
+        py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false, py::arg("valid_len") = -1,
+        py::kw_only(), py::arg("score_mode") = 0);
 }

@@ -76,7 +76,8 @@ at::Tensor& workspace_for(const at::Tensor& like, cudaStream_t stream, size_t by
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tensor q_h, at::Tensor K_g,
                                                                         at::Tensor V_g, int64_t S, uint64_t seed,
-                                                                        int64_t block_n, bool want_vrows) {
+                                                                        int64_t block_n, bool want_vrows,
+                                                                        int64_t score_mode) {
   SANTA_CHECK(q_h.is_cuda(), "q_h must be CUDA");
   SANTA_CHECK(K_g.is_cuda() && V_g.is_cuda(), "K_g and V_g must be CUDA");
   SANTA_CHECK(q_h.scalar_type() == at::kBFloat16 || q_h.scalar_type() == at::kHalf, "q_h must be bf16 or f16");
@@ -115,9 +116,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tens
   const size_t ws_bytes = santa_prop_workspace_bytes(H, KVH, D, L, bn);
   SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  SANTA_CHECK(score_mode == SANTA_SCORE_EXACT || score_mode == SANTA_SCORE_TENSOR, "score_mode must be 0 or 1");
   santa_prop_ext ext{};
   ext.pass1_mode = mode;
   ext.flags = 3;
+  ext.score_mode = (int)score_mode;  // not part of the reference's signature; 0 is its arithmetic
   const int rc = santa_prop_decode(q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(),
                                    q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16, H, KVH, D,
                                    L, S, seed, bn, out.data_ptr(), m_star.data_ptr<float>(),
@@ -136,7 +139,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tens
 std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tensor q_bh, at::Tensor K_g,
                                                                         at::Tensor V_g, at::Tensor seq_lens,
                                                                         int64_t S, uint64_t seed, bool want_vrows,
-                                                                        int64_t max_len) {
+                                                                        int64_t max_len, int64_t score_mode) {
   SANTA_CHECK(q_bh.is_cuda() && K_g.is_cuda() && V_g.is_cuda(), "q_bh, K_g and V_g must be CUDA");
   SANTA_CHECK(q_bh.scalar_type() == at::kBFloat16 || q_bh.scalar_type() == at::kHalf, "q_bh must be bf16 or f16");
   SANTA_CHECK(K_g.scalar_type() == q_bh.scalar_type() && V_g.scalar_type() == q_bh.scalar_type(),
@@ -172,10 +175,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tens
   const size_t ws_bytes = santa_prop_ragged_workspace_bytes(B, H, KVH, D, mlen);
   SANTA_CHECK(ws_bytes > 0, "santa_b200: could not size the workspace");
   at::Tensor& ws = workspace_for(q, stream.stream(), ws_bytes);
+  SANTA_CHECK(score_mode == SANTA_SCORE_EXACT || score_mode == SANTA_SCORE_TENSOR, "score_mode must be 0 or 1");
+  santa_prop_ext ext{};
+  ext.flags = 3;
+  ext.score_mode = (int)score_mode;
   const int rc = santa_prop_decode_ragged(
       q.data_ptr(), K_g.data_ptr(), V_g.data_ptr(), q.scalar_type() == at::kBFloat16 ? SANTA_DTYPE_BF16 : SANTA_DTYPE_F16,
       B, H, KVH, D, L_storage, lens.data_ptr<int>(), mlen, S, seed, out.data_ptr(), m_star.data_ptr<float>(),
-      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), nullptr,
+      want_vrows ? vrows.data_ptr<int>() : nullptr, ws.data_ptr(), (size_t)ws.numel(), &ext,
       (void*)stream.stream());
   SANTA_CHECK(rc == SANTA_OK, "santa_b200: ", santa_strerror(rc), " (code ", rc, ", cuda ", santa_last_cuda_error(),
               ")");
@@ -187,7 +194,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_ragged(at::Tens
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_systematic_ragged", &decode_systematic_ragged, py::arg("q_bh"), py::arg("K_g"), py::arg("V_g"),
         py::arg("seq_lens"), py::arg("S"), py::arg("seed") = 42ULL, py::arg("want_vrows") = false,
-        py::arg("max_len") = -1);
+        py::arg("max_len") = -1, py::kw_only(), py::arg("score_mode") = 0);
+  // the reference's signature (santa_cuda.cpp:354-359) plus one keyword-only extra that defaults to its behaviour
   m.def("decode_systematic_scalar", &decode_systematic_scalar, py::arg("q_h"), py::arg("K_g"), py::arg("V_g"),
-        py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false);
+        py::arg("S"), py::arg("seed") = 42ULL, py::arg("block_n") = 0, py::arg("want_vrows") = false,
+        py::kw_only(), py::arg("score_mode") = 0);
 }

@@ -86,12 +86,15 @@ def _check_flash_inputs(q_h, K_g, V_g):
 
 
 def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_len=-1, *,
-                 batch_offset=0, tile_offset=0, s_per_tile=None, partial=False, trace=False, out=None):
+                 batch_offset=0, tile_offset=0, s_per_tile=None, partial=False, trace=False, out=None,
+                 score_mode=0):
     """S2ANTA-Flash decode.  Returns ``(out, m_star, vrows)``; with ``partial=True``
     the first element is the unnormalised partial ``[B,H,130]`` fp32 instead of
     ``out``; with ``trace=True`` a ``FlashTrace`` is appended.  ``out`` may name the result buffer: a
     contiguous tensor of q's shape and dtype on q's device, or in PINNED HOST memory -- the merge kernel
-    then stores the result straight into the caller's host buffer (no separate device-to-host copy)."""
+    then stores the result straight into the caller's host buffer (no separate device-to-host copy).
+    ``score_mode=1`` forms the scores on the tensor cores (opt-in; sampled counts then differ from the
+    reference's on rare rows), 0 is the reference's fp32 order."""
     batched, B, H, D, L_storage, KVH = _check_flash_inputs(q_h, K_g, V_g)
     if seed < 0:
         raise TypeError("seed must be a non-negative 64-bit integer")
@@ -126,7 +129,8 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
         vrows = torch.empty((B, KVH) if (want_vrows and batched) else ((KVH,) if want_vrows else (0,)),
                             device=dev, dtype=torch.int32)
         ext = capi.FlashExt(batch_offset=int(batch_offset), tile_offset=int(tile_offset),
-                            s_per_tile_override=-1 if s_per_tile is None else int(s_per_tile))
+                            s_per_tile_override=-1 if s_per_tile is None else int(s_per_tile),
+                            score_mode=int(score_mode))
         part = None
         if partial:
             part = torch.empty((B, H, D + 2), **fopt)
@@ -155,7 +159,7 @@ def flash_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, valid_l
 
 
 def flash_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, block_n=0, want_vrows=False, *, max_len=None,
-                        batch_offset=0, trace=False):
+                        batch_offset=0, trace=False, score_mode=0):
     """S2ANTA-Flash decode with per-sequence lengths read from device memory: ``q_bh [B,H,D]``,
     ``K_g/V_g [B,L_storage,KVH,D]``, ``seq_lens`` int32 ``[B]`` (a CPU tensor or list is copied over).
     Sequence ``b`` gets the result of ``flash_decode`` on it alone with ``valid_len=len_b``, the same
@@ -188,7 +192,8 @@ def flash_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, block_n=0, want_vr
         out = torch.empty((B, H, D), device=dev, dtype=q.dtype)
         m_star = torch.empty((B, H), **fopt)
         vrows = torch.empty((B, KVH) if want_vrows else (0,), device=dev, dtype=torch.int32)
-        ext = capi.FlashExt(batch_offset=int(batch_offset), tile_offset=0, s_per_tile_override=-1)
+        ext = capi.FlashExt(batch_offset=int(batch_offset), tile_offset=0, s_per_tile_override=-1,
+                            score_mode=int(score_mode))
         tr = None
         if trace:
             tr = FlashTrace(bn, T_max, -1,
@@ -292,7 +297,7 @@ def _pass1_mode_from_env() -> int:
 
 
 def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace=False, flags=None,
-                pass1_mode=None):
+                pass1_mode=None, score_mode=0):
     """S2ANTA-Prop decode of one sequence: ``q_h [H,D]``, ``K_g/V_g [L,KVH,D]``.
     Returns ``(out [H,D], m_star [H], vrows [KVH] or empty)`` (+ ``PropTrace``)."""
     # messages follow santa_fused_proportional_tile_budgets/santa_cuda.cpp:141-167
@@ -331,7 +336,7 @@ def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace
         out = torch.empty((H, D), device=dev, dtype=q.dtype)
         m_star = torch.empty((H,), device=dev, dtype=torch.float32)
         vrows = torch.empty((KVH,) if want_vrows else (0,), device=dev, dtype=torch.int32)
-        ext = capi.PropExt(pass1_mode=mode, flags=3 if flags is None else int(flags))
+        ext = capi.PropExt(pass1_mode=mode, flags=3 if flags is None else int(flags), score_mode=int(score_mode))
         tr = None
         if trace:
             f32 = dict(device=dev, dtype=torch.float32)
@@ -355,7 +360,7 @@ def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace
 
 
 def prop_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, want_vrows=False, *, max_len=None, trace=False,
-                       flags=None):
+                       flags=None, score_mode=0):
     """S2ANTA-Prop decode of a ragged batch in one launch sequence: ``q_bh [B,H,D]``,
     ``K_g/V_g [B,L_storage,KVH,D]``, ``seq_lens`` int32 ``[B]`` on the device (a CPU tensor or a
     list is copied there).  Sequence ``b`` gets the result of
@@ -395,7 +400,7 @@ def prop_decode_ragged(q_bh, K_g, V_g, seq_lens, S, seed=42, want_vrows=False, *
         out = torch.empty((B, H, D), device=dev, dtype=q.dtype)
         m_star = torch.empty((B, H), device=dev, dtype=torch.float32)
         vrows = torch.empty((B, KVH) if want_vrows else (0,), device=dev, dtype=torch.int32)
-        ext = capi.PropExt(pass1_mode=0, flags=3 if flags is None else int(flags))
+        ext = capi.PropExt(pass1_mode=0, flags=3 if flags is None else int(flags), score_mode=int(score_mode))
         tr = None
         if trace:
             f32 = dict(device=dev, dtype=torch.float32)

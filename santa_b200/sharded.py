@@ -42,10 +42,13 @@ class PeerExchange:
     kernels store their partials straight into them -- no collective call per step.  One object serves
     one (B, H) problem shape on one stream; the ranks must call in lock-step (as with a collective)."""
 
-    def __init__(self, B: int, H: int, device, group=None, device_counted: bool = False):
-        # device_counted: the buffers count the steps themselves, so that the two calls of a step can be
+    def __init__(self, B: int, H: int, device, group=None, device_counted: bool = False, fused: bool = True):
+        # device_counted: the buffers count the steps themselves, so that the call(s) of a step can be
         # captured once in a CUDA graph and replayed (every rank must choose the same mode)
+        # fused: the decode call also does the receiving half (one launch sequence per step); otherwise a
+        # separate wait-and-combine kernel follows
         self.device_counted = bool(device_counted)
+        self.fused = bool(fused)
         self.B, self.H = int(B), int(H)
         self.device = torch.device(device)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -67,10 +70,12 @@ class PeerExchange:
             self.ptrs = [self.buf.data_ptr()]
         self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the buffer's own status word (set by either receiving path when a wait ran out)
+        self._buf_status = self.buf[136:140].view(torch.int32)
 
     def check(self) -> None:
         """Synchronise and raise if a wait ran out (a rank never delivered its partial)."""
-        code = int(self.status.item())
+        code = int(self.status.item()) or int(self._buf_status.item())
         if code != 0:
             raise RuntimeError(f"santa_b200: peer exchange failed with device status {code}")
 
@@ -95,8 +100,10 @@ def seq_sharded_flash_decode(q, K_shard, V_shard, S, seed, L_total, *, block_n=0
             raise RuntimeError("PeerExchange was built for another problem shape or group")
         exchange.epoch += 1
         epoch = 0 if exchange.device_counted else exchange.epoch
-        mod.decode_systematic_exchange(q, K_shard, V_shard, S, seed, bn, row1 - row0, 0, tile0, spt,
-                                       exchange.ptrs, rank, epoch)
+        res = mod.decode_systematic_exchange(q, K_shard, V_shard, S, seed, bn, row1 - row0, 0, tile0, spt,
+                                             exchange.ptrs, rank, epoch, exchange.fused)
+        if exchange.fused:
+            return res
         return mod.lse_combine_wait(exchange.ptrs, rank, epoch, B, H, spt, q.dtype == torch.bfloat16,
                                     exchange.status)
     if row1 > row0:

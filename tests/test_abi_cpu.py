@@ -109,7 +109,11 @@ def test_peer_exchange_layout_and_validation():
     assert lib.santa_peer_exchange_bytes(2, 0) == 0
     for world, BH in ((1, 32), (2, 32), (8, 64), (16, 1024)):
         n = lib.santa_peer_exchange_bytes(world, BH)
-        assert n % 256 == 0 and n >= 256 + 2 * world * BH * 130 * 4 and n < 256 + 2 * world * BH * 130 * 4 + 256
+        # control words, row flags [2][world][BH] int32 (padded to 256 bytes), rows [2][world][BH][130] fp32
+        flags = (2 * world * BH * 4 + 255) // 256 * 256
+        need = 256 + flags + 2 * world * BH * 130 * 4
+        assert n % 256 == 0 and need <= n < need + 256
+    assert lib.santa_peer_exchange_status(4096) == 4096 + 4 * 34 and lib.santa_peer_exchange_status(None) is None
     px = capi.PeerExchange(world=2, rank=0, epoch=1)
     px.peer_buffer[0], px.peer_buffer[1] = 256, 512
     cw = lib.santa_lse_combine_wait
@@ -121,6 +125,11 @@ def test_peer_exchange_layout_and_validation():
     px.rank, px.world = 0, 17
     ext = capi.FlashExt(batch_offset=0, tile_offset=0, s_per_tile_override=-1)
     ext.peer = ctypes.pointer(px)
+    rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 128, 16, 16, 4, 1, 0, None, None, None, None, 0,
+                                ctypes.byref(ext), None)
+    assert rc == -8
+    # the combining form needs somewhere to put the combined result
+    px.world, px.flags = 2, capi.SANTA_PEER_COMBINE
     rc = lib.santa_flash_decode(256, 256, 256, 0, 1, 32, 8, 128, 16, 16, 4, 1, 0, None, None, None, None, 0,
                                 ctypes.byref(ext), None)
     assert rc == -8

@@ -677,6 +677,22 @@ def test_peer_exchange_on_one_device():
     assert status.item() == 0
     steps_done = bufs2[0][4 * 33:4 * 34].view(torch.int32).item()
     assert steps_done == 4
+    # receiving half inside the decode call (SANTA_PEER_COMBINE): the first two 'ranks' only send, the
+    # third finds every row present and returns the combined result -- the same bits as the wait kernel's
+    bufs3 = [torch.zeros(nbytes, dtype=torch.uint8, device=dev()) for _ in range(G)]
+    ptrs3 = [b.data_ptr() for b in bufs3]
+    for epoch in (1, 2):
+        for r, (Ks, Vs, n, t0) in enumerate(shards):
+            res = mod.decode_systematic_exchange(q, Ks, Vs, S, 9, bn, n, 0, t0, spt, ptrs3, r, epoch, r == G - 1)
+        sep = mod.lse_combine_wait(ptrs3, G - 1, epoch, B, H, spt, True, status)
+        assert torch.equal(res[0], sep[0]) and torch.equal(res[1], sep[1])
+        assert close(res[0], full[0]) and bits_eq(res[1], full[1])
+    assert status.item() == 0 and bufs3[G - 1][4 * 34:4 * 35].view(torch.int32).item() == 0
+    # ... and when the others never send, its bounded wait runs out: zeros and status 4, no hang
+    Ks, Vs, n, t0 = shards[0]
+    res = mod.decode_systematic_exchange(q, Ks, Vs, S, 9, bn, n, 0, t0, spt, ptrs3, 0, 3, True)
+    torch.cuda.synchronize()
+    assert (res[0] == 0).all() and bufs3[0][4 * 34:4 * 35].view(torch.int32).item() == 4
     # the one-rank object goes through the same kernels
     ex = sharded.PeerExchange(B, H, dev())
     one = sharded.seq_sharded_flash_decode(q, K[:, :L].contiguous(), V[:, :L].contiguous(), S, 9, L, exchange=ex)

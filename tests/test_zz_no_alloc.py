@@ -3,10 +3,13 @@
 It serves callers that cannot give the library a workspace -- servers that hand all free device memory
 to their KV-cache pool at start-up and forbid allocation while decoding, and C hosts without a device
 allocator -- by keeping its scratch in a fixed array inside the library.  Here it must reproduce the
-regular entry point (same kernels, so the same bits; the assertion uses the suite's output tolerance),
-on two calls in a row because every call reuses the same scratch, and it must refuse problems whose
-scratch need exceeds the fixed array.  This file sorts last so that a failure here cannot hide another
+regular entry point on two calls in a row, because every call reuses the same scratch: within the
+suite's output tolerance, and -- the kernels being the same and deterministic -- in fact bit for bit.
+Its status word, reachable through santa_noalloc_status(), must stay zero, and problems whose scratch
+need exceeds the fixed array must be refused.  This file sorts last so that a failure here cannot hide another
 test's result in a run that stops at the first failure."""
+
+import ctypes
 
 import pytest
 import torch
@@ -15,6 +18,22 @@ import cases
 
 pytestmark = pytest.mark.gpu
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def _read_device_int32(addr):
+    """One int32 at a raw device address (the CUDA runtime's cudaMemcpy, device to host)."""
+    rt = None
+    for name in ("libcudart.so", "libcudart.so.12", "/usr/local/cuda/lib64/libcudart.so"):
+        try:
+            rt = ctypes.CDLL(name)
+            break
+        except OSError:
+            continue
+    if rt is None:
+        pytest.skip("no CUDA runtime library to read the word with")
+    host = (ctypes.c_int32 * 1)()
+    assert rt.cudaMemcpy(host, ctypes.c_void_p(addr), ctypes.c_size_t(4), ctypes.c_int(2)) == 0
+    return int(host[0])
 
 
 def _call_noalloc(lib, q, K, V, S, seed, valid_len, want_vrows=True):
@@ -46,7 +65,12 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
             torch.cuda.synchronize()
             d = (out.float() - ref_out.float()).abs()
             assert d.max().item() <= MAX_ABS and d.mean().item() <= MEAN_ABS
+            assert torch.equal(out, ref_out)            # the same kernels in the same order: the same bits
             assert torch.equal(m_star, ref_m) and torch.equal(vrows, ref_v)
+            # the scratch's status word: reachable once the entry point has run on this device, and zero
+            addr = lib.santa_noalloc_status()
+            assert addr
+            assert _read_device_int32(addr) == 0
 
 
 def test_noalloc_entry_point_rejects_oversized_problems():
