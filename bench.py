@@ -348,6 +348,7 @@ def main():
                     help="skip the end-to-end Llama-3.1-8B-shaped decode extra (needs ~160 GB of HBM)")
     ap.add_argument("--no-ref-kernels", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-b32", action="store_true", help="skip the B=32 variant of the headline workload")
+    ap.add_argument("--no-tensor-mode", action="store_true", help="skip the opt-in tensor-core score mode extras")
     ap.add_argument("--e2e-model-batch", type=int, default=32)
     ap.add_argument("--e2e-prefill", action="store_true",
                     help="run the real 512-token-chunk prefill of the end-to-end extra instead of a synthetic cache")
@@ -497,6 +498,33 @@ def main():
         elif rank == 0 and "vs_reference_cuda_kernels" not in line:
             line["vs_reference_cuda_kernels"] = {"flash": {"unavailable": "oracle/_ref is not built"}}
 
+    # ---- extra: the opt-in tensor-core score mode on the same workload, beside the exact mode -------
+    if not args.no_tensor_mode:
+        tt = timed_blocks(lambda i: ops.flash_decode(qpool[i % QPOOL], K, V, S, seed=SEED, batch_offset=rank * B,
+                                                     out=out_dev, score_mode=1), steps, 3, world, dev, min_s=0.5)
+        r0 = ops.flash_decode(qpool[0], K, V, S, seed=SEED, batch_offset=rank * B, want_vrows=True, trace=True)
+        r1 = ops.flash_decode(qpool[0], K, V, S, seed=SEED, batch_offset=rank * B, want_vrows=True, trace=True,
+                              score_mode=1)
+        c0, c1 = r0[3].counts, r1[3].counts
+        sampled, differing = int((c0 > 0).sum().item()), int((c0 != c1).sum().item())
+        dd = (r0[0].float() - r1[0].float()).abs()
+        if rank == 0:
+            peak, _ = measured_peak_gbs()
+            bt = alg_bytes - vrows_total * D * 2 + int(r1[2].sum().item()) * D * 2
+            line["score_mode_tensor"] = {
+                "what": "scores on the tensor cores (mma.sync, split 16-bit query), opt-in; everything else unchanged. "
+                        "The exact mode's counts equal the reference's bit for bit, so the mismatch below is the "
+                        "distance from the reference",
+                "ms_per_step": tt["ms_per_step"], "exact_ms_per_step": tm["ms_per_step"],
+                "sampled_kv_gbs_per_gpu": bt / (tt["ms_per_step"] * 1e-3) / 1e9,
+                "frac_of_measured_hbm_peak": bt / (tt["ms_per_step"] * 1e-3) / 1e9 / peak,
+                "pct_of_8tbs": bt / (tt["ms_per_step"] * 1e-3) / 1e9 / 80.0,
+                "count_entries_differing": differing, "count_entries_sampled": sampled,
+                "mismatch_rate": differing / max(1, sampled),
+                "out_vs_exact_max_abs": dd.max().item(), "out_vs_exact_mean_abs": dd.mean().item(),
+                "repeats": tt["repeats"]}
+        del r0, r1, c0, c1
+
     # ---- extra: the same workload at B=32 (the fixed per-call cost amortised over 4x the tiles) --
     if not args.no_b32:
         del K, V, qpool
@@ -506,6 +534,10 @@ def main():
         o32 = torch.empty(32, H, D, device=dev, dtype=torch.bfloat16)
         t32 = timed_blocks(lambda i: ops.flash_decode(qp32[i % QPOOL], K32, V32, S, seed=SEED, out=o32),
                            max(5, steps // 4), 3, world, dev, min_s=0.5)
+        t32t = None
+        if not args.no_tensor_mode:
+            t32t = timed_blocks(lambda i: ops.flash_decode(qp32[i % QPOOL], K32, V32, S, seed=SEED, out=o32,
+                                                           score_mode=1), max(5, steps // 4), 3, world, dev, min_s=0.5)
         if rank == 0:
             b32 = 32 * L * KVH * D * 2 + vr32 * D * 2 + 2 * 32 * H * D * 2 + 32 * H * 4
             peak, _ = measured_peak_gbs()
@@ -513,6 +545,12 @@ def main():
                                  "sampled_kv_gbs_per_gpu": b32 / (t32["ms_per_step"] * 1e-3) / 1e9,
                                  "frac_of_measured_hbm_peak": b32 / (t32["ms_per_step"] * 1e-3) / 1e9 / peak,
                                  "repeats": t32["repeats"]}
+            if t32t is not None:
+                line["flash_b32"]["tensor_score_mode"] = {
+                    "ms_per_step": t32t["ms_per_step"],
+                    "sampled_kv_gbs_per_gpu": b32 / (t32t["ms_per_step"] * 1e-3) / 1e9,
+                    "frac_of_measured_hbm_peak": b32 / (t32t["ms_per_step"] * 1e-3) / 1e9 / peak,
+                    "pct_of_8tbs": b32 / (t32t["ms_per_step"] * 1e-3) / 1e9 / 80.0}
         del K32, V32, qp32
         torch.cuda.empty_cache()
     else:
@@ -721,6 +759,10 @@ def prop_extra(dev, rank, world, steps, args):
               .sum().item())
     t2r = timed_blocks(lambda i: prop_mod.decode_systematic_ragged(qr[i % QPOOL], Kr, Vr, lens_dev, S, seed=SEED),
                        n2, 3, world, dev, min_s=0.4)
+    t2rt = None
+    if not args.no_tensor_mode:
+        t2rt = timed_blocks(lambda i: prop_mod.decode_systematic_ragged(qr[i % QPOOL], Kr, Vr, lens_dev, S, seed=SEED,
+                                                                         score_mode=1), n2, 3, world, dev, min_s=0.4)
     res = None
     if rank == 0:
         fixed = 16 * (2 * H * D * 2 + H * 4)
@@ -732,7 +774,9 @@ def prop_extra(dev, rank, world, steps, args):
                 "what": "one decode_systematic_ragged call per step (4 kernels), lengths in device memory",
                 "steps_per_s": world / (t2r["ms_per_step"] * 1e-3), "ms_per_step": t2r["ms_per_step"],
                 "sampled_kv_gbs_per_gpu": pbr / (t2r["ms_per_step"] * 1e-3) / 1e9, "algorithmic_bytes_per_step": pbr,
-                "repeats": t2r["repeats"]},
+                "repeats": t2r["repeats"],
+                "tensor_score_mode_ms_per_step": t2rt["ms_per_step"] if t2rt else None,
+                "tensor_score_mode_gbs": (pbr / (t2rt["ms_per_step"] * 1e-3) / 1e9) if t2rt else None},
             "per_sequence_loop": {
                 "what": "16 decode_systematic_scalar calls per step (the reference adapter's loop, 4 kernels each)",
                 "steps_per_s": world / (t2["ms_per_step"] * 1e-3), "ms_per_step": t2["ms_per_step"],

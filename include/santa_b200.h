@@ -38,7 +38,7 @@ extern "C" {
 
 #define SANTA_OK 0
 #define SANTA_E_DTYPE (-1)      /* dtype is not SANTA_DTYPE_BF16 / SANTA_DTYPE_F16 */
-#define SANTA_E_SHAPE (-2)      /* unsupported H/KVH/D combination */
+#define SANTA_E_SHAPE (-2)      /* unsupported H/KVH/D combination (see each entry point) */
 #define SANTA_E_LENGTH (-3)     /* valid length <= 0 or > storage length */
 #define SANTA_E_BLOCK_N (-4)    /* block_n not supported by this entry point */
 #define SANTA_E_WORKSPACE (-5)  /* workspace NULL, misaligned or too small */
@@ -166,8 +166,11 @@ SANTA_API int santa_flash_decode(const void* q, const void* K, const void* V, in
                        float* m_star, int32_t* vrows, void* workspace, size_t workspace_bytes,
                        const santa_flash_ext* ext, void* stream);
 
-/* Device address of the int32 status word inside a workspace (0 = ok; 1 = a staged K piece never
- * arrived, 2 = a score buffer was never handed over: the result is invalid).  Read it after synchronising the stream. */
+/* Device address of the int32 status word inside a workspace.  0 = ok; 1 = a staged K piece never
+ * arrived, 2 = a score buffer was never handed over (the result is invalid); 3 = santa_rope_append
+ * skipped a position outside the cache; 4 = a rank's rows never arrived in a peer exchange; 5 = the
+ * bounds-checked build of the library (-DSANTA_B200_CHECKS) caught an index outside its array and
+ * skipped the access.  The word is sticky.  Read it after synchronising the stream. */
 SANTA_API int32_t* santa_workspace_status(void* workspace);
 
 /*
@@ -278,8 +281,12 @@ SANTA_API size_t santa_prop_workspace_bytes(int H, int KVH, int D, int L, int bl
  *   out    [H,D]       storage dtype
  *   m_star [H]         fp32
  *   vrows  [KVH] int32 or NULL
- * Requires D == 128, H == 4*KVH, block_n <= 0 (auto) or a multiple of 16 up to 256, and at most
- * 11 622 tiles per sequence (2.9 M tokens at 256-row tiles; SANTA_E_TOO_LARGE beyond).
+ * Shapes: any H % KVH == 0 with up to 8 query heads per kv-head and any D % 16 == 0 up to 256, like
+ * the reference (P.cpp:212-247; its second pass launches 128 x GH threads, P.cu:924-927, hence the 8).
+ * H == 4*KVH with D == 128 runs the vectorised kernels (streaming first pass when block_n == 256),
+ * every other shape the tensor-core first pass and a generic second pass, both with the reference's
+ * arithmetic.  block_n <= 0 (auto) or a multiple of 16 up to 256; at most 11 622 tiles per sequence
+ * (2.9 M tokens at 256-row tiles; SANTA_E_TOO_LARGE beyond).
  * The output is summed in a fixed order, so repeated calls give identical bits (the reference
  * accumulates with atomics and does not).  Workspace rules as for santa_flash_decode.
  */

@@ -185,12 +185,11 @@ def prop_counts(q, K, S, seed=42, block_n=0):
     sfx = "bf16" if q.dtype == torch.bfloat16 else "f16"
     stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
     counts = torch.zeros(H, L, device=q.device, dtype=torch.int32)
-    assert D == 128
     p2 = getattr(lib, f"launch_pass2_grouped_fused_atomic_{sfx}")
     for t in range(T_c):
         n0, n1 = t * bn, min(L, (t + 1) * bn)
-        for half in range((n1 - n0 + 127) // 128):
-            a, b = n0 + 128 * half, min(n1, n0 + 128 * (half + 1))
+        for half in range((n1 - n0 + D - 1) // D):          # D rows at a time: one output dim per row
+            a, b = n0 + D * half, min(n1, n0 + D * (half + 1))
             Vp = torch.zeros(L, KVH, D, device=q.device, dtype=q.dtype)
             idx = torch.arange(a, b, device=q.device)
             Vp[idx, :, idx - a] = 1.0

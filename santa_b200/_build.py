@@ -50,17 +50,27 @@ def _headers():
     return hs
 
 
-def build_library(verbose: bool = False, force: bool = False) -> str:
+CHECKS_LIB_PATH = os.path.join(LIBDIR, "libsanta_b200_checks.so")
+
+
+def build_library(verbose: bool = False, force: bool = False, checks: bool = False) -> str:
+    """Compile the C-ABI library.  ``checks=True`` builds ``libsanta_b200_checks.so`` instead: the same
+    sources with -DSANTA_B200_CHECKS, every data-dependent index compared with its array's extent and
+    violations reported through the status word (select it with the SANTA_B200_LIB environment
+    variable; see santa_b200/capi.py)."""
     os.makedirs(OBJDIR, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
     hdrs = _headers()
     objs = []
     procs = []
+    lib_path = CHECKS_LIB_PATH if checks else LIB_PATH
     for unit, extra in UNITS.items():
         src = os.path.join(CSRC, unit)
         if not os.path.exists(src):
             continue
-        obj = os.path.join(OBJDIR, unit.replace(".cu", ".o"))
+        if checks:
+            extra = extra + ["-DSANTA_B200_CHECKS"]
+        obj = os.path.join(OBJDIR, unit.replace(".cu", ".checks.o" if checks else ".o"))
         objs.append(obj)
         if not force and _newer(obj, [src] + hdrs):
             continue
@@ -72,10 +82,10 @@ def build_library(verbose: bool = False, force: bool = False) -> str:
             sys.stderr.write(out)
         if pr.returncode != 0:
             raise RuntimeError(f"nvcc failed on {unit}")
-    if force or procs or not _newer(LIB_PATH, objs):
-        cmd = [nvcc] + ARCH + ["-shared", "-o", LIB_PATH] + objs
+    if force or procs or not _newer(lib_path, objs):
+        cmd = [nvcc] + ARCH + ["-shared", "-o", lib_path] + objs
         subprocess.check_call(cmd)
-    return LIB_PATH
+    return lib_path
 
 
 EXT_MODULES = {
@@ -120,4 +130,7 @@ def build_all(verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv)
+    if "--checks" in sys.argv:
+        print(build_library(verbose="-v" in sys.argv, checks=True))
+    else:
+        build_all(verbose="-v" in sys.argv)

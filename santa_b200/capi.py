@@ -10,7 +10,9 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libsanta_b200.so")
+# SANTA_B200_LIB selects another build of the same library, e.g. the bounds-checked one
+# (`python -m santa_b200._build --checks` -> lib/libsanta_b200_checks.so)
+LIB_PATH = os.environ.get("SANTA_B200_LIB") or os.path.join(_PKG, "lib", "libsanta_b200.so")
 
 SANTA_DTYPE_BF16 = 0
 SANTA_DTYPE_F16 = 1

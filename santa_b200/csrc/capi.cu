@@ -117,7 +117,7 @@ santa::WorkSplit make_split(int ncol, int T_c, int sms, int* grid, int within = 
 struct FlashPlan {
   int block_n, T_c, grid;
   santa::WorkSplit ws;
-  size_t off_pvrows, off_partials, total;
+  size_t off_pvrows, off_partials, total, slots;
 };
 
 int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
@@ -133,6 +133,7 @@ int plan_flash(int B, int KVH, int L_valid, int block_n, FlashPlan* pl) {
   pl->ws = make_split(B * KVH, pl->T_c, sms, &pl->grid);
   const size_t ncg = (size_t(B) * KVH + pl->ws.gw - 1) / pl->ws.gw;
   const size_t slots = (size_t(pl->ws.nvg) + ncg) * pl->ws.gw;
+  pl->slots = slots;
   pl->off_pvrows = 256;
   pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
   pl->total = pl->off_partials + slots * santa::kGH * santa::kPartialStride * sizeof(float);
@@ -146,19 +147,23 @@ struct PropPlan {
 };
 
 int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPlan* pl) {
-  if (KVH <= 0 || D != santa::kD || H != santa::kGH * KVH) return SANTA_E_SHAPE;
+  // the reference takes any H % KVH == 0 and D % 16 == 0 (P.cpp:155-166, :212-247); its second pass
+  // launches 128 x GH threads per block (P.cu:924-927), which bounds GH by 8
+  if (KVH <= 0 || H <= 0 || H % KVH != 0 || H / KVH > 8 || D <= 0 || D % 16 != 0 || D > 256) return SANTA_E_SHAPE;
   if (L <= 0) return SANTA_E_LENGTH;
+  const int GH = H / KVH;
+  const bool vec_shape = GH == santa::kGH && D == santa::kD;
   int bn = block_n;
   if (bn <= 0) bn = (pass1_mode == 2) ? 256 : santa_block_n_rule(L, 0);  // P.cpp:69-77
   if (bn % 16 != 0 || bn > 256) return SANTA_E_BLOCK_N;
-  if (pass1_mode == 2 && bn != 256) return SANTA_E_BLOCK_N;
+  if (pass1_mode == 2 && (bn != 256 || !vec_shape)) return SANTA_E_BLOCK_N;  // P.cpp:230-234
   int sms = 0;
   if (int rc = sm_count_of_current_device(&sms)) return rc;
   if (sms > santa::kMaxCtas) sms = santa::kMaxCtas;
   pl->block_n = bn;
   pl->T_c = (L + bn - 1) / bn;
   if (size_t(pl->T_c) * 20 > size_t(227) * 1024) return SANTA_E_TOO_LARGE;  // budget tables live in shared memory
-  pl->use_vec = (bn == 256 && pass1_mode != 1) ? 1 : 0;  // P.cpp:215-229
+  pl->use_vec = (vec_shape && bn == 256 && pass1_mode != 1) ? 1 : 0;  // P.cpp:215-229
   pl->ws = make_split(KVH, pl->T_c, sms, &pl->grid);
   const size_t ht = align_up(size_t(H) * pl->T_c * 4, 256);
   pl->off_m = 256;
@@ -168,9 +173,15 @@ int plan_prop(int H, int KVH, int D, int L, int block_n, int pass1_mode, PropPla
   pl->off_a0 = pl->off_inv + ht;
   pl->off_stash = pl->off_a0 + ht;
   pl->off_pvrows = pl->off_stash + align_up(size_t(H) * L * 2, 256);
-  const size_t slots = size_t(santa::prop_pass2_max_groups(sms)) + KVH;
-  pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
-  pl->total = pl->off_partials + slots * santa::kGH * santa::kD * sizeof(float);
+  if (vec_shape) {
+    const size_t slots = size_t(santa::prop_pass2_max_groups(sms)) + KVH;
+    pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
+    pl->total = pl->off_partials + slots * santa::kGH * santa::kD * sizeof(float);
+  } else {  // one partial per (kv-head, tile): [KVH][T_c][GH][D]
+    const size_t tiles = size_t(KVH) * pl->T_c;
+    pl->off_partials = pl->off_pvrows + align_up(tiles * 4, 256);
+    pl->total = pl->off_partials + tiles * GH * D * sizeof(float);
+  }
   return SANTA_OK;
 }
 
@@ -190,6 +201,7 @@ int plan_flash_ragged(int B, int KVH, int max_len, int block_n, FlashPlan* pl) {
   pl->ws = make_split(B * KVH, pl->T_c, sms, &pl->grid, KVH);
   const size_t ncg = size_t(B) * (KVH / pl->ws.gw);
   const size_t slots = (size_t(pl->ws.nvg) + ncg) * pl->ws.gw;
+  pl->slots = slots;
   pl->off_pvrows = 256;
   pl->off_partials = pl->off_pvrows + align_up(slots * 4, 256);
   pl->total = pl->off_partials + slots * santa::kGH * santa::kPartialStride * sizeof(float);
@@ -238,7 +250,9 @@ const char* santa_strerror(int code) {
   switch (code) {
     case SANTA_OK: return "ok";
     case SANTA_E_DTYPE: return "dtype must be bf16 or f16";
-    case SANTA_E_SHAPE: return "unsupported shape: this build supports only D=128 and GH=4 (H/KVH)";
+    case SANTA_E_SHAPE:
+      return "unsupported shape: Flash and the ragged calls take D=128 and H/KVH=4; santa_prop_decode takes "
+             "H%KVH==0 with H/KVH<=8 and D a multiple of 16 up to 256";
     case SANTA_E_LENGTH: return "valid_len must be > 0 and must not exceed the storage length";
     case SANTA_E_BLOCK_N: return "block_n must be 0 (auto) or one of {32,64,256}";
     case SANTA_E_WORKSPACE: return "workspace is NULL, not 256-byte aligned, or too small";
@@ -346,6 +360,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   p.status = reinterpret_cast<int*>(ws);
   p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
   p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.partial_slots = (long long)pl.slots;
   p.m_tiles = ext ? ext->m_tiles : nullptr;
   p.ell_tiles = ext ? ext->ell_tiles : nullptr;
   p.stash = nullptr;
@@ -361,6 +376,7 @@ int santa_flash_decode(const void* q, const void* K, const void* V, int dtype, i
   mp.ws = pl.ws;
   mp.partials = p.partials;
   mp.partial_vrows = p.partial_vrows;
+  mp.partial_slots = p.partial_slots;
   mp.out = out;
   mp.m_star = m_star;
   mp.vrows = vrows;
@@ -431,6 +447,7 @@ int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int d
   p.status = reinterpret_cast<int*>(ws);
   p.partial_vrows = reinterpret_cast<int*>(ws + pl.off_pvrows);
   p.partials = reinterpret_cast<float*>(ws + pl.off_partials);
+  p.partial_slots = (long long)pl.slots;
   p.m_tiles = ext ? ext->m_tiles : nullptr;
   p.ell_tiles = ext ? ext->ell_tiles : nullptr;
   p.stash = nullptr;
@@ -451,6 +468,7 @@ int santa_flash_decode_ragged(const void* q, const void* K, const void* V, int d
   mp.ws = pl.ws;
   mp.partials = p.partials;
   mp.partial_vrows = p.partial_vrows;
+  mp.partial_slots = p.partial_slots;
   mp.out = out;
   mp.m_star = m_star;
   mp.vrows = vrows;
@@ -501,6 +519,7 @@ int santa_prop_decode(const void* q, const void* K, const void* V, int dtype, in
   sp.stash = reinterpret_cast<uint16_t*>(ws + pl.off_stash);
   sp.dbg_u = ext ? ext->u16 : nullptr;
   p.K = K;
+  p.D = D;
   p.block_n = pl.block_n;
   p.T_c = pl.T_c;
   p.use_vec = pl.use_vec;
@@ -567,6 +586,7 @@ int santa_prop_decode_ragged(const void* q, const void* K, const void* V, int dt
   sp.stash = reinterpret_cast<uint16_t*>(ws + pl.off_stash);
   sp.dbg_u = ext ? ext->u16 : nullptr;
   p.K = K;
+  p.D = D;
   p.block_n = 256;
   p.T_c = pl.T_max;
   p.use_vec = 1;

@@ -36,7 +36,24 @@ enum : int {
   kStatusHandoffTimeout = 2,  // a score buffer was never handed over between the warps of a column
   kStatusBadPosition = 3,     // an append position outside the cache was skipped
   kStatusPeerTimeout = 4,     // a rank's partial never arrived in the exchange buffer
+  kStatusBadIndex = 5,        // checked build only: an index left its array; the access was skipped
 };
+
+// Checked build (-DSANTA_B200_CHECKS, `python -m santa_b200._build --checks`): every index that
+// depends on data or on the work split is compared with the extent of its array before the access.
+// A failed check writes kStatusBadIndex to the status word and the access is skipped -- nothing
+// traps, the context stays usable, and the host reads the word as after any call.  In the normal
+// build the macro is the constant `true` and the checks cost nothing.  (Stands in for a memory
+// checker where none can be run; same idea as the reference's SANTA_DEBUG asserts,
+// santa_fused_proportional_tile_budgets/santa_cuda_kernel.cu:24-38, without the trap.)
+#ifdef SANTA_B200_CHECKS
+#define SANTA_IN_RANGE(idx, extent, status_ptr)                                         \
+  (((unsigned long long)(idx) < (unsigned long long)(extent))                           \
+       ? true                                                                           \
+       : (((status_ptr) != nullptr ? (void)atomicExch((status_ptr), kStatusBadIndex) : (void)0), false))
+#else
+#define SANTA_IN_RANGE(idx, extent, status_ptr) (true)
+#endif
 
 // ---------------------------------------------------------------- RNG
 // splitmix64 finaliser over seed ^ (h << 32 ^ t); top 53 bits -> [0,1] double
@@ -211,11 +228,19 @@ __device__ __forceinline__ void combine_rows(const float* rows, size_t stride, i
 
 // Bounded wait of lanes 0..world-1 on one int32 word each (lane r: `word_of_lane`) until it holds
 // `want` or -- counters -- has passed it; system-scope acquire loads, sleeping between polls.
-// Returns true on every lane when all arrived within the limit (about a second).
+// The bound is one second of the GPU's nanosecond timer (and a poll count, should the timer stand
+// still).  Returns true on every lane when all arrived within the bound.
+constexpr unsigned long long kPeerWaitNs = 1000000000ull;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool peer_wait(const int* word_of_lane, bool polls, unsigned want, bool counter) {
   bool ok = true;
   if (polls) {
     ok = false;
+    const unsigned long long t0 = global_timer_ns();
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
       int v;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(word_of_lane) : "memory");
@@ -223,6 +248,7 @@ __device__ __forceinline__ bool peer_wait(const int* word_of_lane, bool polls, u
         ok = true;
         break;
       }
+      if ((spin & 63u) == 63u && global_timer_ns() - t0 > kPeerWaitNs) break;
       __nanosleep(200);
     }
   }

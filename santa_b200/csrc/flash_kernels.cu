@@ -94,7 +94,9 @@ __global__ void __launch_bounds__(kFlashMergeWarps * 32) flash_merge_kernel(cons
     v_first = cta_of_item(item0, items, nvg);
     v_last = cta_of_item(item0 + T_c - 1, items, nvg);
   }
-  const int nv = v_last - v_first + 1;
+  int nv = v_last - v_first + 1;
+  if (nv > 0 && !SANTA_IN_RANGE(size_t(v_last + cg) * gw + w, p.partial_slots, p.status)) nv = 0;
+  if (!SANTA_IN_RANGE(nv, kMaxCtas * kGroupWarps + 1, p.status)) nv = 0;  // the weights live in shared memory
   auto partial = [&](int v) {
     return p.partials + ((size_t(v + cg) * gw + w) * kGH + g) * kPartialStride;
   };
@@ -215,9 +217,11 @@ __global__ void __launch_bounds__(kFlashMergeWarps * 32) flash_merge_kernel(cons
       __syncwarp();
       if (lane < p.px.world) {
         __threadfence_system();
-        int* flag = reinterpret_cast<int*>(p.px.base[lane] + peer_row_flag_offset(parity, p.px.world, p.px.rank, BH)) + bh;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(int(epoch)) : "memory");
-        atomicAdd_system(reinterpret_cast<int*>(p.px.base[lane]) + parity * kMaxPeers + p.px.rank, 1);
+        volatile int* flag =
+            reinterpret_cast<volatile int*>(p.px.base[lane] + peer_row_flag_offset(parity, p.px.world, p.px.rank, BH)) + bh;
+        *flag = int(epoch);  // read by the combining form of this call on the receiving rank
+        if (!p.px.combine)   // counted by the separate wait-and-combine kernel
+          atomicAdd_system(reinterpret_cast<int*>(p.px.base[lane]) + parity * kMaxPeers + p.px.rank, 1);
       }
       if (p.px.combine) {
         // the receiving half for this row, without a second kernel: wait (bounded) until every rank's

@@ -31,15 +31,16 @@
 namespace santa {
 
 // ------------------------------------------------------------------ pass 1, tensor-core path
-// One CTA per (tile, kv-head), one warp per 16 K rows.  The scores are formed
-// exactly like the reference's 16x16x16 WMMA steps (q*scale rounded to the
-// storage type, fp32 accumulation over 16-wide k steps in ascending order); a
-// 16x16x16 WMMA step is two m16n8k16 MMAs on the two 8-column halves.  Tile
-// statistics follow santa_cuda_kernel.cu:190-265: per warp and head a
-// sequential 16-term sum of u, warps added in ascending order.
+// One CTA per (tile, kv-head), one warp per 16 K rows; GH <= 8 query heads per kv-head, any head
+// dimension D that is a multiple of 16.  The scores are formed exactly like the reference's
+// 16x16x16 WMMA steps (santa_cuda_kernel.cu:126-188: q*scale rounded to the storage type, fp32
+// accumulation over 16-wide k steps in ascending order); a 16x16x16 WMMA step is two m16n8k16 MMAs
+// on the two 8-column halves, with the heads in the first GH of the 16 rows.  Tile statistics
+// follow santa_cuda_kernel.cu:190-265: per warp and head a sequential 16-term sum of u, warps
+// added in ascending order.  The stash is [kv-head][row][GH] 16-bit.
 template <typename TK>
-__global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __restrict__ K, int H, int KVH, int L,
-                                      int bn, int T_c, float q_scale, float* __restrict__ m_tiles,
+__global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __restrict__ K, int H, int KVH, int GH,
+                                      int D, int L, int bn, int T_c, float q_scale, float* __restrict__ m_tiles,
                                       float* __restrict__ ell_tiles, uint16_t* __restrict__ stash,
                                       uint16_t* __restrict__ dbg_u) {
   extern __shared__ float smf[];
@@ -54,10 +55,10 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
 
   const int r0 = lane >> 2, c0 = 2 * (lane & 3);
   float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  for (int k0 = 0; k0 < kD; k0 += 16) {
+  for (int k0 = 0; k0 < D; k0 += 16) {
     uint32_t a[4] = {0u, 0u, 0u, 0u};
-    if (r0 < kGH) {  // rows r0+8 are padding (GH == 4)
-      const TK* qp = Q + (size_t(kv) * kGH + r0) * kD + k0 + c0;
+    if (r0 < GH) {  // rows GH..15 are padding (GH <= 8: the rows r0+8 are never used)
+      const TK* qp = Q + (size_t(kv) * GH + r0) * D + k0 + c0;
       const float2 lo = Store16<TK>::unpack(*reinterpret_cast<const uint32_t*>(qp));
       const float2 hi = Store16<TK>::unpack(*reinterpret_cast<const uint32_t*>(qp + 8));
       a[0] = uint32_t(Store16<TK>::bits(lo.x * q_scale)) | (uint32_t(Store16<TK>::bits(lo.y * q_scale)) << 16);
@@ -68,7 +69,7 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
       const int n = n0 + 16 * w + 8 * nb + r0;
       uint32_t b[2] = {0u, 0u};
       if (n < L) {
-        const TK* kp = K + (size_t(n) * KVH + kv) * kD + k0 + c0;
+        const TK* kp = K + (size_t(n) * KVH + kv) * D + k0 + c0;
         b[0] = *reinterpret_cast<const uint32_t*>(kp);
         b[1] = *reinterpret_cast<const uint32_t*>(kp + 8);
       }
@@ -85,7 +86,7 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
   __syncthreads();
   if (lane < 16) {
     float mp = -CUDART_INF_F;
-    if (lane < kGH)
+    if (lane < GH)
       for (int j = 0; j < 16; ++j)
         if (n0 + 16 * w + j < L) mp = fmaxf(mp, Ct[lane * 16 + j]);
     rowMax[lane * NWARP + w] = mp;
@@ -94,21 +95,21 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
   if (w == 0 && lane < 16) {
     float mv = -CUDART_INF_F;
     for (int ww = 0; ww < NWARP; ++ww) mv = fmaxf(mv, rowMax[lane * NWARP + ww]);
-    mRow[lane] = (lane < kGH) ? mv : -CUDART_INF_F;
+    mRow[lane] = (lane < GH) ? mv : -CUDART_INF_F;
   }
   __syncthreads();
   if (lane < 16) {
     float ep = 0.f;
-    if (lane < kGH) {
+    if (lane < GH) {
       const float mr = mRow[lane];
-      const int h = kv * kGH + lane;
+      const int h = kv * GH + lane;
       for (int j = 0; j < 16; ++j) {
         const int n = n0 + 16 * w + j;
         if (n < L) {
           const float u = __expf(Ct[lane * 16 + j] - mr);
           ep = __fadd_rn(ep, u);
           const uint16_t ub = Store16<TK>::bits(u);
-          stash[(size_t(kv) * L + n) * kGH + lane] = ub;  // [kv][row][head of the group]
+          stash[(size_t(kv) * L + n) * GH + lane] = ub;  // [kv][row][head of the group]
           if (dbg_u != nullptr) dbg_u[size_t(h) * L + n] = ub;
         }
       }
@@ -116,10 +117,10 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
     rowEll[lane * NWARP + w] = ep;
   }
   __syncthreads();
-  if (w == 0 && lane < kGH) {
+  if (w == 0 && lane < GH) {
     float e = 0.f;
     for (int ww = 0; ww < NWARP; ++ww) e = __fadd_rn(e, rowEll[lane * NWARP + ww]);
-    const int h = kv * kGH + lane;
+    const int h = kv * GH + lane;
     m_tiles[size_t(h) * T_c + t] = mRow[lane];
     ell_tiles[size_t(h) * T_c + t] = e;
   }
@@ -278,6 +279,8 @@ struct Pass2Params {
   WorkSplit ws;             // gw == 1: one column (sequence, kv-head) per warp
   float* partials;          // [nvg + columns][4][128]
   int* partial_vrows;       // [nvg + columns]
+  long long partial_slots;  // nvg + columns (the checked build compares slots with it)
+  int* status;              // the call's status word
   int16_t* dbg_c;           // [nseq,H,len_stride] or null
   int* rowmask;             // [nseq,KVH,len_stride] or null
 };
@@ -367,7 +370,7 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
 #pragma unroll
       for (int ch = 0; ch < kMaxTileRows / kChunkRows; ++ch) {
         const int r = ch * kChunkRows + lane;
-        if (r < tile_len) cp_async8(raw + r, stash_col + n0 + r);
+        if (r < tile_len && SANTA_IN_RANGE(n0 + r, p.len_stride, p.status)) cp_async8(raw + r, stash_col + n0 + r);
       }
       if (lane < 2 * kGH) {
         const float* src = (lane < kGH ? p.invdelta : p.a0) + (bh0 + (lane & (kGH - 1))) * p.tile_stride + t;
@@ -403,18 +406,29 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
       if (t + 1 < t_hi) fetch(t + 1);
       if (empty) continue;
       RowTrace tr;
+      tr.status = p.status;
+      tr.rows_left = p.L_storage - n0;
       tr.head_stride = ls;
       tr.u16 = nullptr;
       tr.counts = p.dbg_c ? p.dbg_c + bh0 * ls + n0 : nullptr;
       tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * ls + n0 : nullptr;
-      const int n_emit = tile_counts<TK, true, kPass2TwoChunks>(sb, tile_len, lane, invdel, a0, tr);
+      // heads of this tile without a budget sample nothing: only the others are scanned
+      const uint32_t active = (invdel[0] > 0.f ? 1u : 0u) | (invdel[1] > 0.f ? 2u : 0u) | (invdel[2] > 0.f ? 4u : 0u) |
+                              (invdel[3] > 0.f ? 8u : 0u);
+      int n_emit;
+      switch (__popc(active)) {
+        case 1: n_emit = tile_counts_some<TK, true, kPass2TwoChunks, 1>(sb, tile_len, lane, invdel, a0, tr, active); break;
+        case 2: n_emit = tile_counts_some<TK, true, kPass2TwoChunks, 2>(sb, tile_len, lane, invdel, a0, tr, active); break;
+        case 3: n_emit = tile_counts_some<TK, true, kPass2TwoChunks, 3>(sb, tile_len, lane, invdel, a0, tr, active); break;
+        default: n_emit = tile_counts<TK, true, kPass2TwoChunks>(sb, tile_len, lane, invdel, a0, tr); break;
+      }
       vrow_count += n_emit;
       float o[kGH][4];
 #pragma unroll
       for (int g = 0; g < kGH; ++g)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
-      gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o);
+      gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o, p.status, tr.rows_left);
       if (n_emit > 0) {
 #pragma unroll
         for (int g = 0; g < kGH; ++g)
@@ -424,10 +438,12 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
     }
     const size_t pslot = size_t(vg) + size_t(b) * p.KVH + kv;
     float* ps = p.partials + pslot * (kGH * kD);
+    if (SANTA_IN_RANGE(pslot, p.partial_slots, p.status)) {
 #pragma unroll
-    for (int g = 0; g < kGH; ++g)
-      reinterpret_cast<float4*>(ps + g * kD)[lane] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-    if (lane == 0) p.partial_vrows[pslot] = vrow_count;
+      for (int g = 0; g < kGH; ++g)
+        reinterpret_cast<float4*>(ps + g * kD)[lane] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      if (lane == 0) p.partial_vrows[pslot] = vrow_count;
+    }
     it += (t_hi - t_lo);
   }
 }
@@ -540,6 +556,143 @@ __global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const Prop
   }
 }
 
+// ------------------------------------------------------------------ pass 2 and merge for any GH <= 8, D % 16 == 0
+// The shapes the vectorised kernels above do not cover (they are written for GH == 4, D == 128) go
+// through these two: the arithmetic of the reference's pass2_grouped_tile_fused_atomic_kernel_x
+// (santa_cuda_kernel.cu:734-864) with one warp per query head of the group, and a merge that adds
+// the tiles in ascending order instead of the reference's atomics (deterministic).
+struct Pass2GenericParams {
+  const void* V;          // [L,KVH,D]
+  const uint16_t* stash;  // [KVH][L][GH]
+  const float* invdelta;  // [H,T_c]
+  const float* a0;        // [H,T_c]
+  const int* S_tiles;     // [H,T_c]
+  int H, KVH, GH, D, L, bn, T_c;
+  float* partials;        // [KVH][T_c][GH][D]
+  int* partial_vrows;     // [KVH][T_c]
+  int16_t* dbg_c;         // [H,L] or null
+  int* rowmask;           // [KVH,L] or null
+  int* status;            // the call's status word
+};
+
+template <typename TK>
+__global__ void prop_pass2_generic_kernel(const Pass2GenericParams p) {
+  cudaGridDependencySynchronize();
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  int16_t* c_tile = reinterpret_cast<int16_t*>(s_dyn);                       // [GH][bn]
+  int* emit = reinterpret_cast<int*>(s_dyn + size_t(p.GH) * p.bn * 2);      // [bn]
+  __shared__ int s_emit_len;
+  const int kv = blockIdx.x, t = blockIdx.y;
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;  // one warp per head of the group
+  const int h = kv * p.GH + g;
+  const int n0 = t * p.bn;
+  const int tile_len = (p.L - n0 < p.bn) ? (p.L - n0) : p.bn;
+  const size_t ht = size_t(h) * p.T_c + t;
+
+  // counts of head g (santa_cuda_kernel.cu:771-808), the scan as in tile_counts of sampler.cuh
+  {
+    const float invdel = p.invdelta[ht], a0 = p.a0[ht];
+    float carry = 0.f;
+    for (int base = 0; base < tile_len; base += kChunkRows) {
+      const int r = base + lane;
+      const bool valid = r < tile_len;
+      float x = 0.f;
+      if (valid && invdel > 0.f) {
+        const uint32_t ub = p.stash[(size_t(kv) * p.L + n0 + r) * p.GH + g];
+        x = __fmul_rn(Store16<TK>::unpack(ub).x, invdel);
+      }
+      float res = x;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float nb = __shfl_up_sync(0xffffffffu, res, off);
+        if (lane >= off) res = __fadd_rn(res, nb);
+      }
+      const float pre = __fsub_rn(res, x);
+      const int remain = tile_len - base;
+      const int last = remain > 32 ? 31 : remain - 1;
+      const float tot = __shfl_sync(0xffffffffu, __fadd_rn(pre, x), last);
+      const float pg = __fadd_rn(carry, pre);
+      const float cg = __fadd_rn(pg, x);
+      int c = __float2int_rd(__fadd_rn(a0, cg)) - __float2int_rd(__fadd_rn(a0, pg));
+      c = c < 0 ? 0 : (c > 32767 ? 32767 : c);
+      if (valid) {
+        c_tile[g * p.bn + r] = (int16_t)c;
+        if (p.dbg_c != nullptr) p.dbg_c[size_t(h) * p.L + n0 + r] = (int16_t)c;
+      }
+      carry = __fadd_rn(carry, tot);
+    }
+  }
+  __syncthreads();
+  // rows sampled by any head, ascending (:810-838)
+  if (g == 0) {
+    int n_emit = 0;
+    for (int base = 0; base < tile_len; base += kChunkRows) {
+      const int r = base + lane;
+      int sum = 0;
+      if (r < tile_len)
+        for (int gg = 0; gg < p.GH; ++gg) sum += c_tile[gg * p.bn + r];
+      const bool flag = sum > 0;
+      const uint32_t mask = __ballot_sync(0xffffffffu, flag);
+      if (flag && SANTA_IN_RANGE(n_emit + __popc(mask & ((1u << lane) - 1u)), p.bn, p.status)) {
+        emit[n_emit + __popc(mask & ((1u << lane) - 1u))] = r;
+        if (p.rowmask != nullptr) p.rowmask[size_t(kv) * p.L + n0 + r] = 1;
+      }
+      n_emit += __popc(mask);
+    }
+    if (lane == 0) {
+      s_emit_len = n_emit;
+      p.partial_vrows[size_t(kv) * p.T_c + t] = n_emit;
+    }
+  }
+  __syncthreads();
+  // sparse sum of c*V for head g (:843-857): lane l owns dims l, l+32, ...
+  const int n_emit = s_emit_len;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const TK* Vt = static_cast<const TK*>(p.V);
+  for (int i = 0; i < n_emit; ++i) {
+    const int r = emit[i];
+    if (!SANTA_IN_RANGE(r, tile_len, p.status)) continue;
+    const int c = c_tile[g * p.bn + r];
+    if (c != 0) {
+      const float cf = (float)c;
+      const uint16_t* vrow = reinterpret_cast<const uint16_t*>(Vt + (size_t(n0 + r) * p.KVH + kv) * p.D);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int d = lane + 32 * k;
+        if (d < p.D) acc[k] = fmaf(cf, Store16<TK>::unpack(uint32_t(vrow[d])).x, acc[k]);
+      }
+    }
+  }
+  float* po = p.partials + ((size_t(kv) * p.T_c + t) * p.GH + g) * p.D;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int d = lane + 32 * k;
+    if (d < p.D) po[d] = acc[k];
+  }
+}
+
+// One CTA per head: out[h, :] = (sum over tiles, ascending, of the tile's partial) / S.
+template <typename TK>
+__global__ void prop_merge_generic_kernel(const float* __restrict__ partials, const int* __restrict__ partial_vrows,
+                                          const int* __restrict__ S_tiles, int KVH, int GH, int D, int T_c,
+                                          float scale, TK* __restrict__ out, int* __restrict__ vrows) {
+  cudaGridDependencySynchronize();
+  const int h = blockIdx.x, kv = h / GH, g = h - kv * GH;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int t = 0; t < T_c; ++t)
+      if (S_tiles[size_t(h) * T_c + t] > 0) acc = __fadd_rn(acc, __ldcg(partials + ((size_t(kv) * T_c + t) * GH + g) * D + d));
+    reinterpret_cast<uint16_t*>(out)[size_t(h) * D + d] = Store16<TK>::bits(acc * scale);
+  }
+  if (g == 0 && vrows != nullptr && threadIdx.x == 0) {
+    int n = 0;
+    for (int t = 0; t < T_c; ++t) n += __ldcg(partial_vrows + size_t(kv) * T_c + t);
+    vrows[kv] = n;
+  }
+}
+
 // ------------------------------------------------------------------ launch
 template <typename KernelT, typename... Args>
 static cudaError_t launch_dependent(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -593,8 +746,8 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
     const int nwarp = p.block_n / 16;
     const size_t smem = size_t(nwarp * 256 + 2 * 16 * nwarp + 16) * sizeof(float);
     prop_pass1_mma_kernel<TK><<<dim3(p.T_c, KVH), nwarp * 32, smem, stream>>>(
-        static_cast<const TK*>(p.sp.q), static_cast<const TK*>(p.K), H, KVH, L, p.block_n, p.T_c, p.sp.q_scale,
-        p.sp.m_tiles, p.sp.ell_tiles, p.sp.stash, p.sp.dbg_u);
+        static_cast<const TK*>(p.sp.q), static_cast<const TK*>(p.K), H, KVH, H / KVH, p.D, L, p.block_n, p.T_c,
+        p.sp.q_scale, p.sp.m_tiles, p.sp.ell_tiles, p.sp.stash, p.sp.dbg_u);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -609,6 +762,36 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
                        (const float*)p.sp.m_tiles, (const float*)p.sp.ell_tiles, p.T_c, p.sp.seq_lens, L,
                        p.block_n, p.sp.tile_stride, p.S, p.sp.seed, p.flags, p.m_star, p.S_tiles, p.invdelta, p.a0);
   if (e != cudaSuccess) return e;
+
+  const int GH = H / KVH;
+  if (GH != kGH || p.D != kD) {
+    // shapes outside the vectorised kernels: one CTA per (kv-head, tile), one warp per head of the group
+    Pass2GenericParams pg{};
+    pg.V = p.sp.V;
+    pg.stash = p.sp.stash;
+    pg.invdelta = p.invdelta;
+    pg.a0 = p.a0;
+    pg.S_tiles = p.S_tiles;
+    pg.H = H;
+    pg.KVH = KVH;
+    pg.GH = GH;
+    pg.D = p.D;
+    pg.L = L;
+    pg.bn = p.block_n;
+    pg.T_c = p.T_c;
+    pg.partials = p.partials;
+    pg.partial_vrows = p.partial_vrows;
+    pg.dbg_c = p.dbg_c;
+    pg.rowmask = p.rowmask;
+    pg.status = p.sp.status;
+    const size_t smem2 = size_t(GH) * p.block_n * 2 + size_t(p.block_n) * 4;
+    e = launch_dependent(prop_pass2_generic_kernel<TK>, dim3(KVH, p.T_c), dim3(GH * 32), smem2, stream, pg);
+    if (e != cudaSuccess) return e;
+    const float scale = (p.S > 0) ? (1.0f / (float)p.S) : 0.0f;
+    return launch_dependent(prop_merge_generic_kernel<TK>, dim3(H), dim3(128), 0, stream,
+                            (const float*)p.partials, (const int*)p.partial_vrows, (const int*)p.S_tiles, KVH, GH,
+                            p.D, p.T_c, scale, static_cast<TK*>(p.out), p.vrows);
+  }
 
   Pass2Params p2{};
   p2.V = p.sp.V;
@@ -635,6 +818,8 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   p2.ws.nvg = int(p2.ws.items < max_warps ? p2.ws.items : max_warps);
   p2.partials = p.partials;
   p2.partial_vrows = p.partial_vrows;
+  p2.partial_slots = max_warps + (long long)nseq * KVH;
+  p2.status = p.sp.status;
   p2.dbg_c = p.dbg_c;
   p2.rowmask = p.rowmask;
   const int grid2 = (p2.ws.nvg + kPass2Warps - 1) / kPass2Warps;

@@ -110,6 +110,8 @@ struct RowTrace {
   int16_t* counts;  // same indexing
   int* rowmask;     // + row index
   size_t head_stride;
+  int* status;      // the call's status word (checked build)
+  int rows_left;    // rows of the V tensor from the tile's first row to the end of its sequence's storage
 };
 
 // Systematic counts and row compaction of one tile,
@@ -222,15 +224,138 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
     const uint32_t maskB = __ballot_sync(0xffffffffu, flagB);
     __syncwarp();
     const uint32_t lt = (1u << lane) - 1u;
-    if (flagA) {
+    if (flagA && SANTA_IN_RANGE(n_emit + __popc(maskA & lt), kChunkRows * ((tile_len + kChunkRows - 1) / kChunkRows), tr.status)) {
       emit[n_emit + __popc(maskA & lt)] =
           make_uint4((uint32_t)cA[0] | ((uint32_t)cA[1] << 16), (uint32_t)cA[2] | ((uint32_t)cA[3] << 16),
                      (uint32_t)(ch * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
     }
-    if (flagB) {
+    if (flagB && SANTA_IN_RANGE(n_emit + __popc(maskA) + __popc(maskB & lt), kChunkRows * ((tile_len + kChunkRows - 1) / kChunkRows), tr.status)) {
       emit[n_emit + __popc(maskA) + __popc(maskB & lt)] =
           make_uint4((uint32_t)cB[0] | ((uint32_t)cB[1] << 16), (uint32_t)cB[2] | ((uint32_t)cB[3] << 16),
+                     (uint32_t)((ch + 1) * kChunkRows + lane), 0u);
+      if (tr.rowmask != nullptr) tr.rowmask[(ch + 1) * kChunkRows + lane] = 1;
+    }
+    n_emit += __popc(maskA) + __popc(maskB);
+  }
+  __syncwarp();
+  return n_emit;
+}
+
+// The same for a tile in which only NA < 4 of the heads have a budget (Prop, long contexts: most
+// (head, tile) pairs get none).  A head without budget has step 0, so all its counts are zero and its
+// scans can be left out entirely: the NA active heads (bits of `active`, ascending) are gathered into
+// dense arrays, run through the same arithmetic, and their counts scattered back.  Bit-identical to
+// tile_counts on the same input.
+__device__ __forceinline__ float pick4(const float4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+template <typename TK, bool ROUNDED, bool TWO, int NA>
+__device__ __forceinline__ int tile_counts_some(float4* sb, int tile_len, int lane, const float (&invdel)[kGH],
+                                                const float (&a0)[kGH], const RowTrace& tr, uint32_t active) {
+  int hs[NA];
+  float inv[NA], off0[NA], carry[NA];
+  {
+    uint32_t m = active;
+#pragma unroll
+    for (int k = 0; k < NA; ++k) {
+      hs[k] = __ffs(m) - 1;
+      m &= m - 1u;
+      inv[k] = hs[k] == 0 ? invdel[0] : (hs[k] == 1 ? invdel[1] : (hs[k] == 2 ? invdel[2] : invdel[3]));
+      off0[k] = hs[k] == 0 ? a0[0] : (hs[k] == 1 ? a0[1] : (hs[k] == 2 ? a0[2] : a0[3]));
+      carry[k] = 0.f;
+    }
+  }
+  const int nch = (tile_len + kChunkRows - 1) / kChunkRows;
+  int n_emit = 0;
+  uint4* emit = reinterpret_cast<uint4*>(sb);
+#pragma unroll 1
+  for (int ch = 0; ch < nch; ch += (TWO ? 2 : 1)) {
+    const int remainA = tile_len - ch * kChunkRows;
+    const int remainB = remainA - kChunkRows;
+    const bool hasB = TWO && remainB > 0;
+    const int lastA = remainA > 32 ? 31 : remainA - 1;
+    const int lastB = remainB > 32 ? 31 : (hasB ? remainB - 1 : 0);
+    const bool validA = lane < remainA;
+    const bool validB = TWO && lane < remainB;
+    const float4 uA4 = sb[ch * kChunkRows + lane];
+    const float4 uB4 = hasB ? sb[(ch + 1) * kChunkRows + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float xA[NA], xB[NA], rA[NA], rB[NA];
+#pragma unroll
+    for (int k = 0; k < NA; ++k) {
+      const float uA = pick4(uA4, hs[k]), uB = pick4(uB4, hs[k]);
+      const float ruA = ROUNDED ? uA : Store16<TK>::round(uA);
+      const float ruB = ROUNDED ? uB : Store16<TK>::round(uB);
+      xA[k] = validA ? __fmul_rn(ruA, inv[k]) : 0.f;
+      xB[k] = validB ? __fmul_rn(ruB, inv[k]) : 0.f;
+      rA[k] = xA[k];
+      rB[k] = xB[k];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float nA[NA], nB[NA];
+#pragma unroll
+      for (int k = 0; k < NA; ++k) {
+        nA[k] = __shfl_up_sync(0xffffffffu, rA[k], o);
+        nB[k] = __shfl_up_sync(0xffffffffu, rB[k], o);
+      }
+      if (lane >= o) {
+#pragma unroll
+        for (int k = 0; k < NA; ++k) {
+          rA[k] = __fadd_rn(rA[k], nA[k]);
+          rB[k] = __fadd_rn(rB[k], nB[k]);
+        }
+      }
+    }
+    int c4A[kGH] = {0, 0, 0, 0}, c4B[kGH] = {0, 0, 0, 0};
+#pragma unroll
+    for (int k = 0; k < NA; ++k) {
+      const float preA = __fsub_rn(rA[k], xA[k]);
+      const float preB = __fsub_rn(rB[k], xB[k]);
+      const float totA = __shfl_sync(0xffffffffu, __fadd_rn(preA, xA[k]), lastA);
+      const float totB = __shfl_sync(0xffffffffu, __fadd_rn(preB, xB[k]), lastB);
+      const float carryB = __fadd_rn(carry[k], totA);
+      const float pgA = __fadd_rn(carry[k], preA);
+      const float cgA = __fadd_rn(pgA, xA[k]);
+      const float pgB = __fadd_rn(carryB, preB);
+      const float cgB = __fadd_rn(pgB, xB[k]);
+      int a = __float2int_rd(__fadd_rn(off0[k], cgA)) - __float2int_rd(__fadd_rn(off0[k], pgA));
+      int b = __float2int_rd(__fadd_rn(off0[k], cgB)) - __float2int_rd(__fadd_rn(off0[k], pgB));
+      a = a < 0 ? 0 : (a > 32767 ? 32767 : a);
+      b = b < 0 ? 0 : (b > 32767 ? 32767 : b);
+      a = validA ? a : 0;
+      b = validB ? b : 0;
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        c4A[g] = (hs[k] == g) ? a : c4A[g];
+        c4B[g] = (hs[k] == g) ? b : c4B[g];
+      }
+      carry[k] = hasB ? __fadd_rn(carryB, totB) : carryB;
+    }
+    if (tr.counts != nullptr) {
+#pragma unroll
+      for (int g = 0; g < kGH; ++g) {
+        const size_t o = size_t(g) * tr.head_stride + ch * kChunkRows + lane;
+        if (validA) tr.counts[o] = (int16_t)c4A[g];
+        if (validB) tr.counts[o + kChunkRows] = (int16_t)c4B[g];
+      }
+    }
+    const bool flagA = (c4A[0] + c4A[1] + c4A[2] + c4A[3]) > 0;
+    const bool flagB = (c4B[0] + c4B[1] + c4B[2] + c4B[3]) > 0;
+    const uint32_t maskA = __ballot_sync(0xffffffffu, flagA);
+    const uint32_t maskB = __ballot_sync(0xffffffffu, flagB);
+    __syncwarp();
+    const uint32_t lt = (1u << lane) - 1u;
+    const int room = kChunkRows * nch;
+    if (flagA && SANTA_IN_RANGE(n_emit + __popc(maskA & lt), room, tr.status)) {
+      emit[n_emit + __popc(maskA & lt)] =
+          make_uint4((uint32_t)c4A[0] | ((uint32_t)c4A[1] << 16), (uint32_t)c4A[2] | ((uint32_t)c4A[3] << 16),
+                     (uint32_t)(ch * kChunkRows + lane), 0u);
+      if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
+    }
+    if (flagB && SANTA_IN_RANGE(n_emit + __popc(maskA) + __popc(maskB & lt), room, tr.status)) {
+      emit[n_emit + __popc(maskA) + __popc(maskB & lt)] =
+          make_uint4((uint32_t)c4B[0] | ((uint32_t)c4B[1] << 16), (uint32_t)c4B[2] | ((uint32_t)c4B[3] << 16),
                      (uint32_t)((ch + 1) * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[(ch + 1) * kChunkRows + lane] = 1;
     }
@@ -247,7 +372,10 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
 // `vrow0` points at the V row of the tile's first row for this kv-head.
 template <typename TK>
 __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const unsigned char* __restrict__ vrow0,
-                                            size_t row_stride, int lane, float (&o)[kGH][4]) {
+                                            size_t row_stride, int lane, float (&o)[kGH][4], int* status = nullptr,
+                                            int rows_left = 0) {
+  (void)status;
+  (void)rows_left;
   constexpr int kInFlight = 8;
   const uint4* emit = reinterpret_cast<const uint4*>(sb);
 #pragma unroll 1
@@ -255,7 +383,10 @@ __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const 
     uint2 vv[kInFlight];
 #pragma unroll
     for (int k = 0; k < kInFlight; ++k) {
-      if (i0 + k < n_emit)
+#ifdef SANTA_B200_CHECKS
+      vv[k] = make_uint2(0u, 0u);  // a skipped row contributes nothing
+#endif
+      if (i0 + k < n_emit && SANTA_IN_RANGE(emit[i0 + k].z, rows_left, status))
         vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z) * row_stride) + lane);
     }
 #pragma unroll

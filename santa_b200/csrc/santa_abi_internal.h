@@ -47,6 +47,7 @@ struct StreamParams {
   // Flash: per (virtual group, column group) partials, read by the merge kernel
   float* partials;     // [nvg + column groups][gw][4][kPartialStride]
   int* partial_vrows;  // [nvg + column groups][gw]
+  long long partial_slots;  // (nvg + column groups) * gw: the extent the checked build compares slots with
   // Prop pass 1 outputs / Flash trace ([B,H,T_c]); Flash: may be null
   float* m_tiles;
   float* ell_tiles;
@@ -90,6 +91,7 @@ struct FlashMergeParams {
   WorkSplit ws;
   const float* partials;
   const int* partial_vrows;
+  long long partial_slots;
   void* out;           // [B,H,128] storage dtype or nullptr
   float* m_star;       // [B,H] or nullptr
   int* vrows;          // [B,KVH] or nullptr
@@ -104,7 +106,8 @@ cudaError_t launch_flash(const StreamParams& p, const FlashMergeParams& mp, int 
 // Prop: pass 1 (vec streaming or tensor-core), budgets, pass 2, merge.
 struct PropParams {
   StreamParams sp;      // pass 1 (vec path) -- also carries q, V, H, KVH, L, ws, status, stash, m/ell tiles
-  const void* K;        // [L,KVH,128]
+  const void* K;        // [L,KVH,D]
+  int D;                // head dimension; with H / KVH != 4 or D != 128 the generic pass 2 / merge run
   int block_n, T_c;
   int use_vec;          // 1: streaming vec pass 1, 0: tensor-core pass 1
   int S;
@@ -115,7 +118,7 @@ struct PropParams {
   float* a0;
   float* m_star;        // [H] output
   // pass 2 partials
-  float* partials;      // [nvg + column groups][gw][4][128]
+  float* partials;      // [nvg + column groups][gw][4][128]; generic shapes: [KVH][T_c][GH][D]
   int* partial_vrows;
   // outputs
   void* out;            // [H,128] storage dtype

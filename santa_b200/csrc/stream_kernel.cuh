@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           dead = true;
           if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
-        const int npc = (tile_len + kStageRows - 1) / kStageRows;
+        int npc = (tile_len + kStageRows - 1) / kStageRows;
+        if (!SANTA_IN_RANGE(npc * kStageRows - 1, kMaxTileRows, p.status)) npc = 0;  // a piece past the score buffer
 #pragma unroll 1
         for (int pc = 0; pc < npc; ++pc) {
           if (!dead && !ring.wait(ring.count)) {
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 #pragma unroll 1
           for (int ch = 0; ch < nch; ++ch) {
             const int r = ch * kChunkRows + lane;
-            if (r < tile_len) {
+            if (r < tile_len && SANTA_IN_RANGE(n0 + r, p.len_stride, p.status)) {
               const float4 u = sb[r];
               const uint32_t w01 = uint32_t(Store16<TK>::bits(u.x)) | (uint32_t(Store16<TK>::bits(u.y)) << 16);
               const uint32_t w23 = uint32_t(Store16<TK>::bits(u.z)) | (uint32_t(Store16<TK>::bits(u.w)) << 16);
@@ -251,9 +252,11 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
             iv = (lane == g) ? invdel[g] : iv;
           }
           const size_t o = (bh0 + lane) * p.tile_stride + t;
-          p.m_tiles[o] = mv;
-          p.ell_tiles[o] = ev;
-          if (p.dbg_invdel != nullptr) p.dbg_invdel[o] = iv;
+          if (SANTA_IN_RANGE(t, p.tile_stride, p.status) && SANTA_IN_RANGE(bh0 + lane, size_t(p.nseq) * p.H, p.status)) {
+            p.m_tiles[o] = mv;
+            p.ell_tiles[o] = ev;
+            if (p.dbg_invdel != nullptr) p.dbg_invdel[o] = iv;
+          }
         }
 
         if (MODE == kModeFlash) {
@@ -264,6 +267,8 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
 #pragma unroll
           for (int g = 0; g < kGH; ++g) a0[g] = __shfl_sync(0xffffffffu, a0_lane, g);
           RowTrace tr;
+          tr.status = p.status;
+          tr.rows_left = p.L_storage - n0;
           tr.head_stride = size_t(p.len_stride);
           tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.len_stride + n0 : nullptr;
           tr.counts = p.dbg_c ? p.dbg_c + bh0 * p.len_stride + n0 : nullptr;
@@ -276,7 +281,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           for (int g = 0; g < kGH; ++g)
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
-          gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o);
+          gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o, p.status, tr.rows_left);
 
 #pragma unroll
           for (int g = 0; g < kGH; ++g) {
@@ -296,6 +301,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         // ---- publish this column's partial -------------------------------
         const size_t pslot = size_t(ww.vg + cg) * p.ws.gw + ww.col_in_group;
         float* ps = p.partials + pslot * (kGH * kPartialStride);
+        if (SANTA_IN_RANGE(pslot, p.partial_slots, p.status)) {
 #pragma unroll
         for (int g = 0; g < kGH; ++g) {
           reinterpret_cast<float4*>(ps + g * kPartialStride)[lane] = make_float4(A[g][0], A[g][1], A[g][2], A[g][3]);
@@ -305,6 +311,7 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           }
         }
         if (lane == 0) p.partial_vrows[pslot] = vrow_count;
+        }
       }
     } else {
       handoff += uint32_t(t_hi - t_lo);

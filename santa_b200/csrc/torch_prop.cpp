@@ -93,15 +93,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> decode_systematic_scalar(at::Tens
   SANTA_CHECK(K_g.is_contiguous() && V_g.is_contiguous(), "K_g/V_g must be contiguous with layout [L, KVH, D] (NHD)");
 
   const int H = (int)q_h.size(0), D = (int)q_h.size(1), L = (int)K_g.size(0), KVH = (int)K_g.size(1);
-  SANTA_CHECK(D == 128 && H / KVH == 4, "This build supports only D=128 and GH=4 (H/KVH). Got D=", D,
-              " GH=", H / KVH);
+  // any GH and D % 16 == 0 like the reference (santa_cuda.cpp:212-247); its second pass launches 128 x GH
+  // threads per block (santa_cuda_kernel.cu:924-927), which bounds GH by 8
+  SANTA_CHECK(H / KVH <= 8, "This build supports up to 8 query heads per kv-head. Got GH=", H / KVH);
+  SANTA_CHECK(D <= 256, "This build supports head dimensions up to 256. Got D=", D);
   const int mode = pass1_mode_from_env();
   int bn = (int)block_n;
   if (bn <= 0) bn = (mode == 2) ? 256 : santa_block_n_rule(L, 0);
-  SANTA_CHECK(mode != 2 || bn == 256, "SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH=", H / KVH,
-              " D=", D, " block_n=", bn);
-  SANTA_CHECK(bn % 16 == 0, "Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D=", D,
-              " block_n=", bn);
+  SANTA_CHECK(mode != 2 || (H / KVH == 4 && D == 128 && bn == 256),
+              "SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH=", H / KVH, " D=", D, " block_n=", bn);
+  SANTA_CHECK(D % 16 == 0 && bn % 16 == 0,
+              "Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D=", D, " block_n=", bn);
   SANTA_CHECK(bn <= 256, "This build supports block_n up to 256. Got block_n=", bn);
 
   // argument errors are raised above, before any device state is touched

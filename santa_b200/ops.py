@@ -319,13 +319,17 @@ def prop_decode(q_h, K_g, V_g, S, seed=42, block_n=0, want_vrows=False, *, trace
     H, D = q.shape
     L, KVH = K_g.size(0), K_g.size(1)
     mode = _pass1_mode_from_env() if pass1_mode is None else int(pass1_mode)
-    _check(D == 128 and H // KVH == 4,
-           f"This build supports only D=128 and GH=4 (H/KVH). Got D={D} GH={H // KVH}")
+    # any GH and D % 16 == 0 like the reference (santa_cuda.cpp:212-247); its second pass launches
+    # 128 x GH threads per block (santa_cuda_kernel.cu:924-927), which bounds GH by 8
+    _check(H // KVH <= 8, f"This build supports up to 8 query heads per kv-head. Got GH={H // KVH}")
+    _check(D <= 256, f"This build supports head dimensions up to 256. Got D={D}")
     bn = int(block_n)
     if bn <= 0:
         bn = 256 if mode == 2 else capi.block_n_rule(L, 0)
-    _check(mode != 2 or bn == 256, f"SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH={H // KVH} D={D} block_n={bn}")
-    _check(bn % 16 == 0, f"Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D={D} block_n={bn}")
+    _check(mode != 2 or (bn == 256 and H // KVH == 4 and D == 128),
+           f"SANTA_PASS1=vec requires GH=4, D=128, block_n=256. Got GH={H // KVH} D={D} block_n={bn}")
+    _check(D % 16 == 0 and bn % 16 == 0,
+           f"Pass-1 WMMA-GQA requires D % 16 == 0 and block_n % 16 == 0. Got D={D} block_n={bn}")
     _check(bn <= 256, f"This build supports block_n up to 256. Got block_n={bn}")
     T_c = (L + bn - 1) // bn
     dev = q.device

@@ -29,13 +29,38 @@ def main():
     tol = lambda a, b: (a.float() - b.float()).abs().max().item() <= 2e-2  # noqa: E731
     o_nccl, m_nccl = sharded.seq_sharded_flash_decode(q, Ks, Vs, S, 77, L)
     assert tol(o_nccl, full[0]) and torch.equal(m_nccl, full[1]), "all-gather path differs from the unsharded call"
-    ex = sharded.PeerExchange(B, 32, dev)
-    for step in range(5):                                  # several epochs: both buffer halves are reused
-        qs = q if step % 2 == 0 else (q * 0.75).to(torch.bfloat16)
+    # the receiving half inside the decode call (fused) and as a kernel of its own
+    for fused in (True, False):
+        ex = sharded.PeerExchange(B, 32, dev, fused=fused)
+        for step in range(5):                              # several epochs: both buffer halves are reused
+            qs = q if step % 2 == 0 else (q * 0.75).to(torch.bfloat16)
+            ref = sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L)
+            got = sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L, exchange=ex)
+            ex.check()
+            assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), \
+                f"peer exchange (fused={fused}) differs at step {step}"
+            if step == 0:
+                assert tol(got[0], full[0]) and torch.equal(got[1], full[1]), "peer exchange differs from the unsharded call"
+    # epochs counted on the device: one captured step replayed
+    exg = sharded.PeerExchange(B, 32, dev, device_counted=True)
+    qs = q.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L, exchange=exg)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        outg = sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L, exchange=exg)
+    for step in range(3):
+        qs.copy_(q if step % 2 == 0 else (q * 0.75).to(torch.bfloat16))
+        graph.replay()
+        exg.check()
         ref = sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L)
-        got = sharded.seq_sharded_flash_decode(qs, Ks, Vs, S, 77, L, exchange=ex)
-        ex.check()
-        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), f"peer exchange differs at step {step}"
+        assert torch.equal(outg[0], ref[0]) and torch.equal(outg[1], ref[1]), f"graph replay differs at step {step}"
+    del graph
     dist.barrier()
     if rank == 0:
         print("MP_SEQ_SHARDED_OK", world)
