@@ -221,11 +221,12 @@ def gather_ranks(x, world, dev):
     return [float(v) for v in out.tolist()]
 
 
-def timed_blocks(fn, steps, warmup, world, dev, min_s=MIN_TIMED_S, sampler=None):
+def timed_blocks(fn, steps, warmup, world, dev, min_s=None, sampler=None):
     """W warm-up steps, then blocks of exactly K steps; every block sits between barrier + synchronize
     on both sides and is timed by CUDA events on the launching stream.  Blocks repeat until `min_s`
     seconds of device time have passed on the slowest rank.  Returns a dict: `s_per_block` is the
     median block of the slowest rank; `per_rank_ms_per_step` lists every rank's median."""
+    min_s = MIN_TIMED_S if min_s is None else min(min_s, MIN_TIMED_S)
     for i in range(warmup):
         fn(i)
     blocks, spent, i0 = [], 0.0, warmup
@@ -337,6 +338,7 @@ def reference_cuda_flash(dev, qpool, K, V, steps, world):
 
 
 def main():
+    global MIN_TIMED_S
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
@@ -349,6 +351,11 @@ def main():
     ap.add_argument("--no-ref-kernels", action="store_true", help="skip timing the reference's CUDA kernels")
     ap.add_argument("--no-b32", action="store_true", help="skip the B=32 variant of the headline workload")
     ap.add_argument("--no-tensor-mode", action="store_true", help="skip the opt-in tensor-core score mode extras")
+    ap.add_argument("--min-timed-s", type=float, default=MIN_TIMED_S,
+                    help="device seconds to accumulate over the repeated K-step blocks (0: one block; for profiling)")
+    ap.add_argument("--score-mode", type=int, default=0, choices=[0, 1],
+                    help="score arithmetic of the headline measurement: 0 = the reference's order (default), "
+                         "1 = the opt-in tensor-core mode (the line then says so in config.score_mode)")
     ap.add_argument("--e2e-model-batch", type=int, default=32)
     ap.add_argument("--e2e-prefill", action="store_true",
                     help="run the real 512-token-chunk prefill of the end-to-end extra instead of a synthetic cache")
@@ -356,6 +363,7 @@ def main():
     if args.impl == "reference":
         reference_arm(args)
         return
+    MIN_TIMED_S = args.min_timed_s
 
     import santa_b200
     from santa_b200 import ops, sharded
@@ -371,14 +379,16 @@ def main():
 
     # algorithmic bytes of one step: every valid K row once per kv-head + the distinct sampled V rows
     # + q + out + m_star
-    _, _, vrows = ops.flash_decode(qpool[0], K, V, S, seed=SEED, want_vrows=True, batch_offset=rank * B)
+    _, _, vrows = ops.flash_decode(qpool[0], K, V, S, seed=SEED, want_vrows=True, batch_offset=rank * B,
+                                   score_mode=args.score_mode)
     vrows_total = int(vrows.sum().item())
     alg_bytes = B * L * KVH * D * 2 + vrows_total * D * 2 + 2 * B * H * D * 2 + B * H * 4
 
     # ---- kernel-resident measurement (C ABI, inputs in HBM) -----------------------------------
     out_dev = torch.empty(B, H, D, device=dev, dtype=torch.bfloat16)
     tm = timed_blocks(lambda i: ops.flash_decode(qpool[i % QPOOL], K, V, S, seed=SEED, batch_offset=rank * B,
-                                                 out=out_dev), steps, warmup, world, dev, sampler=sampler)
+                                                 out=out_dev, score_mode=args.score_mode),
+                      steps, warmup, world, dev, sampler=sampler)
     clocks = sampler.stop()
     status = ops.workspace_status("flash", dev)
 
@@ -460,6 +470,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": B, "parallelism": f"batch-sharded x{world}, no collective",
+                       "score_mode": "exact (the reference's fp32 order)" if args.score_mode == 0 else "tensor cores (opt-in)",
                        "l2": "inputs (1 GiB of K+V per GPU) exceed the 126 MB L2", "q": f"pool of {QPOOL} cycled"},
             "timing": {"what": f"median of {tm['repeats']} blocks of {steps} steps (max over ranks of the rank medians)",
                        "ms_per_step_min": tm["ms_per_step_min"], "ms_per_step_max": tm["ms_per_step_max"],
@@ -815,7 +826,7 @@ def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefil
             ids = torch.randint(0, rt.shape.vocab, (batch, prompt_len), generator=torch.Generator().manual_seed(11))
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            first = rt.prefill(ids.to(dev), chunk=512)
+            first = rt.prefill(ids.to(dev), chunk=512, seqs_per_pass=2)
             e1.record()
             torch.cuda.synchronize(dev)
             out["prefill_s"] = e0.elapsed_time(e1) * 1e-3

@@ -408,6 +408,8 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
       RowTrace tr;
       tr.status = p.status;
       tr.rows_left = p.L_storage - n0;
+      tr.vrow0 = vcol + size_t(n0) * row_stride;
+      tr.row_stride = row_stride;
       tr.head_stride = ls;
       tr.u16 = nullptr;
       tr.counts = p.dbg_c ? p.dbg_c + bh0 * ls + n0 : nullptr;

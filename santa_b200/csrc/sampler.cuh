@@ -112,7 +112,20 @@ struct RowTrace {
   size_t head_stride;
   int* status;      // the call's status word (checked build)
   int rows_left;    // rows of the V tensor from the tile's first row to the end of its sequence's storage
+  // V row of the tile's first row for this kv-head and the bytes between rows (or null): a row is
+  // prefetched into L2 the moment the counts show it is sampled, so that the gather after the last
+  // chunk finds it there instead of waiting a DRAM round trip
+  const unsigned char* vrow0;
+  size_t row_stride;
+#ifdef SANTA_EXP_TIMERS
+  long long* tm;  // timing experiment: cycles of the four sub-phases of tile_counts
+#endif
 };
+
+__device__ __forceinline__ void prefetch_row_l2(const unsigned char* row) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(row));
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(row + 128));
+}
 
 // Systematic counts and row compaction of one tile,
 // flash_style_fused_santa_fixed_tile_budgets/santa_cuda_kernel.cu:275-345
@@ -146,6 +159,9 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
     const int lastB = remainB > 32 ? 31 : (hasB ? remainB - 1 : 0);
     const bool validA = lane < remainA;
     const bool validB = TWO && lane < remainB;
+#ifdef SANTA_EXP_TIMERS
+    const long long q0 = clock64();
+#endif
     const float4 uA4 = sb[ch * kChunkRows + lane];
     const float4 uB4 = hasB ? sb[(ch + 1) * kChunkRows + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
     const float uA[kGH] = {uA4.x, uA4.y, uA4.z, uA4.w};
@@ -160,6 +176,9 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
       rA[g] = xA[g];
       rB[g] = xB[g];
     }
+#ifdef SANTA_EXP_TIMERS
+    const long long q1 = clock64();
+#endif
     // inclusive Hillis-Steele scans (offsets 1,2,4,8,16)
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -169,14 +188,18 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
         nA[g] = __shfl_up_sync(0xffffffffu, rA[g], off);
         nB[g] = __shfl_up_sync(0xffffffffu, rB[g], off);
       }
-      if (lane >= off) {
+      // lanes below `off` add +0.0f, which leaves their (non-negative) value bit for bit as it is:
+      // no divergent branch inside the scan
+      const bool take = lane >= off;
 #pragma unroll
-        for (int g = 0; g < kGH; ++g) {
-          rA[g] = __fadd_rn(rA[g], nA[g]);
-          rB[g] = __fadd_rn(rB[g], nB[g]);
-        }
+      for (int g = 0; g < kGH; ++g) {
+        rA[g] = __fadd_rn(rA[g], take ? nA[g] : 0.f);
+        rB[g] = __fadd_rn(rB[g], take ? nB[g] : 0.f);
       }
     }
+#ifdef SANTA_EXP_TIMERS
+    const long long q2 = clock64();
+#endif
     float preA[kGH], preB[kGH], totA[kGH], totB[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
@@ -217,6 +240,9 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
         }
       }
     }
+#ifdef SANTA_EXP_TIMERS
+    const long long q3 = clock64();
+#endif
     // compaction in ascending row order: A's rows, then B's
     const bool flagA = (cA[0] + cA[1] + cA[2] + cA[3]) > 0;
     const bool flagB = (cB[0] + cB[1] + cB[2] + cB[3]) > 0;
@@ -229,14 +255,25 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
           make_uint4((uint32_t)cA[0] | ((uint32_t)cA[1] << 16), (uint32_t)cA[2] | ((uint32_t)cA[3] << 16),
                      (uint32_t)(ch * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
+      if (tr.vrow0 != nullptr) prefetch_row_l2(tr.vrow0 + size_t(ch * kChunkRows + lane) * tr.row_stride);
     }
     if (flagB && SANTA_IN_RANGE(n_emit + __popc(maskA) + __popc(maskB & lt), kChunkRows * ((tile_len + kChunkRows - 1) / kChunkRows), tr.status)) {
       emit[n_emit + __popc(maskA) + __popc(maskB & lt)] =
           make_uint4((uint32_t)cB[0] | ((uint32_t)cB[1] << 16), (uint32_t)cB[2] | ((uint32_t)cB[3] << 16),
                      (uint32_t)((ch + 1) * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[(ch + 1) * kChunkRows + lane] = 1;
+      if (tr.vrow0 != nullptr) prefetch_row_l2(tr.vrow0 + size_t((ch + 1) * kChunkRows + lane) * tr.row_stride);
     }
     n_emit += __popc(maskA) + __popc(maskB);
+#ifdef SANTA_EXP_TIMERS
+    if (tr.tm != nullptr) {
+      const long long q4 = clock64();
+      tr.tm[0] += q1 - q0;
+      tr.tm[1] += q2 - q1;
+      tr.tm[2] += q3 - q2;
+      tr.tm[3] += q4 - q3;
+    }
+#endif
   }
   __syncwarp();
   return n_emit;
@@ -299,12 +336,11 @@ __device__ __forceinline__ int tile_counts_some(float4* sb, int tile_len, int la
         nA[k] = __shfl_up_sync(0xffffffffu, rA[k], o);
         nB[k] = __shfl_up_sync(0xffffffffu, rB[k], o);
       }
-      if (lane >= o) {
+      const bool take = lane >= o;
 #pragma unroll
-        for (int k = 0; k < NA; ++k) {
-          rA[k] = __fadd_rn(rA[k], nA[k]);
-          rB[k] = __fadd_rn(rB[k], nB[k]);
-        }
+      for (int k = 0; k < NA; ++k) {
+        rA[k] = __fadd_rn(rA[k], take ? nA[k] : 0.f);
+        rB[k] = __fadd_rn(rB[k], take ? nB[k] : 0.f);
       }
     }
     int c4A[kGH] = {0, 0, 0, 0}, c4B[kGH] = {0, 0, 0, 0};
@@ -352,12 +388,14 @@ __device__ __forceinline__ int tile_counts_some(float4* sb, int tile_len, int la
           make_uint4((uint32_t)c4A[0] | ((uint32_t)c4A[1] << 16), (uint32_t)c4A[2] | ((uint32_t)c4A[3] << 16),
                      (uint32_t)(ch * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[ch * kChunkRows + lane] = 1;
+      if (tr.vrow0 != nullptr) prefetch_row_l2(tr.vrow0 + size_t(ch * kChunkRows + lane) * tr.row_stride);
     }
     if (flagB && SANTA_IN_RANGE(n_emit + __popc(maskA) + __popc(maskB & lt), room, tr.status)) {
       emit[n_emit + __popc(maskA) + __popc(maskB & lt)] =
           make_uint4((uint32_t)c4B[0] | ((uint32_t)c4B[1] << 16), (uint32_t)c4B[2] | ((uint32_t)c4B[3] << 16),
                      (uint32_t)((ch + 1) * kChunkRows + lane), 0u);
       if (tr.rowmask != nullptr) tr.rowmask[(ch + 1) * kChunkRows + lane] = 1;
+      if (tr.vrow0 != nullptr) prefetch_row_l2(tr.vrow0 + size_t((ch + 1) * kChunkRows + lane) * tr.row_stride);
     }
     n_emit += __popc(maskA) + __popc(maskB);
   }
@@ -387,7 +425,11 @@ __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const 
       vv[k] = make_uint2(0u, 0u);  // a skipped row contributes nothing
 #endif
       if (i0 + k < n_emit && SANTA_IN_RANGE(emit[i0 + k].z, rows_left, status))
+#ifdef SANTA_EXP_GATHER_L2  // timing experiment: always the same eight rows (cache hits), same instructions
+        vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z & 7u) * row_stride) + lane);
+#else
         vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z) * row_stride) + lane);
+#endif
     }
 #pragma unroll
     for (int k = 0; k < kInFlight; ++k) {
