@@ -117,9 +117,6 @@ struct RowTrace {
   // chunk finds it there instead of waiting a DRAM round trip
   const unsigned char* vrow0;
   size_t row_stride;
-#ifdef SANTA_EXP_TIMERS
-  long long* tm;  // timing experiment: cycles of the four sub-phases of tile_counts
-#endif
 };
 
 __device__ __forceinline__ void prefetch_row_l2(const unsigned char* row) {
@@ -159,9 +156,6 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
     const int lastB = remainB > 32 ? 31 : (hasB ? remainB - 1 : 0);
     const bool validA = lane < remainA;
     const bool validB = TWO && lane < remainB;
-#ifdef SANTA_EXP_TIMERS
-    const long long q0 = clock64();
-#endif
     const float4 uA4 = sb[ch * kChunkRows + lane];
     const float4 uB4 = hasB ? sb[(ch + 1) * kChunkRows + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
     const float uA[kGH] = {uA4.x, uA4.y, uA4.z, uA4.w};
@@ -176,9 +170,6 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
       rA[g] = xA[g];
       rB[g] = xB[g];
     }
-#ifdef SANTA_EXP_TIMERS
-    const long long q1 = clock64();
-#endif
     // inclusive Hillis-Steele scans (offsets 1,2,4,8,16)
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -197,9 +188,6 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
         rB[g] = __fadd_rn(rB[g], take ? nB[g] : 0.f);
       }
     }
-#ifdef SANTA_EXP_TIMERS
-    const long long q2 = clock64();
-#endif
     float preA[kGH], preB[kGH], totA[kGH], totB[kGH];
 #pragma unroll
     for (int g = 0; g < kGH; ++g) {
@@ -240,9 +228,6 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
         }
       }
     }
-#ifdef SANTA_EXP_TIMERS
-    const long long q3 = clock64();
-#endif
     // compaction in ascending row order: A's rows, then B's
     const bool flagA = (cA[0] + cA[1] + cA[2] + cA[3]) > 0;
     const bool flagB = (cB[0] + cB[1] + cB[2] + cB[3]) > 0;
@@ -265,15 +250,6 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
       if (tr.vrow0 != nullptr) prefetch_row_l2(tr.vrow0 + size_t((ch + 1) * kChunkRows + lane) * tr.row_stride);
     }
     n_emit += __popc(maskA) + __popc(maskB);
-#ifdef SANTA_EXP_TIMERS
-    if (tr.tm != nullptr) {
-      const long long q4 = clock64();
-      tr.tm[0] += q1 - q0;
-      tr.tm[1] += q2 - q1;
-      tr.tm[2] += q3 - q2;
-      tr.tm[3] += q4 - q3;
-    }
-#endif
   }
   __syncwarp();
   return n_emit;
@@ -425,11 +401,7 @@ __device__ __forceinline__ void gather_rows(const float4* sb, int n_emit, const 
       vv[k] = make_uint2(0u, 0u);  // a skipped row contributes nothing
 #endif
       if (i0 + k < n_emit && SANTA_IN_RANGE(emit[i0 + k].z, rows_left, status))
-#ifdef SANTA_EXP_GATHER_L2  // timing experiment: always the same eight rows (cache hits), same instructions
-        vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z & 7u) * row_stride) + lane);
-#else
         vv[k] = __ldg(reinterpret_cast<const uint2*>(vrow0 + size_t(emit[i0 + k].z) * row_stride) + lane);
-#endif
     }
 #pragma unroll
     for (int k = 0; k < kInFlight; ++k) {

@@ -213,10 +213,6 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         for (int i = 0; i < 4; ++i) A[g][i] = 0.f;
       }
       int vrow_count = 0;
-#ifdef SANTA_EXP_TIMERS
-      long long tm_wait = 0, tm_stats = 0, tm_counts = 0, tm_gather = 0, tm_all = clock64();
-      long long tm_sub[4] = {0, 0, 0, 0};
-#endif
 
 #pragma unroll 1
       for (int t = t_lo; t < t_hi; ++t, ++handoff) {
@@ -224,17 +220,10 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         const int tile_len = (L_b - n0 < BN) ? (L_b - n0) : BN;
         const uint32_t buf = handoff & 1u;
         float4* sb = reinterpret_cast<float4*>(scorebufs + buf * (kScoreBytes / 4));
-#ifdef SANTA_EXP_TIMERS
-        long long c0 = clock64();
-#endif
         if (!dead && !mbar_wait_bounded(bar_full + 8 * buf, (handoff >> 1) & 1u, 256)) {
           dead = true;
           if (lane == 0) atomicExch(p.status, kStatusHandoffTimeout);
         }
-#ifdef SANTA_EXP_TIMERS
-        long long c1 = clock64();
-        tm_wait += c1 - c0;
-#endif
 
         float m[kGH], ell[kGH];
         if constexpr (MMA) {  // computed by the score warp (see there)
@@ -246,10 +235,6 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
         } else {
           tile_stats<NW>(sb, tile_len, lane, m, ell);
         }
-#ifdef SANTA_EXP_TIMERS
-        long long c2 = clock64();
-        tm_stats += c2 - c1;
-#endif
         const size_t bh0 = size_t(b) * p.H + h0;
 
         if (MODE == kModePropPass1) {
@@ -312,37 +297,19 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           tr.rows_left = p.L_storage - n0;
           tr.vrow0 = vcol + size_t(n0) * row_stride;
           tr.row_stride = row_stride;
-#ifdef SANTA_EXP_TIMERS
-          tr.tm = tm_sub;
-#endif
           tr.head_stride = size_t(p.len_stride);
           tr.u16 = p.dbg_u ? p.dbg_u + bh0 * p.len_stride + n0 : nullptr;
           tr.counts = p.dbg_c ? p.dbg_c + bh0 * p.len_stride + n0 : nullptr;
           tr.rowmask = p.rowmask ? p.rowmask + (size_t(b) * p.KVH + kv) * p.len_stride + n0 : nullptr;
-#ifdef SANTA_EXP_NOCOUNTS
-          const int n_emit = 0;
-#else
           const int n_emit = tile_counts<TK>(sb, tile_len, lane, invdel, a0, tr);
-#endif
           vrow_count += n_emit;
-#ifdef SANTA_EXP_TIMERS
-          long long c3 = clock64();
-          tm_counts += c3 - c2;
-#endif
 
           float o[kGH][4];
 #pragma unroll
           for (int g = 0; g < kGH; ++g)
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
-#ifdef SANTA_EXP_GATHER_L2
-          gather_rows<TK>(sb, n_emit, vcol, row_stride, lane, o, p.status, tr.rows_left);
-#elif !defined(SANTA_EXP_NOGATHER)
           gather_rows<TK>(sb, n_emit, vcol + size_t(n0) * row_stride, row_stride, lane, o, p.status, tr.rows_left);
-#endif
-#ifdef SANTA_EXP_TIMERS
-          tm_gather += clock64() - c3;
-#endif
 
 #pragma unroll
           for (int g = 0; g < kGH; ++g) {
@@ -372,19 +339,6 @@ __global__ void __launch_bounds__(kCtaWarps * 32, 1) stream_kernel(const __grid_
           }
         }
         if (lane == 0) p.partial_vrows[pslot] = vrow_count;
-#ifdef SANTA_EXP_TIMERS  // timing experiment: phase cycles of this range in the slot's unused words
-        if (lane == 0) {
-          ps[0 * kPartialStride + kD + 2] = float(tm_wait);
-          ps[0 * kPartialStride + kD + 3] = float(tm_stats);
-          ps[1 * kPartialStride + kD + 2] = float(tm_counts);
-          ps[1 * kPartialStride + kD + 3] = float(tm_gather);
-          (void)tm_all;
-          ps[2 * kPartialStride + kD + 2] = float(tm_sub[0]);
-          ps[2 * kPartialStride + kD + 3] = float(t_hi - t_lo);
-          ps[3 * kPartialStride + kD + 2] = float(tm_sub[1]);
-          ps[3 * kPartialStride + kD + 3] = float(tm_sub[2]);
-        }
-#endif
         }
       }
     } else {
