@@ -179,13 +179,12 @@ __device__ __forceinline__ int tile_counts(float4* sb, int tile_len, int lane, c
         nA[g] = __shfl_up_sync(0xffffffffu, rA[g], off);
         nB[g] = __shfl_up_sync(0xffffffffu, rB[g], off);
       }
-      // lanes below `off` add +0.0f, which leaves their (non-negative) value bit for bit as it is:
-      // no divergent branch inside the scan
-      const bool take = lane >= off;
+      if (lane >= off) {
 #pragma unroll
-      for (int g = 0; g < kGH; ++g) {
-        rA[g] = __fadd_rn(rA[g], take ? nA[g] : 0.f);
-        rB[g] = __fadd_rn(rB[g], take ? nB[g] : 0.f);
+        for (int g = 0; g < kGH; ++g) {
+          rA[g] = __fadd_rn(rA[g], nA[g]);
+          rB[g] = __fadd_rn(rB[g], nB[g]);
+        }
       }
     }
     float preA[kGH], preB[kGH], totA[kGH], totB[kGH];
@@ -312,11 +311,12 @@ __device__ __forceinline__ int tile_counts_some(float4* sb, int tile_len, int la
         nA[k] = __shfl_up_sync(0xffffffffu, rA[k], o);
         nB[k] = __shfl_up_sync(0xffffffffu, rB[k], o);
       }
-      const bool take = lane >= o;
+      if (lane >= o) {
 #pragma unroll
-      for (int k = 0; k < NA; ++k) {
-        rA[k] = __fadd_rn(rA[k], take ? nA[k] : 0.f);
-        rB[k] = __fadd_rn(rB[k], take ? nB[k] : 0.f);
+        for (int k = 0; k < NA; ++k) {
+          rA[k] = __fadd_rn(rA[k], nA[k]);
+          rB[k] = __fadd_rn(rB[k], nB[k]);
+        }
       }
     }
     int c4A[kGH] = {0, 0, 0, 0}, c4B[kGH] = {0, 0, 0, 0};
