@@ -877,8 +877,8 @@ def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefil
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stream_kernel launch on this workload, from one
-# ncu capture of that kernel (read 557.92 MB + write 7.83 MB).
-TRAFFIC_BYTES_PER_LAUNCH = 565_754_112
+# ncu capture of that kernel (read 557.80 MB + write 10.40 MB).
+TRAFFIC_BYTES_PER_LAUNCH = 568_195_840
 
 if __name__ == "__main__":
     main()
