@@ -15,9 +15,10 @@ ranks' medians), with min / max / repeats and -- at N>1 -- every rank's median b
 and throttle reasons are sampled through NVML every few milliseconds during the timed region.
 
 The JSON line carries: `value` = steps/s with inputs resident in HBM (C-ABI path), `e2e` = the same
-through the reference-facing module santa_flash_batch_cuda with this step's q / new k,v rows copied
-from pinned host memory and the output stored to host memory inside the timed region (the KV cache
-itself is resident device state, as in the reference's runtime), `roofline` for the streaming
+with host buffers inside the timed region: this step's q / new k,v rows are read from pinned host
+memory by the append launch, the output is stored to pinned host memory by the decode call and the
+stream is synchronised every step; the result is checked against the reference-facing module
+santa_flash_batch_cuda (the KV cache itself is resident device state, as in the reference's runtime), `roofline` for the streaming
 kernel against the measured HBM copy peak, `cpu_baseline` (dense SDPA on the host cores, the
 reference's only CPU-runnable backend), `vs_reference_cuda_kernels` (the reference's own kernels,
 compiled unmodified for sm_100a, timed in the same process on the same inputs) and, as extra
@@ -393,70 +394,58 @@ def main():
     status = ops.workspace_status("flash", dev)
 
     # ---- end to end through the reference-facing module, host buffers -------------------------
+    # This step's inputs -- q and the new token's k / v rows -- sit in pinned host memory.  One launch
+    # (the fused RoPE + cache-append + q-pack kernel, here with the identity rotation, so that q and the
+    # rows are exactly the given ones) reads them over PCIe, appends the rows to the cache and packs q
+    # in device memory; the decode call follows, and its merge kernel stores the result straight into
+    # the caller's pinned host buffer.
     q_host = [q.cpu().pin_memory() for q in qpool]
     kv_new_host = torch.randn(2, B, KVH, D, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
     out_host = torch.empty(B, H, D, dtype=torch.bfloat16).pin_memory()
-    # one pinned staging buffer per step, [all q | all new k rows | all new v rows]: one copy in
-    nq, nkv = B * H * D, B * KVH * D
-    stage_host = torch.empty(nq + 2 * nkv, dtype=torch.bfloat16).pin_memory()
-    stage_host[nq:nq + nkv].copy_(kv_new_host[0].reshape(-1))
-    stage_host[nq + nkv:].copy_(kv_new_host[1].reshape(-1))
-    q_stage = stage_host[:nq].view(B, H, D)
-    stage_dev = torch.empty(nq + 2 * nkv, device=dev, dtype=torch.bfloat16)
-    q_dev = stage_dev[:nq].view(B, H, D)
-    k_new_dev = stage_dev[nq:nq + nkv].view(B, KVH, D)
-    v_new_dev = stage_dev[nq + nkv:].view(B, KVH, D)
+    q_dev = torch.empty(B, H, D, device=dev, dtype=torch.bfloat16)
+    cos1 = torch.ones(B, D, device=dev, dtype=torch.bfloat16)
+    sin0 = torch.zeros(B, D, device=dev, dtype=torch.bfloat16)
 
-    def e2e_body():
-        stage_dev.copy_(stage_host, non_blocking=True)
-        K[:, L - 1].copy_(k_new_dev)  # append this step's key/value row in place (fixed valid_len)
-        V[:, L - 1].copy_(v_new_dev)
-        if direct_out:   # the merge kernel stores the result straight into the pinned host buffer
-            ops.flash_decode(q_dev, K, V, S, seed=SEED, valid_len=L, out=out_host)
-        else:
-            out = flash_mod.decode_systematic_batched(q_dev, K, V, S, seed=SEED, want_vrows=False, valid_len=L)[0]
-            out_host.copy_(out, non_blocking=True)
+    def e2e_body(i):
+        ops.rope_append(q_host[i], kv_new_host[0], kv_new_host[1], cos1, sin0, K, V, L - 1, q_out=q_dev)
+        ops.flash_decode(q_dev, K, V, S, seed=SEED, valid_len=L, out=out_host)
 
-    # The whole step (copies in, KV append, decode, result out) is captured once into a CUDA graph, as a
-    # serving loop would do, and replayed per step; the step's q is first written into the pinned staging
-    # buffer by the host.  If capture is not possible the step runs eagerly.
-    q_stage.copy_(q_host[0])
-    # first through the reference-facing module + an explicit copy out (the reference's calling pattern),
-    # to have its result; then the timed variant, whose output goes straight to the host buffer
-    direct_out = False
-    e2e_body()
-    torch.cuda.synchronize()
-    module_out = out_host.clone()
-    direct_out = True
+    # first through the reference-facing module + explicit copies in and out (the reference's calling
+    # pattern), to have its result; then the timed variant on the same q
+    K[:, L - 1].copy_(kv_new_host[0].to(dev))
+    V[:, L - 1].copy_(kv_new_host[1].to(dev))
+    module_out = flash_mod.decode_systematic_batched(q_host[0].to(dev), K, V, S, seed=SEED, want_vrows=False,
+                                                     valid_len=L)[0].cpu()
     out_host.zero_()
-    e2e_body()
+    e2e_body(0)
     torch.cuda.synchronize()
-    assert torch.equal(module_out, out_host), "direct-to-host output differs from the module's output"
-    graph = None
+    assert torch.equal(module_out, out_host), "host-buffer step differs from the module's output"
+    # One CUDA graph per q of the pool (a graph fixes its source address), each holding the whole step;
+    # if capture is not possible the step runs eagerly.
+    graphs = None
     try:
-        graph = graphed(e2e_body, dev)
-        eager_out = out_host.clone()  # from the calls above (same q, same seed)
+        graphs = [graphed(lambda i=i: e2e_body(i), dev) for i in range(QPOOL)]
         out_host.zero_()
-        graph.replay()
+        graphs[0].replay()
         torch.cuda.synchronize()
-        if not torch.equal(eager_out, out_host):
+        if not torch.equal(module_out, out_host):
             raise RuntimeError("graph replay differs from the eager call")
     except Exception as exc:  # noqa: BLE001
-        graph = None
+        graphs = None
         e2e_note = f"eager (graph capture failed: {str(exc)[:80]})"
     else:
-        e2e_note = "cuda graph replay per step; result stored by the merge kernel into the pinned host buffer"
+        e2e_note = ("cuda graph replay per step: one launch reads q and the new k/v rows from pinned host memory "
+                    "(append + q pack), decode, result stored by the merge kernel into the pinned host buffer")
 
     def e2e_step(i):
-        q_stage.copy_(q_host[i % QPOOL])  # host-side write of this step's q into the staging buffer
-        if graph is not None:
-            graph.replay()
+        if graphs is not None:
+            graphs[i % QPOOL].replay()
         else:
-            e2e_body()
+            e2e_body(i % QPOOL)
         torch.cuda.current_stream().synchronize()  # the caller consumes the result every step
 
     te = timed_blocks(e2e_step, steps, 3, world, dev, min_s=0.5)
-    h2d = stage_host.numel() * 2
+    h2d = (q_host[0].numel() + kv_new_host.numel()) * 2
     d2h = out_host.numel() * 2
 
     line = None
@@ -614,11 +603,13 @@ def seq_sharded_extra(dev, rank, world, steps, sharded, ops):
     qp3, K3f, V3f = make_inputs(dev, SEED + 3, batch=1, length=L3)
     # the unsharded result, computed by every rank on the whole sequence before it keeps its shard
     whole = [ops.flash_decode(qp3[i], K3f, V3f, S3, seed=SEED)[0].clone() for i in range(2)]
+    n3 = max(20, steps // 5)
+    # ... and its time on this GPU: the one-GPU reference of the strong-scaling efficiency
+    t1 = timed_blocks(lambda i: ops.flash_decode(qp3[i % QPOOL], K3f, V3f, S3, seed=SEED), n3, 5, world, dev, min_s=0.3)
     K3, V3 = K3f[:, row0:row1].contiguous(), V3f[:, row0:row1].contiguous()
     del K3f, V3f
     torch.cuda.empty_cache()
     gbuf = torch.empty(world, 1, H, 130, device=dev, dtype=torch.float32)
-    n3 = max(20, steps // 5)
     checks = {}
     for i in range(2):
         got = sharded.seq_sharded_flash_decode(qp3[i], K3, V3, S3, SEED, L3, gather_buf=gbuf)[0]
@@ -692,11 +683,13 @@ def seq_sharded_extra(dev, rank, world, steps, sharded, ops):
                           "ms_per_step": t3["ms_per_step"], "k_gbs_total": kb / (t3["ms_per_step"] * 1e-3) / 1e9,
                           "per_rank_ms_per_step": t3["per_rank_ms_per_step"]},
             "peer_exchange": ({"what": "partials stored into every rank's peer-mapped buffer by the merge kernel, "
-                                       "bounded wait + combine kernel; no collective call",
+                                       "which then waits (bounded) for the other ranks' rows and combines; no collective call",
                                "ms_per_step": t3x["ms_per_step"], "k_gbs_total": kb / (t3x["ms_per_step"] * 1e-3) / 1e9,
                                "per_rank_ms_per_step": t3x["per_rank_ms_per_step"],
                                "ms_per_step_graph_replay": t3g["ms_per_step"] if t3g else None} if t3x else x_note),
             "ms_per_step": min(t3["ms_per_step"], t3x["ms_per_step"]) if t3x else t3["ms_per_step"]}
+        res["unsharded_one_gpu_ms_per_step"] = t1["ms_per_step"]
+        res["efficiency_vs_n1"] = t1["ms_per_step"] / (world * res["ms_per_step"])
     del K3, V3, qp3
     torch.cuda.empty_cache()
     return res

@@ -343,7 +343,9 @@ SANTA_API int santa_prop_decode_ragged(const void* q, const void* K, const void*
  *   q_out [B,H,D]                             rotated q, the layout santa_flash_decode reads
  *   seq_lens_out [B] int32 or NULL            position + 1: the lengths for the *_ragged decode calls
  *   status  one int32 in device memory or NULL
- * All tensors in the storage dtype, contiguous, 8-byte aligned; D == 128.
+ * All tensors in the storage dtype, contiguous, 8-byte aligned; D == 128.  q_proj, k_proj and v_proj may
+ * also point into pinned (page-locked, device-mapped) host memory: the kernel reads them over PCIe,
+ * which replaces a separate host-to-device copy of a decode step's inputs.
  */
 SANTA_API int santa_rope_append(const void* q_proj, const void* k_proj, const void* v_proj, int64_t q_stride,
                                 int64_t k_stride, int64_t v_stride, const void* cos, const void* sin, int dtype,

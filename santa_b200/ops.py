@@ -220,14 +220,20 @@ def rope_append(q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, pos, *, seq_
     """Rotary embedding of one new token's q/k, append of k/v to the NHD caches at ``pos`` and the packed
     ``q [B,H,D]`` -- one launch for runtime_common.py:540-556 of the reference.  ``q_proj`` is
     ``[B,H*D]``/``[B,1,H*D]``/``[B,H,D]``, ``k_proj``/``v_proj`` likewise with KVH heads, ``cos``/``sin``
-    ``[B,D]`` or ``[B,1,D]``; ``pos`` is an int or an int32 device tensor ``[B]``.  Returns the rotated q."""
+    ``[B,D]`` or ``[B,1,D]``; ``pos`` is an int or an int32 device tensor ``[B]``.  The three projections
+    may also be pinned host tensors: the kernel then reads them over PCIe, which saves the separate
+    host-to-device copy of a step's inputs.  Returns the rotated q."""
     B, L_storage, KVH, D = k_cache.shape
     _check(D == 128, f"This build supports only D=128. Got D={D}")
     _check(k_cache.shape == v_cache.shape and k_cache.is_contiguous() and v_cache.is_contiguous(),
            "k_cache/v_cache must be contiguous [B,L,KVH,D] tensors of one shape")
-    _check(q_proj.is_cuda and q_proj.dtype in (torch.bfloat16, torch.float16), "q_proj must be a CUDA bf16/f16 tensor")
-    for t in (k_proj, v_proj, cos, sin, k_cache, v_cache):
-        _check(t.dtype == q_proj.dtype and t.device == q_proj.device, "all tensors must share q_proj's dtype and device")
+    dev = k_cache.device
+    _check(k_cache.is_cuda and q_proj.dtype in (torch.bfloat16, torch.float16), "the caches must be CUDA tensors, q_proj bf16/f16")
+    for t in (q_proj, k_proj, v_proj):  # the new token's projections: on the caches' device, or in pinned host memory
+        _check(t.dtype == q_proj.dtype and (t.device == dev or (t.device.type == "cpu" and t.is_pinned())),
+               "q_proj/k_proj/v_proj must share one dtype and live on the caches' device or in pinned host memory")
+    for t in (cos, sin, k_cache, v_cache):
+        _check(t.dtype == q_proj.dtype and t.device == dev, "cos/sin and the caches must share q_proj's dtype and one device")
     _check(q_proj.size(0) == B and q_proj.numel() % (B * D) == 0, "q_proj must hold [B, H*D] elements")
     H = q_proj.numel() // (B * D)
     _check(k_proj.numel() == B * KVH * D and v_proj.numel() == B * KVH * D, "k_proj/v_proj must hold [B, KVH*D] elements")
@@ -240,7 +246,6 @@ def rope_append(q_proj, k_proj, v_proj, cos, sin, k_cache, v_cache, pos, *, seq_
         return t, t.numel() // B
     (q_proj, qs), (k_proj, ks), (v_proj, vs) = rows(q_proj), rows(k_proj), rows(v_proj)
     cos, sin = cos.contiguous(), sin.contiguous()
-    dev = q_proj.device
     pos_dev = None
     if isinstance(pos, torch.Tensor):
         _check(pos.dtype == torch.int32 and pos.device == dev and pos.numel() == B and pos.is_contiguous(),

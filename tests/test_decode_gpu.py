@@ -544,6 +544,14 @@ def test_rope_append_matches_reference_golden(name):
     assert (cases.bits(kc_d[:, pos]) == g["ref_k_row"]).all()
     assert (cases.bits(vc_d[:, pos]) == g["ref_v_row"]).all()
     assert kc_d.float().abs().sum().item() == float(g["ref_k_cache_sum"])
+    # the same with the three projections left in pinned host memory (read by the kernel over PCIe)
+    kc_h, vc_h = kc.to(d), vc.to(d)
+    q_h = ops().rope_append(q_proj.pin_memory(), k_proj.pin_memory(), v_proj.pin_memory(), cos.to(d), sin.to(d),
+                            kc_h, vc_h, pos)
+    torch.cuda.synchronize()
+    assert torch.equal(q_h, q) and torch.equal(kc_h, kc_d) and torch.equal(vc_h, vc_d)
+    with pytest.raises(RuntimeError, match="pinned host memory"):
+        ops().rope_append(q_proj, k_proj.to(d), v_proj.to(d), cos.to(d), sin.to(d), kc_h, vc_h, pos)
     # device positions, one per sequence, with the new lengths written for the attention call
     q_proj, k_proj, v_proj, kc2, vc2 = cases.make_rope_inputs(c)
     plist = [(pos + 3 * b) % c["L"] for b in range(B)]
