@@ -103,6 +103,50 @@ def test_flash_matches_reference_binary(B, L, Ls, KVH, S, seed, dtype, block_n):
         assert (out == 0).all()
 
 
+VALUE_RANGES = [  # kscale, qscale, L, dtype, block_n
+    (0.0, 1.0, 5000, "bf16", 0),     # every score equal: all weights 1
+    (6.0, 1.0, 5000, "bf16", 0),     # scores spread over +-70: most weights underflow (flush-to-zero territory)
+    (6.0, 1.0, 700, "f16", 0),
+    (12.0, 2.0, 3000, "bf16", 0),    # +-270: exp of the whole tile but its maximum is zero
+    (1e-3, 1e-3, 4096, "bf16", 256),  # tiny scores: weights all within an ulp of 1
+]
+
+
+@needs_ref
+@pytest.mark.parametrize("kscale,qscale,L,dtype,block_n", VALUE_RANGES)
+def test_extreme_value_ranges_match_reference_binary(kscale, qscale, L, dtype, block_n):
+    """Score distributions at the edges of the arithmetic (equal scores; weights that underflow, where the
+    Flash build's flush-to-zero and the Prop build's denormals differ; tiny scores): both variants against the
+    reference binary, bit for bit."""
+    q, K, V = cases.make_qkv(2, L, 2, dtype, 900 + L, kscale, False)
+    q = (q.float() * qscale).to(q.dtype)
+    q, K, V = q.to(dev()), K.to(dev()), V.to(dev())
+    S, seed = 128, 77
+    out, m_star, vrows, tr = ops().flash_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True, trace=True)
+    ref_counts, _ = ref_gpu.flash_counts(q, K, S, seed=seed, block_n=block_n)
+    r = ref_gpu.flash_decode(q, K, V, S, seed=seed, block_n=block_n, want_vrows=True)
+    torch.cuda.synchronize()
+    assert ops().workspace_status("flash", dev()) == 0
+    assert (tr.counts.int() == ref_counts).all()
+    assert bits_eq(tr.m_tiles, r.m_tiles) and bits_eq(tr.ell_tiles, r.ell_tiles) and bits_eq(m_star, r.m_star)
+    assert (vrows == r.vrows).all() and close(out, r.out)
+    for b in range(2):
+        po, pm, pv, pt = ops().prop_decode(q[b], K[b], V[b], S, seed=seed, block_n=block_n, want_vrows=True, trace=True)
+        pr = ref_gpu.prop_decode(q[b], K[b], V[b], S, seed=seed, block_n=block_n, want_vrows=True)
+        torch.cuda.synchronize()
+        assert ops().workspace_status("prop", dev()) == 0
+        assert bits_eq(pt.m_tiles, pr.m_tiles) and bits_eq(pt.ell_tiles, pr.ell_tiles) and bits_eq(pm, pr.m_star)
+        assert (pt.u16 == pr.u_stash.view(torch.int16).t()).all()
+        dS = (pt.S_tiles - pr.S_tiles).abs()     # the reference's Z is an unordered atomic sum
+        assert dS.max().item() <= 1
+        if dS.max().item() == 0:
+            assert bits_eq(pt.invdelta, pr.invdelta) and (pv == pr.vrows).all()
+            if L <= 4096:
+                rc, _ = ref_gpu.prop_counts(q[b], K[b], S, seed=seed, block_n=block_n)
+                assert (pt.counts.int() == rc).all()
+        assert close(po, pr.out)
+
+
 @pytest.mark.parametrize("name", list(cases.FLASH_CASES))
 def test_flash_matches_golden_and_oracle(name):
     """No reference build needed: golden fixtures (from the reference kernels) + CPU oracle."""
