@@ -310,6 +310,76 @@ __device__ __forceinline__ void build_item_starts(const int* __restrict__ seq_le
   if (lane == 0) start[nseq] = carry;
 }
 
+// ---------------------------------------------------------------- weighted split (Prop, second pass)
+// A (kv-head, tile) unit of Prop's second pass costs more in a short sequence than in a long one: the
+// budget S is spread over fewer tiles, so every tile holds more samples (more rows to gather, no head
+// without a budget).  Measured on uniform batches at S = 256, per unit and warp with all warps busy:
+// 11.4 / 8.0 / 6.3 / 5.5 us at 32 / 64 / 128 / 256 tiles, i.e. about 4.9 + 0.8 * S / T.  A ragged
+// batch is therefore cut into ranges of equal WEIGHT, not of equal item count: every item of a
+// sequence of T tiles weighs prop_unit_weight(T, S), item k of sequence b starts at weight
+// wstart[b] + k * w_b, and range i owns the items whose start lies in [lo(i), lo(i + 1)) with
+// lo(i) = floor(i * W / ranges) -- range_lo / cta_of_item in weight space.  With no more than
+// W / max_b(w_b) ranges every range holds at least one item.
+__host__ __device__ __forceinline__ int prop_unit_weight(int T, long long S) {
+  if (T <= 0) return 49;
+  long long r = S > 0 ? (8 * S + T / 2) / T : 0;
+  if (r > 512) r = 512;
+  return int(49 + r);
+}
+
+// Built by one full warp: wstart[b] = weight before sequence b (nseq + 1 entries); returns the largest
+// weight of a sequence that has items (0 if none has).
+__device__ __forceinline__ int build_weight_starts(const int* __restrict__ seq_lens, int nseq, int max_len, int bn,
+                                                   int groups_per_seq, long long S, long long* wstart, int lane) {
+  long long carry = 0;
+  int wmax = 0;
+  for (int base = 0; base < nseq; base += 32) {
+    const int b = base + lane;
+    long long n = 0;
+    if (b < nseq) {
+      const int T = (ragged_len(seq_lens, b, max_len) + bn - 1) / bn;
+      const int w = prop_unit_weight(T, S);
+      n = (long long)T * groups_per_seq * w;
+      if (T > 0) wmax = wmax > w ? wmax : w;
+    }
+    long long incl = n;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const long long t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (b < nseq) wstart[b] = carry + incl - n;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) wstart[nseq] = carry;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const int o = __shfl_xor_sync(0xffffffffu, wmax, off);
+    wmax = wmax > o ? wmax : o;
+  }
+  return wmax;
+}
+
+// The first item whose weight start is >= wpos (0 <= wpos <= wstart[nseq]).
+__device__ __forceinline__ long long item_at_weight(const int* start, const long long* wstart, int nseq, long long wpos,
+                                                    const int* __restrict__ seq_lens, int max_len, int bn,
+                                                    long long S) {
+  int lo = 0, hi = nseq;  // the largest b < nseq with wstart[b] <= wpos
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (wstart[mid] <= wpos)
+      lo = mid;
+    else
+      hi = mid;
+  }
+  const int n_b = start[lo + 1] - start[lo];
+  const int T = (ragged_len(seq_lens, lo, max_len) + bn - 1) / bn;
+  const int w = prop_unit_weight(T, S);
+  long long k = (wpos - wstart[lo] + w - 1) / w;
+  if (k > n_b) k = n_b;
+  return (long long)start[lo] + k;
+}
+
 // The sequence owning item `it` (0 <= it < start[nseq]): the largest b with start[b] <= it.
 __device__ __forceinline__ int seq_of_item(const int* start, int nseq, int it) {
   int lo = 0, hi = nseq;

@@ -281,6 +281,7 @@ struct Pass2Params {
   int* partial_vrows;       // [nvg + columns]
   long long partial_slots;  // nvg + columns (the checked build compares slots with it)
   int* status;              // the call's status word
+  long long S;              // the per-head budget: enters the weights of a ragged batch's split
   int16_t* dbg_c;           // [nseq,H,len_stride] or null
   int* rowmask;             // [nseq,KVH,len_stride] or null
 };
@@ -312,22 +313,42 @@ template <typename TK>
 __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_kernel(const Pass2Params p) {
   extern __shared__ __align__(16) unsigned char s_dyn[];
   __shared__ int s_start[kMaxRaggedSeqs + 1];
+  __shared__ long long s_wstart[kMaxRaggedSeqs + 1];
+  __shared__ int s_wmax;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool ragged = p.seq_lens != nullptr;
   if (ragged) {  // lengths are inputs of the call, not results of the preceding kernels
     if (warp == 0) build_item_starts(p.seq_lens, p.nseq, p.L, p.bn, p.KVH, s_start, lane);
+    if (warp == 1) {
+      const int wmax = build_weight_starts(p.seq_lens, p.nseq, p.L, p.bn, p.KVH, p.S, s_wstart, lane);
+      if (lane == 0) s_wmax = wmax;
+    }
     __syncthreads();
   }
   cudaGridDependencySynchronize();
   long long items = p.ws.items;
   int nvg = p.ws.nvg;
-  if (ragged) {
+  if (ragged) {  // ranges of equal weight, never more than hold an item each
     items = s_start[p.nseq];
-    nvg = (items < (long long)nvg) ? int(items) : nvg;
+    const long long fit = s_wmax > 0 ? s_wstart[p.nseq] / s_wmax : 0;
+    nvg = (fit < (long long)nvg) ? int(fit) : nvg;
   }
-  const int vg = blockIdx.x * kPass2Warps + warp;
+  // The item ranges are dealt to the warps with a stride of the grid: the eight warps of a CTA (and
+  // the CTAs that share an SM) work on ranges spread over the whole batch.  Ranges differ in cost --
+  // a short sequence puts several samples into every tile, a long one leaves tiles empty -- and with
+  // neighbouring ranges in one CTA the SMs that drew the expensive sequences ran half as long again
+  // as the average.  Which warp runs a range does not change any result.
+  const int vg = warp * int(gridDim.x) + int(blockIdx.x);
   if (vg >= nvg) return;
-  const long long lo = range_lo(vg, items, nvg), hi = range_lo(vg + 1, items, nvg);
+  long long lo, hi;
+  if (ragged) {
+    const long long W = s_wstart[p.nseq];
+    lo = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg, W, nvg), p.seq_lens, p.L, p.bn, p.S);
+    hi = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg + 1, W, nvg), p.seq_lens, p.L, p.bn, p.S);
+  } else {
+    lo = range_lo(vg, items, nvg);
+    hi = range_lo(vg + 1, items, nvg);
+  }
   float4* sb = reinterpret_cast<float4*>(s_dyn + size_t(warp) * kPass2WarpSmem);
   uint2* raw = reinterpret_cast<uint2*>(s_dyn + size_t(warp) * kPass2WarpSmem + kMaxTileRows * 16);
   float* par = reinterpret_cast<float*>(s_dyn + size_t(warp) * kPass2WarpSmem + kMaxTileRows * 16 + kPass2RawBytes);
@@ -459,6 +480,7 @@ struct PropMergeParams {
   int nseq, max_len, bn;
   WorkSplit ws;
   float scale;   // 1/S, or 0 when S <= 0 (santa_cuda.cpp:333)
+  long long S;   // the per-head budget (weights of a ragged batch's split)
   void* out;     // [nseq,H,128]
   int* vrows;    // [nseq,KVH] or null
 };
@@ -471,45 +493,68 @@ template <typename TK>
 __global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const PropMergeParams p) {
   __shared__ float4 s_acc[kMergeWarps][32];
   __shared__ int s_vr[kMergeWarps];
-  __shared__ int s_before[kMergeWarps], s_total[kMergeWarps];
+  __shared__ int s_before[kMergeWarps], s_total[kMergeWarps], s_wmx[kMergeWarps];
+  __shared__ long long s_wbefore[kMergeWarps], s_wtotal[kMergeWarps];
   const int col = blockIdx.x >> 2;  // (sequence, kv-head)
   const int kv = col, g = blockIdx.x & 3, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   long long items = p.ws.items, item0 = (long long)col * p.T_c;
   int nvg = p.ws.nvg, T_b = p.T_c;
+  long long item_last = item0 + T_b - 1;
   if (p.seq_lens != nullptr) {
     // item range of this column: tiles of the sequences before it, times KVH, plus its own offset
     const int b = col / p.KVH, kvb = col - b * p.KVH;
-    int before = 0, total = 0;
+    // ... and the same in weight space, in which the second pass cut its ranges (prop_unit_weight)
+    int before = 0, total = 0, wmx = 0;
+    long long wbefore = 0, wtotal = 0;
     for (int i = threadIdx.x; i < p.nseq; i += kMergeWarps * 32) {
       const int t = (ragged_len(p.seq_lens, i, p.max_len) + p.bn - 1) / p.bn;
+      const int wi = prop_unit_weight(t, p.S);
       total += t;
       before += (i < b) ? t : 0;
+      wtotal += (long long)t * wi;
+      wbefore += (i < b) ? (long long)t * wi : 0;
+      if (t > 0) wmx = wmx > wi ? wmx : wi;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
       before += __shfl_xor_sync(0xffffffffu, before, off);
       total += __shfl_xor_sync(0xffffffffu, total, off);
+      wbefore += __shfl_xor_sync(0xffffffffu, wbefore, off);
+      wtotal += __shfl_xor_sync(0xffffffffu, wtotal, off);
+      const int o = __shfl_xor_sync(0xffffffffu, wmx, off);
+      wmx = wmx > o ? wmx : o;
     }
     if (lane == 0) {
       s_before[w] = before;
       s_total[w] = total;
+      s_wbefore[w] = wbefore;
+      s_wtotal[w] = wtotal;
+      s_wmx[w] = wmx;
     }
     __syncthreads();
-    before = total = 0;
+    before = total = wmx = 0;
+    wbefore = wtotal = 0;
     for (int k = 0; k < kMergeWarps; ++k) {
       before += s_before[k];
       total += s_total[k];
+      wbefore += s_wbefore[k];
+      wtotal += s_wtotal[k];
+      wmx = wmx > s_wmx[k] ? wmx : s_wmx[k];
     }
     T_b = (ragged_len(p.seq_lens, b, p.max_len) + p.bn - 1) / p.bn;
-    items = (long long)total * p.KVH;
-    nvg = (items < (long long)nvg) ? int(items) : nvg;
-    item0 = (long long)before * p.KVH + (long long)kvb * T_b;
+    const long long w_b = prop_unit_weight(T_b, p.S);
+    // weight starts of the column's first and last item; the item totals become weight totals
+    items = wtotal * p.KVH;
+    const long long fit = wmx > 0 ? items / wmx : 0;
+    nvg = (fit < (long long)nvg) ? int(fit) : nvg;
+    item0 = wbefore * p.KVH + (long long)kvb * T_b * w_b;
+    item_last = item0 + (long long)(T_b - 1) * w_b;
   }
   cudaGridDependencySynchronize();
   int v_first = 0, v_last = -1;  // an empty sequence contributes nothing
   if (T_b > 0) {
     v_first = cta_of_item(item0, items, nvg);
-    v_last = cta_of_item(item0 + T_b - 1, items, nvg);
+    v_last = cta_of_item(item_last, items, nvg);
   }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int v0 = v_first + w; v0 <= v_last; v0 += 4 * kMergeWarps) {
@@ -822,6 +867,7 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   p2.partial_vrows = p.partial_vrows;
   p2.partial_slots = max_warps + (long long)nseq * KVH;
   p2.status = p.sp.status;
+  p2.S = p.S;
   p2.dbg_c = p.dbg_c;
   p2.rowmask = p.rowmask;
   const int grid2 = (p2.ws.nvg + kPass2Warps - 1) / kPass2Warps;
@@ -844,6 +890,7 @@ static cudaError_t launch_prop_t(const PropParams& p, int grid, cudaStream_t str
   pm.bn = p.block_n;
   pm.ws = p2.ws;
   pm.scale = (p.S > 0) ? (1.0f / (float)p.S) : 0.0f;
+  pm.S = p.S;
   pm.out = p.out;
   pm.vrows = p.vrows;
   return launch_dependent(prop_merge_kernel<TK>, dim3(nseq * KVH * kGH), dim3(kMergeWarps * 32), 0, stream, pm);
