@@ -428,6 +428,9 @@ RAGGED_SETS = [
     ([300, 5000, 1, 777, 4096], 5120, 256, "bf16", 8),
     ([256, 0, 513], 600, 64, "f16", 2),
     ([8769, 23132, 11428, 9000], 23132, 256, "bf16", 8),
+    # very unequal lengths: the second pass cuts its ranges by weight (a unit of a short sequence costs more)
+    ([8192, 0, 65536, 300, 9000, 256, 1, 40000], 65536, 32, "bf16", 2),
+    ([300, 60000, 700, 512, 33000], 60000, 2048, "f16", 2),
 ]
 
 
