@@ -360,10 +360,10 @@ __device__ __forceinline__ int build_weight_starts(const int* __restrict__ seq_l
   return wmax;
 }
 
-// The first item whose weight start is >= wpos (0 <= wpos <= wstart[nseq]).
-__device__ __forceinline__ long long item_at_weight(const int* start, const long long* wstart, int nseq, long long wpos,
-                                                    const int* __restrict__ seq_lens, int max_len, int bn,
-                                                    long long S) {
+// The first item whose weight start is >= wpos (0 <= wpos <= wstart[nseq]); `start` / `wstart` are the
+// item and weight prefixes over the sequences, each of which has groups_per_seq items per tile.
+__host__ __device__ __forceinline__ long long item_at_weight(const int* start, const long long* wstart, int nseq,
+                                                             long long wpos, int groups_per_seq, long long S) {
   int lo = 0, hi = nseq;  // the largest b < nseq with wstart[b] <= wpos
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -373,8 +373,7 @@ __device__ __forceinline__ long long item_at_weight(const int* start, const long
       hi = mid;
   }
   const int n_b = start[lo + 1] - start[lo];
-  const int T = (ragged_len(seq_lens, lo, max_len) + bn - 1) / bn;
-  const int w = prop_unit_weight(T, S);
+  const int w = prop_unit_weight(n_b / groups_per_seq, S);
   long long k = (wpos - wstart[lo] + w - 1) / w;
   if (k > n_b) k = n_b;
   return (long long)start[lo] + k;

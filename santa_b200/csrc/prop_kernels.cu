@@ -343,8 +343,8 @@ __global__ void __launch_bounds__(kPass2Warps * 32, kPass2CtasPerSm) prop_pass2_
   long long lo, hi;
   if (ragged) {
     const long long W = s_wstart[p.nseq];
-    lo = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg, W, nvg), p.seq_lens, p.L, p.bn, p.S);
-    hi = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg + 1, W, nvg), p.seq_lens, p.L, p.bn, p.S);
+    lo = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg, W, nvg), p.KVH, p.S);
+    hi = item_at_weight(s_start, s_wstart, p.nseq, range_lo(vg + 1, W, nvg), p.KVH, p.S);
   } else {
     lo = range_lo(vg, items, nvg);
     hi = range_lo(vg + 1, items, nvg);

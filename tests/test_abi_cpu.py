@@ -159,3 +159,18 @@ def test_library_is_self_contained():
     funcs = [ln.split()[-1] for ln in syms if " T " in ln]
     assert funcs and all(f.startswith("santa_") for f in funcs), funcs
     assert sorted(funcs) == sorted(capi.EXPORTS)
+
+
+def test_work_split_arithmetic_of_the_kernels(tmp_path):
+    """tests/split_host.cu compiles the kernels' own split functions (csrc/common.cuh) as host code and
+    checks on random ragged batches that the weighted ranges of Prop's second pass tile the items exactly
+    once, that none is empty, and that the merge kernel finds the owning range of every column."""
+    import shutil
+    import subprocess
+    if shutil.which("nvcc") is None:
+        pytest.skip("no nvcc on this machine")
+    exe = str(tmp_path / "split_host")
+    subprocess.check_call(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O1", "-std=c++17", "-o", exe,
+                           os.path.join(ROOT, "tests", "split_host.cu")])
+    txt = subprocess.check_output([exe], text=True, timeout=300)
+    assert txt.startswith("ok "), txt
