@@ -29,6 +29,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -577,6 +578,10 @@ def main():
         if rank == 0:
             line["e2e_llama8b_decode"] = res4
 
+    # ---- extra: the reference's CPU-runnable case (B=1, L=4096, S=32) on the GPU: a latency figure ---
+    if world == 1:
+        line["config0_b1_l4096"] = config0_extra(dev, steps, args)
+
     if rank == 0:
         if world == 1:
             line["cpu_baseline"] = cpu_dense_baseline()
@@ -591,6 +596,35 @@ def main():
 
         dist.barrier()
         dist.destroy_process_group()
+
+
+def config0_extra(dev, steps, args):
+    """B=1, L=4096, S=32, seed 1690 (K scaled by 1/sqrt(D)): the case the reference can run on a CPU.  The
+    16 MiB of K and V stay in L2, so this is the latency of one call, replayed from a CUDA graph; the
+    reference's kernels are timed the same way beside it."""
+    from santa_b200 import ops
+
+    g = torch.Generator().manual_seed(SEED)
+    q0 = torch.randn(1, H, D, generator=g).to(torch.bfloat16).to(dev)
+    K0 = (torch.randn(1, 4096, KVH, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).to(dev)
+    V0 = torch.randn(1, 4096, KVH, D, generator=g).to(torch.bfloat16).to(dev)
+    o0 = torch.empty(1, H, D, device=dev, dtype=torch.bfloat16)
+    n0 = max(50, steps)
+    g0 = graphed(lambda: ops.flash_decode(q0, K0, V0, 32, seed=SEED, out=o0), dev)
+    t0 = timed_blocks(lambda i: g0.replay(), n0, 5, 1, dev, min_s=0.2)
+    res = {"workload": "santa_flash B=1 Hq=32 Hkv=8 D=128 L=4096 S=32 seed=1690 bf16 (L2-resident: a latency figure)",
+           "ms_per_step": t0["ms_per_step"], "steps_per_s": 1e3 / t0["ms_per_step"], "how": "cuda graph replay"}
+    if not args.no_ref_kernels:
+        from oracle import ref_gpu
+        if ref_gpu.available():
+            r = ref_gpu.flash_decode(q0, K0, V0, 32, seed=SEED)
+            res["out_vs_reference_kernels_max_abs"] = (r.out.float() - o0.float()).abs().max().item()
+            gr = graphed(lambda: ref_gpu.flash_decode(q0, K0, V0, 32, seed=SEED), dev)
+            tr = timed_blocks(lambda i: gr.replay(), n0, 5, 1, dev, min_s=0.2)
+            res["reference_cuda_kernels_ms_per_step"] = tr["ms_per_step"]
+            del gr
+    del g0
+    return res
 
 
 def seq_sharded_extra(dev, rank, world, steps, sharded, ops):
