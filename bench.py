@@ -574,7 +574,8 @@ def main():
 
     # ---- extra: end-to-end decode of a Llama-3.1-8B-shaped model -----------------------------------
     if not args.no_e2e_model:
-        res4 = e2e_model_decode(dev, args.e2e_model_batch, world, prefill=args.e2e_prefill)
+        res4 = e2e_model_decode(dev, args.e2e_model_batch, world, prefill=args.e2e_prefill,
+                                tensor_mode=not args.no_tensor_mode)
         if rank == 0:
             line["e2e_llama8b_decode"] = res4
 
@@ -832,7 +833,7 @@ def prop_extra(dev, rank, world, steps, args):
     return res
 
 
-def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefill=False):
+def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefill=False, tensor_mode=True):
     """Random-init (seed 0) Llama-3.1-8B-shaped decoder, `batch` sequences with `prompt_len` cached tokens
     each, `new_tokens` greedy tokens with santa_flash S=256; one replica per GPU.  By default the caches
     are filled with seeded N(0,1) values instead of running the prefill (random weights: the prefill
@@ -896,6 +897,20 @@ def e2e_model_decode(dev, batch, world, prompt_len=32768, new_tokens=128, prefil
             "attention_k_gbs": kv_bytes / (attn_ms * 1e-3) / 1e9,
             "hbm_gb_allocated": torch.cuda.max_memory_allocated(dev) / 1e9,
             "device_status_word": res["device_status_word"]})
+        if tensor_mode:   # the same generation with the opt-in tensor-core scores in every attention call
+            rt.score_mode = 1
+            rt.capture(prompt_len + new_tokens)
+            rt.generate(first, prompt_len, 4)
+            if world > 1:
+                dist.barrier()
+            res1 = rt.generate(first, prompt_len, new_tokens)
+            t = torch.tensor([res1["decode_time_s"]], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out["tensor_score_mode"] = {
+                "tokens_per_s": world * res1["timed_generated_tokens"] / float(t.item()),
+                "ms_per_step_graph": float(t.item()) / max(1, res1["steps_sampled"] - 1) * 1e3,
+                "device_status_word": res1["device_status_word"]}
         del rt
     except torch.OutOfMemoryError as exc:
         out["error"] = f"out of device memory: {str(exc)[:120]}"

@@ -76,7 +76,7 @@ class SDPABackend(DecodeAttentionBackend):
 class _SantaBackend(DecodeAttentionBackend):
     module_name = ""
 
-    def __init__(self, *, S: int, seed: int, block_n: Optional[int] = None) -> None:
+    def __init__(self, *, S: int, seed: int, block_n: Optional[int] = None, score_mode: int = 0) -> None:
         import santa_b200
         santa_b200.enable_dropin()
         import importlib
@@ -86,12 +86,16 @@ class _SantaBackend(DecodeAttentionBackend):
             raise BackendError(f"Could not import the {self.name} extension module {self.module_name}: {exc}")
         self.S, self.seed = int(S), int(seed)
         self.block_n = None if block_n is None else int(block_n)
+        # 0: the reference's score arithmetic (sampled rows equal the reference's); 1: the opt-in
+        # tensor-core scores.  Passed on only when set, so the default call is the reference adapter's.
+        self._mode_kw = {"score_mode": int(score_mode)} if int(score_mode) != 0 else {}
         self.actual_mode = "unknown"
         self.supports_true_batch_decode = hasattr(self.module, "decode_systematic_batched")
 
     def info(self) -> Dict[str, Any]:
         return {**super().info(), "module": self.module_name, "requested_S": self.S, "seed": self.seed,
-                "block_n": self.block_n, "actual_mode": self.actual_mode}
+                "block_n": self.block_n, "actual_mode": self.actual_mode,
+                "score_mode": self._mode_kw.get("score_mode", 0)}
 
     @staticmethod
     def _lengths(valid_len, B, device):
@@ -109,18 +113,19 @@ class SantaFlashBackend(_SantaBackend):
         if isinstance(valid_len, torch.Tensor):   # per-sequence lengths on the device
             self.actual_mode = "batch_ragged"
             return self.module.decode_systematic_ragged(q_bhd, k_nhd, v_nhd, valid_len, self.S, seed=self.seed,
-                                                        block_n=bn, want_vrows=False)[0]
+                                                        block_n=bn, want_vrows=False, **self._mode_kw)[0]
         self.actual_mode = "batch"
         return self.module.decode_systematic_batched(q_bhd, k_nhd, v_nhd, self.S, seed=self.seed, block_n=bn,
-                                                     want_vrows=False, valid_len=int(valid_len))[0]
+                                                     want_vrows=False, valid_len=int(valid_len), **self._mode_kw)[0]
 
 
 class SantaPropBackend(_SantaBackend):
     name = "santa_prop"
     module_name = "santa_prop_batch_cuda"
 
-    def __init__(self, *, S: int, seed: int, block_n: Optional[int] = None, loop: bool = False) -> None:
-        super().__init__(S=S, seed=seed, block_n=block_n)
+    def __init__(self, *, S: int, seed: int, block_n: Optional[int] = None, loop: bool = False,
+                 score_mode: int = 0) -> None:
+        super().__init__(S=S, seed=seed, block_n=block_n, score_mode=score_mode)
         self.loop = bool(loop)
 
     def decode(self, q_bhd, k_nhd, v_nhd, valid_len):
@@ -135,11 +140,11 @@ class SantaPropBackend(_SantaBackend):
             self.actual_mode = "batch_ragged"
             lens = self._lengths(valid_len, B, q_bhd.device)
             return self.module.decode_systematic_ragged(q_bhd, k_nhd, v_nhd, lens, self.S, seed=self.seed,
-                                                        want_vrows=False)[0]
+                                                        want_vrows=False, **self._mode_kw)[0]
         # the reference adapter's per-sequence loop over contiguous prefixes
         self.actual_mode = "single_loop_fallback"
         lens = [int(n) for n in valid_len.tolist()] if isinstance(valid_len, torch.Tensor) else [int(valid_len)] * B
-        kw = {} if self.block_n is None else {"block_n": self.block_n}
+        kw = dict(self._mode_kw) if self.block_n is None else {"block_n": self.block_n, **self._mode_kw}
         outs = [self.module.decode_systematic_scalar(q_bhd[b].contiguous(), k_nhd[b, :lens[b]].contiguous(),
                                                      v_nhd[b, :lens[b]].contiguous(), self.S, seed=self.seed,
                                                      want_vrows=False, **kw)[0] for b in range(B)]
@@ -147,12 +152,12 @@ class SantaPropBackend(_SantaBackend):
 
 
 def make_backend(name: str, *, santa_s: int = 256, santa_seed: int = 1690,
-                 santa_block_n: Optional[int] = None) -> DecodeAttentionBackend:
+                 santa_block_n: Optional[int] = None, score_mode: int = 0) -> DecodeAttentionBackend:
     """Backend by the reference's names: "sdpa", "santa_flash", "santa_prop"."""
     if name == "sdpa":
         return SDPABackend()
     if name == "santa_flash":
-        return SantaFlashBackend(S=santa_s, seed=santa_seed, block_n=santa_block_n)
+        return SantaFlashBackend(S=santa_s, seed=santa_seed, block_n=santa_block_n, score_mode=score_mode)
     if name == "santa_prop":
-        return SantaPropBackend(S=santa_s, seed=santa_seed, block_n=santa_block_n)
+        return SantaPropBackend(S=santa_s, seed=santa_seed, block_n=santa_block_n, score_mode=score_mode)
     raise BackendError(f"unknown backend {name!r} (this package provides sdpa, santa_flash, santa_prop)")

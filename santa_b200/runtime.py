@@ -55,7 +55,7 @@ class DecodeRuntime:
 
     def __init__(self, shape: LlamaShape, batch: int, total_len: int, device, *, dtype=torch.bfloat16,
                  weight_seed: int = 0, attention: str = "santa_flash", S: int = 256, attn_seed: int = 1690,
-                 block_n: int = 0, init_std: float = 0.02):
+                 block_n: int = 0, init_std: float = 0.02, score_mode: int = 0):
         if shape.head_dim != 128 or shape.heads != 4 * shape.kv_heads:
             raise RuntimeError("This build supports only D=128 and GH=4 (H/KVH)")
         if attention not in ("santa_flash", "santa_prop", "sdpa"):
@@ -63,6 +63,7 @@ class DecodeRuntime:
         self.shape, self.B, self.T = shape, int(batch), int(total_len)
         self.dev, self.dtype = torch.device(device), dtype
         self.attention, self.S, self.attn_seed, self.block_n = attention, int(S), int(attn_seed), int(block_n)
+        self.score_mode = int(score_mode)  # 0: the reference's score arithmetic; 1: opt-in tensor-core scores
         s, g = shape, torch.Generator(device=self.dev).manual_seed(weight_seed)
 
         def w(*size):
@@ -200,11 +201,12 @@ class DecodeRuntime:
         if self.attention == "santa_flash":
             return self._flash.decode_systematic_ragged(q_bhd, self.k_cache[li], self.v_cache[li], self.seq_lens,
                                                         self.S, seed=self.attn_seed, block_n=self._bn,
-                                                        want_vrows=False, max_len=max_len)[0]
+                                                        want_vrows=False, max_len=max_len,
+                                                        score_mode=self.score_mode)[0]
         if self.attention == "santa_prop":
             return self._prop.decode_systematic_ragged(q_bhd, self.k_cache[li], self.v_cache[li], self.seq_lens,
                                                        self.S, seed=self.attn_seed, want_vrows=False,
-                                                       max_len=max_len)[0]
+                                                       max_len=max_len, score_mode=self.score_mode)[0]
         # dense reference backend over the valid prefix (host-known bound; eager only)
         L = int(max_len)
         kk = self.k_cache[li][:, :L].permute(0, 2, 1, 3)

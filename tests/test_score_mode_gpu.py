@@ -87,3 +87,12 @@ def test_ragged_and_prop_entries_take_the_tensor_mode():
     assert torch.equal(t, sb[0])
     with pytest.raises(TypeError):
         fm.decode_systematic_batched(q, K, V, 256, 5, 0, False, -1, 1)      # keyword-only
+    # the backend objects and the decode runtime pass the switch on; unset, they make the reference's call
+    from santa_b200 import backends
+    fb0, fb1 = backends.make_backend("santa_flash", santa_s=256, santa_seed=5), \
+        backends.make_backend("santa_flash", santa_s=256, santa_seed=5, score_mode=1)
+    assert torch.equal(fb0.decode(q, K, V, 9000), e) and torch.equal(fb1.decode(q, K, V, 9000), t0 := fm.decode_systematic_batched(q, K, V, 256, seed=5, score_mode=1)[0])
+    assert fb0.info()["score_mode"] == 0 and fb1.info()["score_mode"] == 1 and not torch.equal(e, t0)
+    pb1 = backends.make_backend("santa_prop", santa_s=256, santa_seed=5, score_mode=1)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=dev())
+    assert torch.equal(pb1.decode(q, K, V, lens_t), pb[0])
