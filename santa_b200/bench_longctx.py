@@ -35,6 +35,8 @@ def parse_args(argv=None):
     ap.add_argument("--santa-s", type=int, default=256)
     ap.add_argument("--santa-seed", type=int, default=1690)
     ap.add_argument("--santa-block-n", type=int, default=0)
+    ap.add_argument("--score-mode", type=int, default=0, choices=[0, 1],
+                    help="0: the reference's score arithmetic (default); 1: the opt-in tensor-core scores")
     ap.add_argument("--warmup-runs", type=int, default=1)
     ap.add_argument("--timed-runs", type=int, default=3)
     ap.add_argument("--seed", type=int, default=0)
@@ -88,7 +90,7 @@ def main(argv=None) -> None:
     for backend in args.backends:
         rt = DecodeRuntime(shape, args.batch_size, args.prompt_len + args.max_new_tokens, dev, attention=backend,
                            S=args.santa_s, attn_seed=args.santa_seed, block_n=args.santa_block_n,
-                           weight_seed=args.seed)
+                           weight_seed=args.seed, score_mode=args.score_mode)
         for phase, runs in (("warmup", args.warmup_runs), ("timed", args.timed_runs)):
             for run_idx in range(runs):
                 rows = []
