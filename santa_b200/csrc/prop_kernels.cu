@@ -493,7 +493,7 @@ template <typename TK>
 __global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const PropMergeParams p) {
   __shared__ float4 s_acc[kMergeWarps][32];
   __shared__ int s_vr[kMergeWarps];
-  __shared__ int s_before[kMergeWarps], s_total[kMergeWarps], s_wmx[kMergeWarps];
+  __shared__ int s_wmx[kMergeWarps];
   __shared__ long long s_wbefore[kMergeWarps], s_wtotal[kMergeWarps];
   const int col = blockIdx.x >> 2;  // (sequence, kv-head)
   const int kv = col, g = blockIdx.x & 3, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -501,49 +501,42 @@ __global__ void __launch_bounds__(kMergeWarps * 32) prop_merge_kernel(const Prop
   int nvg = p.ws.nvg, T_b = p.T_c;
   long long item_last = item0 + T_b - 1;
   if (p.seq_lens != nullptr) {
-    // item range of this column: tiles of the sequences before it, times KVH, plus its own offset
+    // The second pass cut its ranges in weight space (prop_unit_weight): this column's place there is
+    // the weight of the sequences before it, times KVH, plus its own offset.
     const int b = col / p.KVH, kvb = col - b * p.KVH;
-    // ... and the same in weight space, in which the second pass cut its ranges (prop_unit_weight)
-    int before = 0, total = 0, wmx = 0;
+    int wmx = 0;
     long long wbefore = 0, wtotal = 0;
     for (int i = threadIdx.x; i < p.nseq; i += kMergeWarps * 32) {
       const int t = (ragged_len(p.seq_lens, i, p.max_len) + p.bn - 1) / p.bn;
       const int wi = prop_unit_weight(t, p.S);
-      total += t;
-      before += (i < b) ? t : 0;
       wtotal += (long long)t * wi;
       wbefore += (i < b) ? (long long)t * wi : 0;
       if (t > 0) wmx = wmx > wi ? wmx : wi;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
-      before += __shfl_xor_sync(0xffffffffu, before, off);
-      total += __shfl_xor_sync(0xffffffffu, total, off);
       wbefore += __shfl_xor_sync(0xffffffffu, wbefore, off);
       wtotal += __shfl_xor_sync(0xffffffffu, wtotal, off);
       const int o = __shfl_xor_sync(0xffffffffu, wmx, off);
       wmx = wmx > o ? wmx : o;
     }
     if (lane == 0) {
-      s_before[w] = before;
-      s_total[w] = total;
       s_wbefore[w] = wbefore;
       s_wtotal[w] = wtotal;
       s_wmx[w] = wmx;
     }
     __syncthreads();
-    before = total = wmx = 0;
+    wmx = 0;
     wbefore = wtotal = 0;
     for (int k = 0; k < kMergeWarps; ++k) {
-      before += s_before[k];
-      total += s_total[k];
       wbefore += s_wbefore[k];
       wtotal += s_wtotal[k];
       wmx = wmx > s_wmx[k] ? wmx : s_wmx[k];
     }
     T_b = (ragged_len(p.seq_lens, b, p.max_len) + p.bn - 1) / p.bn;
     const long long w_b = prop_unit_weight(T_b, p.S);
-    // weight starts of the column's first and last item; the item totals become weight totals
+    // from here on `items`, `item0` and `item_last` are weights: the total and the weight starts of
+    // the column's first and last item
     items = wtotal * p.KVH;
     const long long fit = wmx > 0 ? items / wmx : 0;
     nvg = (fit < (long long)nvg) ? int(fit) : nvg;
