@@ -127,6 +127,89 @@ __global__ void prop_pass1_mma_kernel(const TK* __restrict__ Q, const TK* __rest
 }
 
 // ------------------------------------------------------------------ budgets
+// The bitonic network of the budgets kernel on up to 256 keys, run by ONE warp in registers instead of
+// by the CTA in shared memory with a barrier per stage (36 stages for 256 keys).  Lane l holds the
+// elements l*R .. l*R+R-1 of the N = 32*R positions (R = 1 also serves N < 32).  Same comparators in
+// the same order as the shared-memory form below: pair (i, i^j) with i < i^j, direction from bit k of
+// i, swap iff (a_i > a_j) == up; positions >= T_c are virtual -- they read as (-inf, -1) and whatever
+// a comparator would have put there is dropped -- so they are reset after every stage.
+template <int R>
+__device__ __forceinline__ void warp_bitonic(float (&f)[R], int (&ix)[R], int N, int T_c, int lane) {
+#pragma unroll 1
+  for (int k = 2; k <= N; k <<= 1) {
+    // stages whose partner sits in another lane (lane ^ (j / R), same register): rolled
+#pragma unroll 1
+    for (int j = k >> 1; j >= R; j >>= 1) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int i = lane * R + r;
+        const float of = __shfl_xor_sync(0xffffffffu, f[r], j / R);
+        const int oi = __shfl_xor_sync(0xffffffffu, ix[r], j / R);
+        const bool lower = (i & j) == 0;
+        const bool up = ((lower ? i : (i ^ j)) & k) != 0;
+        const float a_low = lower ? f[r] : of, a_high = lower ? of : f[r];
+        if ((a_low > a_high) == up) {
+          f[r] = of;
+          ix[r] = oi;
+        }
+        if (i >= T_c) {
+          f[r] = -CUDART_INF_F;
+          ix[r] = -1;
+        }
+      }
+    }
+    // stages whose partner is register r ^ j of this lane: j is a compile-time constant
+#pragma unroll
+    for (int j = R / 2; j > 0; j >>= 1) {
+      if (j < k) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if ((r & j) == 0) {
+            const int i = lane * R + r;
+            const bool up = (i & k) != 0;
+            if ((f[r] > f[r | j]) == up) {
+              const float tf = f[r];
+              f[r] = f[r | j];
+              f[r | j] = tf;
+              const int ti = ix[r];
+              ix[r] = ix[r | j];
+              ix[r | j] = ti;
+            }
+            if (i >= T_c) {
+              f[r] = -CUDART_INF_F;
+              ix[r] = -1;
+            }
+            if ((i | j) >= T_c) {
+              f[r | j] = -CUDART_INF_F;
+              ix[r | j] = -1;
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// Sort the keys in `frac` (shared memory, T_c of them) with the network above and give the first `rem`
+// positions' tiles one more sample each.
+template <int R>
+__device__ __forceinline__ void warp_sort_and_top_up(const float* frac, int* bud, int N, int T_c, int rem, int lane) {
+  float f[R];
+  int ix[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = lane * R + r;
+    f[r] = (i < T_c) ? frac[i] : -CUDART_INF_F;
+    ix[r] = (i < T_c) ? i : -1;
+  }
+  warp_bitonic<R>(f, ix, N, T_c, lane);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = lane * R + r;
+    if (i < rem && ix[r] >= 0) bud[ix[r]] += 1;  // the entries are distinct tiles
+  }
+}
+
 // One CTA of 128 threads per head; restates tile_budgets_kernel
 // (santa_cuda_kernel.cu:577-726) step by step: m* = max_t m_t,
 // W_t = __expf(m_t - m*) * ell_t, Z, q_t = S * (W_t / Z), floor, fractional part
@@ -231,6 +314,20 @@ __global__ void __launch_bounds__(128) prop_budgets_kernel(const float* __restri
 
   int N = 1;
   while (N < T_c) N <<= 1;
+  if (N <= 256) {  // one warp sorts in registers: no barrier per stage
+    if (wq == 0) {
+      if (N <= 32)
+        warp_sort_and_top_up<1>(frac, bud, N, T_c, rem, lane);
+      else if (N == 64)
+        warp_sort_and_top_up<2>(frac, bud, N, T_c, rem, lane);
+      else if (N == 128)
+        warp_sort_and_top_up<4>(frac, bud, N, T_c, rem, lane);
+      else
+        warp_sort_and_top_up<8>(frac, bud, N, T_c, rem, lane);
+    }
+    N = 0;  // skips the shared-memory network and its top-up below
+    rem = 0;
+  }
   for (int k = 2; k <= N; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
       for (int i = tid; i < N; i += 128) {
